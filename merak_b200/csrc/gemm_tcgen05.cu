@@ -1,0 +1,443 @@
+// bf16 GEMM on 5th-generation tensor cores: C[M,N] = epilogue(alpha * A[M,K] * B[N,K]^T).
+//
+// Persistent, warp-specialised kernel (one CTA per SM):
+//   warp 0      TMA producer: tiled bulk loads of A and B k-blocks into a ring of 128B-swizzled
+//               shared-memory stages (no multicast).
+//   warp 1      allocates TMEM, then one lane issues tcgen05.mma (128 x BN x 16 per instruction)
+//               into one of two TMEM accumulator buffers and commits stage / accumulator barriers.
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread), apply
+//               bias / activation / residual / activation-derivative, store bf16 or fp32.
+// The two accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Either operand may be K-major ("row r holds the K values of output row r") or MN-major
+// (the transposed storage), so the three GEMMs of a linear layer
+//   Y = X W^T,   dX = dY W,   dW = dY^T X
+// all run from the same row-major tensors without materialising a transpose.
+//
+// Covers the GEMM call sites of the reference's Column/RowParallelLinear and lm_head
+// (Merak/core/mpu/layers.py:252,354) plus the bias/GELU/residual elementwise passes that
+// follow them there.
+#include "gemm_tcgen05.h"
+
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+
+namespace mrk {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;            // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kNumThreads = 192;
+constexpr int kFirstEpilogueWarp = 2;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* bias;
+  const __nv_bfloat16* aux_in;
+  long long ld_aux_in;
+  __nv_bfloat16* aux_out;
+  long long ld_aux_out;
+  int act;        // MrkAct
+  int aux_mode;   // MrkAuxMode
+  int flags;      // MrkGemmFlags
+  float alpha;
+  unsigned* status;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 alignment slack
+};
+
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+}
+__device__ __forceinline__ float gelu_erf_grad(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_grad(float x) {
+  const float s = 1.0f / (1.0f + __expf(-x));
+  return s * (1.0f + x * (1.0f - s));
+}
+
+__device__ __forceinline__ float apply_act(int act, float v) {
+  switch (act) {
+    case MRK_ACT_GELU_ERF: return gelu_erf(v);
+    case MRK_ACT_GELU_TANH: return gelu_tanh(v);
+    case MRK_ACT_RELU: return v > 0.f ? v : 0.f;
+    case MRK_ACT_SILU: return silu(v);
+    default: return v;
+  }
+}
+__device__ __forceinline__ float apply_act_grad(int act, float x) {
+  switch (act) {
+    case MRK_ACT_GELU_ERF: return gelu_erf_grad(x);
+    case MRK_ACT_GELU_TANH: return gelu_tanh_grad(x);
+    case MRK_ACT_RELU: return x > 0.f ? 1.f : 0.f;
+    case MRK_ACT_SILU: return silu_grad(x);
+    default: return 1.f;
+  }
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
+  // Grouped raster: 8 row-blocks share their B panel in L2 before the next group starts.
+  constexpr int kGroup = 8;
+  const int per_group = kGroup * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * kGroup;
+  const int gsz = min(num_m - first_m, kGroup);
+  const int r = tile - g * per_group;
+  m_blk = first_m + r % gsz;
+  n_blk = r / gsz;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int kStages = L::kStages;
+  constexpr uint32_t kTmemCols = (2 * BN <= 512) ? (2 * BN < 32 ? 32 : 2 * BN) : 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_base = smem + kStages * L::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
+  const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&tmem_full_bar[s]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[s]), 4 * 32);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+          mbar_arrive_expect_tx(fb, L::kStageBytes);
+          const int k0 = kb * kBlockK;
+          if (!a_mn) {
+            tma_load_2d(sa, &tma_a, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int atom = 0; atom < kBlockM / 64; ++atom)
+              tma_load_2d(sa + atom * (kBlockK * 128), &tma_a, fb, m0 + atom * 64, k0);
+          }
+          if (!b_mn) {
+            tma_load_2d(sb, &tma_b, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int atom = 0; atom < BN / 64; ++atom)
+              tma_load_2d(sb + atom * (kBlockK * 128), &tma_b, fb, n0 + atom * 64, k0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(kBlockM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t da = a_mn ? desc_mnmajor(sa, k, kBlockK) : desc_kmajor(sa, k);
+            const uint64_t db = b_mn ? desc_mnmajor(sb, k, kBlockK) : desc_kmajor(sb, k);
+            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    const bool out_f32 = (p.flags & MRK_GEMM_OUT_F32) != 0;
+    const bool accumulate = (p.flags & MRK_GEMM_ACCUMULATE) != 0;
+    const bool bias_f32 = (p.flags & MRK_GEMM_BIAS_F32) != 0;
+    const bool vec_ok = ((p.ldc & 7) == 0) && ((p.ld_aux_in & 7) == 0) && ((p.ld_aux_out & 7) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.aux_in) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.aux_out) & 15) == 0);
+    int iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      int m_blk, n_blk;
+      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const long long row = (long long)m_blk * kBlockM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n_blk * BN + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tmem_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (col0 + 32 <= p.N);
+        if (p.bias != nullptr) {
+          if (bias_f32) {
+            const float* b = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += __ldg(b + j);
+          } else {
+            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += __bfloat162float(__ldg(b + j));
+          }
+        }
+        if (row_ok) {
+          if (full && vec_ok) {
+            if (p.aux_out != nullptr) {
+              uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                    pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+            }
+            if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = apply_act(p.act, v[j]);
+            }
+            if (p.aux_mode != MRK_AUX_NONE) {
+              const uint4* src = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 a = __ldg(src + q);
+                const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = unpack_bf16x2(w[e]);
+                  if (p.aux_mode == MRK_AUX_ADD) {
+                    v[8 * q + 2 * e] += f.x;
+                    v[8 * q + 2 * e + 1] += f.y;
+                  } else {
+                    v[8 * q + 2 * e] *= apply_act_grad(p.act, f.x);
+                    v[8 * q + 2 * e + 1] *= apply_act_grad(p.act, f.y);
+                  }
+                }
+              }
+            }
+            if (out_f32) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + row * p.ldc + col0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                if (accumulate) {
+                  const float4 old = dst[q];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                dst[q] = o;
+              }
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (accumulate) {
+                  const uint4 old = dst[q];
+                  const uint32_t w[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf16x2(w[e]);
+                    v[8 * q + 2 * e] += f.x;
+                    v[8 * q + 2 * e + 1] += f.y;
+                  }
+                }
+                dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                    pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+              }
+            }
+          } else {
+            // ragged right edge or unaligned pitches: element-wise
+#pragma unroll 1
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col >= p.N) break;
+              float x = v[j];
+              if (p.aux_out != nullptr) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(x);
+              if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) x = apply_act(p.act, x);
+              if (p.aux_mode == MRK_AUX_ADD) {
+                x += __bfloat162float(p.aux_in[row * p.ld_aux_in + col]);
+              } else if (p.aux_mode == MRK_AUX_DACT) {
+                x *= apply_act_grad(p.act, __bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
+              }
+              if (out_f32) {
+                float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
+                *dst = accumulate ? (*dst + x) : x;
+              } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+                *dst = __float2bfloat16(accumulate ? (__bfloat162float(*dst) + x) : x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MRK_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MRK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     L::kTotal));
+    configured[dev & 63] = true;
+  }
+  p.num_m_blocks = (p.M + kBlockM - 1) / kBlockM;
+  p.num_n_blocks = (p.N + BN - 1) / BN;
+  p.num_k_blocks = (p.K + kBlockK - 1) / kBlockK;
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_bf16_kernel<BN><<<grid, kNumThreads, L::kTotal, stream>>>(ta, tb, p);
+  MRK_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace mrk
+
+using namespace mrk;
+
+MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, const void* bias, const void* aux_in,
+                          long long ld_aux_in, void* aux_out, long long ld_aux_out, int act, int aux_mode,
+                          int flags, float alpha, int block_n, void* stream) {
+  MRK_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %dx%dx%d", M, N, K);
+  MRK_REQUIRE(A && B && C, "gemm: null operand");
+  MRK_REQUIRE(aux_mode == MRK_AUX_NONE || aux_in != nullptr, "gemm: aux_mode set without aux_in");
+  const bool a_mn = flags & MRK_GEMM_A_MN, b_mn = flags & MRK_GEMM_B_MN;
+  int bn = block_n;
+  if (bn == 0) {
+    // Heuristic: widest tile that still fills the SMs reasonably; narrow tiles for small N.
+    const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    bn = (N <= 128 || tiles256 < sm_count()) ? 128 : 256;
+    if (N <= 64) bn = 64;
+  }
+  MRK_REQUIRE(bn == 64 || bn == 128 || bn == 256, "gemm: block_n must be 64, 128 or 256");
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d(&ta, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBlockK, kBlockM, 3);
+  else       rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, kBlockK, 3);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_2d(&tb, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBlockK, (uint32_t)bn, 3);
+  else       rc = make_tmap_2d(&tb, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, kBlockK, 3);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = bias;
+  p.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in); p.ld_aux_in = ld_aux_in;
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out); p.ld_aux_out = ld_aux_out;
+  p.act = act; p.aux_mode = aux_mode; p.flags = flags; p.alpha = alpha;
+  p.status = status_word_device();
+  MRK_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256) return launch<256>(ta, tb, p, s);
+  if (bn == 128) return launch<128>(ta, tb, p, s);
+  return launch<64>(ta, tb, p, s);
+}

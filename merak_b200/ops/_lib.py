@@ -1,0 +1,121 @@
+"""ctypes bindings of the sm_100a kernel library (``_mrk_kernels.so``) and of the host-only
+native library (``_mrk_native.so``).
+
+The kernel library is mandatory on a machine with a GPU: :func:`kernels` raises instead of
+letting callers fall back silently to eager PyTorch.  On a CPU-only machine the ops in this
+package run their PyTorch reference implementations, which is what the CPU test-suite checks.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_KERNEL_LIB_PATH = os.path.join(_PKG_DIR, "_mrk_kernels.so")
+_NATIVE_LIB_PATH = os.path.join(_PKG_DIR, "_mrk_native.so")
+
+_lock = threading.Lock()
+_kernels = None
+_native = None
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+
+class KernelError(RuntimeError):
+    """A native entry point returned a non-zero code."""
+
+
+def _maybe_build():
+    if os.environ.get("MERAK_B200_NO_BUILD") == "1":
+        return
+    try:
+        from .. import build as _build
+
+        _build.build()
+    except Exception as exc:  # pragma: no cover - surfaced by the caller
+        raise RuntimeError("building the native libraries failed: %s" % exc) from exc
+
+
+def _declare(lib):
+    def sig(name, restype, *argtypes):
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.restype = restype
+            fn.argtypes = list(argtypes)
+
+    sig("mrk_last_error", ctypes.c_char_p)
+    sig("mrk_status_read", ctypes.c_uint, c_int)
+    sig("mrk_abi_version", c_int)
+    sig("mrk_gemm_bf16", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll,
+        c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p)
+    return lib
+
+
+def kernels():
+    """Returns the loaded kernel library, building it first if the shared object is missing."""
+    global _kernels
+    if _kernels is not None:
+        return _kernels
+    with _lock:
+        if _kernels is None:
+            if not os.path.exists(_KERNEL_LIB_PATH):
+                _maybe_build()
+            if not os.path.exists(_KERNEL_LIB_PATH):
+                raise RuntimeError(
+                    "merak_b200: %s is missing; run `python -m merak_b200.build`" % _KERNEL_LIB_PATH)
+            _kernels = _declare(ctypes.CDLL(_KERNEL_LIB_PATH))
+    return _kernels
+
+
+def native():
+    """Returns the host-only native library (AutoPipe partitioner, schedule simulator)."""
+    global _native
+    if _native is not None:
+        return _native
+    with _lock:
+        if _native is None:
+            if not os.path.exists(_NATIVE_LIB_PATH):
+                _maybe_build()
+            if not os.path.exists(_NATIVE_LIB_PATH):
+                raise RuntimeError(
+                    "merak_b200: %s is missing; run `python -m merak_b200.build`" % _NATIVE_LIB_PATH)
+            _native = ctypes.CDLL(_NATIVE_LIB_PATH)
+    return _native
+
+
+def use_kernels(*tensors) -> bool:
+    """True when the inputs live on a CUDA device, i.e. the sm_100a kernels must run."""
+    return len(tensors) > 0 and all(t is None or t.is_cuda for t in tensors) and any(
+        t is not None for t in tensors)
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = kernels().mrk_last_error()
+        raise KernelError("%s failed (code %d): %s" % (what, rc, msg.decode() if msg else "?"))
+
+
+def status(clear: bool = False) -> int:
+    """Status word of the current device: non-zero after a device-side bounded wait gave up."""
+    return int(kernels().mrk_status_read(1 if clear else 0))
+
+
+def assert_status_ok(what: str = ""):
+    s = status(clear=True)
+    if s != 0:
+        raise KernelError("device status word is 0x%x after %s (1=mbarrier timeout, 2=peer-flag "
+                          "timeout, 4=bad argument)" % (s, what or "kernel"))
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
