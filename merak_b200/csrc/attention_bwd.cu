@@ -1,0 +1,484 @@
+// Flash attention backward on tcgen05.  One CTA owns one 128-key block of one (batch, kv head)
+// and walks over the query blocks (and, for grouped-query attention, over the query heads that
+// share the kv head).  Five products per (key block, query block):
+//
+//   S^T  = K Q^T          P^T  = exp2(S^T * scale - lse)
+//   dP^T = V dO^T         dS^T = P^T o (dP^T - delta) * scale
+//   dV  += P^T dO         dK  += dS^T Q            dQ += dS K     (dQ through fp32 red.add)
+//
+// All five run on the tensor core with TMEM accumulators: S^T, dP^T (consumed by the compute
+// warps one key row per thread), dK and dV (resident for the whole CTA), and a dQ partial that is
+// drained to global memory with vector reductions.  P^T and dS^T are written to shared memory once
+// and serve as the K-major A operand of dV/dK and as the MN-major A operand of dQ; the Q and dO
+// tiles likewise serve as K-major B of the first two products and MN-major B of dK/dV.
+//
+//   warp 0       TMA producer           warp 1   UMMA issuer
+//   warps 2..9   compute: two warpgroups, each handles 64 of the 128 query columns of every row.
+#include "attention.h"
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+
+namespace mrk {
+
+int make_bshd_tmap(CUtensorMap* out, const void* base, int D, int L, int H, int B, long long sb, long long ss,
+                   long long sh, int box_rows);
+
+constexpr int kBwdThreads = 320;
+
+struct AttnBwdParams {
+  const float* lse;        // [B, H, Lq]
+  const float* delta;      // [B, H, Lq]  rowsum(dO o O)
+  float* dq_acc;           // [B, Lq, H, D] fp32, zero-initialised
+  __nv_bfloat16* dk;       // [B, Lk, Hkv, D] strides below
+  __nv_bfloat16* dv;
+  long long dk_sb, dk_ss, dk_sh;
+  long long dv_sb, dv_ss, dv_sh;
+  const float* key_bias;   // optional [B, Lk]
+  int B, H, Hkv, Lq, Lk;
+  int causal;
+  float scale, scale_log2;
+  unsigned* status;
+};
+
+template <int D>
+struct AttnBwdSmem {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kTile;
+  static constexpr int kStageOff = 2 * kTile;                    // [Q_j | dO_j] per stage
+  static constexpr int kPOff = kStageOff + kStages * 2 * kTile;  // P^T   [128 kv][128 q] bf16
+  static constexpr int kDSOff = kPOff + 32768;                   // dS^T
+  static constexpr int kStatOff = kDSOff + 32768;                // lse2 / delta, double buffered
+  static constexpr int kBarOff = kStatOff + 2 * 2 * 128 * 4;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+__device__ __forceinline__ void compute_bar_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                const AttnBwdParams p) {
+  using L = AttnBwdSmem<D>;
+  constexpr int kStages = L::kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSCol = 0, kDPCol = 128, kDKCol = 256, kDVCol = 256 + D;
+  constexpr uint32_t kDQCol = (D == 64) ? 384 : 0;   // D=128: the dQ partial reuses the S^T columns
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* kv_full = bars;                    // 1
+  uint64_t* qdo_full = bars + 1;               // kStages
+  uint64_t* qdo_empty = qdo_full + kStages;    // kStages
+  uint64_t* sp_full = qdo_empty + kStages;     // 1
+  uint64_t* pds_full = sp_full + 1;            // 1 (256 arrivals)
+  uint64_t* dq_full = pds_full + 1;            // 1
+  uint64_t* dq_empty = dq_full + 1;            // 1 (256 arrivals)
+  uint64_t* dkv_full = dq_empty + 1;           // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stat = reinterpret_cast<float*>(smem + L::kStatOff);  // [2 buffers][lse2[128] | delta[128]]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_blk = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  const int k0 = kv_blk * 128;
+  const int shift = p.Lk - p.Lq;   // key k visible to query q iff k <= q + shift (causal)
+  const int n_qblocks = (p.Lq + 127) / 128;
+  int j_begin = 0;
+  if (p.causal) {
+    const int first_q = k0 - shift;          // smallest query index that sees key k0
+    j_begin = first_q <= 0 ? 0 : first_q / 128;
+  }
+  const int iters_per_head = max(0, n_qblocks - j_begin);
+  const int total_iters = iters_per_head * group;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(smem_u32(kv_full), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&qdo_full[s]), 1);
+      mbar_init(smem_u32(&qdo_empty[s]), 1);
+    }
+    mbar_init(smem_u32(sp_full), 1);
+    mbar_init(smem_u32(pds_full), 256);
+    mbar_init(smem_u32(dq_full), 1);
+    mbar_init(smem_u32(dq_empty), 256);
+    mbar_init(smem_u32(dkv_full), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+    tma_prefetch_desc(&tdo);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t k_smem = smem_u32(smem + L::kKOff), v_smem = smem_u32(smem + L::kVOff);
+  const uint32_t p_smem = smem_u32(smem + L::kPOff), ds_smem = smem_u32(smem + L::kDSOff);
+
+  if (warp == 0) {
+    if (lane == 0 && total_iters > 0) {
+      mbar_arrive_expect_tx(smem_u32(kv_full), 2 * L::kTile);
+#pragma unroll
+      for (int a = 0; a < D / 64; ++a) {
+        tma_load_4d(k_smem + a * 16384, &tk, smem_u32(kv_full), a * 64, k0, hkv, b);
+        tma_load_4d(v_smem + a * 16384, &tv, smem_u32(kv_full), a * 64, k0, hkv, b);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int it = 0; it < total_iters; ++it) {
+        const int h = hkv * group + it / iters_per_head;
+        const int j = j_begin + it % iters_per_head;
+        if (!mbar_wait(smem_u32(&qdo_empty[stage]), phase ^ 1u, abort_flag, p.status)) break;
+        const uint32_t fb = smem_u32(&qdo_full[stage]);
+        const uint32_t qs = smem_u32(smem + L::kStageOff + stage * 2 * L::kTile);
+        const uint32_t dos = qs + L::kTile;
+        mbar_arrive_expect_tx(fb, 2 * L::kTile);
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a) {
+          tma_load_4d(qs + a * 16384, &tq, fb, a * 64, j * 128, h, b);
+          tma_load_4d(dos + a * 16384, &tdo, fb, a * 64, j * 128, h, b);
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && total_iters > 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_dkv = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);
+      bool ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, p.status);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int it = 0; it < total_iters && ok; ++it) {
+        ok = mbar_wait(smem_u32(&qdo_full[stage]), phase, abort_flag, p.status);
+        if (!ok) break;
+        if (D == 128 && it > 0) {
+          ok = mbar_wait(smem_u32(dq_empty), (it - 1) & 1, abort_flag, p.status);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        const uint32_t qs = smem_u32(smem + L::kStageOff + stage * 2 * L::kTile);
+        const uint32_t dos = qs + L::kTile;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tmem_base + kSCol, desc_kmajor(k_smem + (k / 4) * 16384, k % 4),
+                       desc_kmajor(qs + (k / 4) * 16384, k % 4), idesc_s, k != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tmem_base + kDPCol, desc_kmajor(v_smem + (k / 4) * 16384, k % 4),
+                       desc_kmajor(dos + (k / 4) * 16384, k % 4), idesc_s, k != 0 ? 1u : 0u);
+        umma_commit(smem_u32(sp_full));
+        ok = mbar_wait(smem_u32(pds_full), it & 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)   // contraction over the 128 queries of this block
+          umma_bf16_ss(tmem_base + kDVCol, desc_kmajor(p_smem + (k / 4) * 16384, k % 4),
+                       desc_mnmajor(dos, k, 128), idesc_dkv, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(tmem_base + kDKCol, desc_kmajor(ds_smem + (k / 4) * 16384, k % 4),
+                       desc_mnmajor(qs, k, 128), idesc_dkv, (it | k) != 0 ? 1u : 0u);
+        if (D == 64 && it > 0) {
+          ok = mbar_wait(smem_u32(dq_empty), (it - 1) & 1, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)   // contraction over the 128 keys of this CTA
+          umma_bf16_ss(tmem_base + kDQCol, desc_mnmajor(ds_smem, k, 128), desc_mnmajor(k_smem, k, 128),
+                       idesc_dq, k != 0 ? 1u : 0u);
+        umma_commit(smem_u32(&qdo_empty[stage]));
+        umma_commit(smem_u32(dq_full));
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(smem_u32(dkv_full));
+    }
+  } else {
+    // ------------------------------- compute warps -------------------------------
+    const int cw = warp - 2;                 // 0..7
+    const int wg = cw >> 2;                  // column half
+    const int quad = warp & 3;               // TMEM lane quadrant
+    const int r = quad * 32 + lane;          // key row inside the block (also query row for dQ)
+    const int key = k0 + r;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const int tid_c = threadIdx.x - 64;      // 0..255
+    const float kbias = (p.key_bias && key < p.Lk) ? p.key_bias[(long long)b * p.Lk + key] * 1.4426950408889634f : 0.f;
+    bool ok = true;
+    for (int it = 0; it < total_iters && ok; ++it) {
+      const int h = hkv * group + it / iters_per_head;
+      const int j = j_begin + it % iters_per_head;
+      const int q0 = j * 128;
+      float* st = stat + (it & 1) * 256;
+      {
+        // stage lse (in log2 units) and delta of this query block
+        const int q = q0 + (tid_c & 127);
+        const long long off = ((long long)b * p.H + h) * p.Lq + q;
+        if (tid_c < 128) st[tid_c] = q < p.Lq ? p.lse[off] * 1.4426950408889634f : INFINITY;
+        else             st[tid_c] = q < p.Lq ? p.delta[off] : 0.f;
+      }
+      compute_bar_sync();
+      ok = mbar_wait(smem_u32(sp_full), it & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool need_mask = (key >= p.Lk) || (p.causal && (k0 + 127 > q0 + shift));
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = wg * 64 + c * 32;
+        uint32_t s[32], dp[32];
+        tmem_ld32(tmem_base + lane_off + kSCol + col0, s);
+        tmem_ld32(tmem_base + lane_off + kDPCol + col0, dp);
+        tmem_wait_ld();
+        uint32_t pk[16], dsk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pv[2], dv_[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = col0 + i + e;
+            const float lse2 = st[col], dl = st[128 + col];
+            float x = fmaf(__uint_as_float(s[i + e]), p.scale_log2, kbias - lse2);
+            float pe = exp2f(x);
+            if (need_mask) {
+              const int q = q0 + col;
+              if (key >= p.Lk || (p.causal && key > q + shift)) pe = 0.f;
+            }
+            pv[e] = pe;
+            dv_[e] = pe * (__uint_as_float(dp[i + e]) - dl) * p.scale;
+          }
+          pk[i >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dsk[i >> 1] = pack_bf16x2(dv_[0], dv_[1]);
+        }
+        // columns col0..col0+31 -> atom (col0/64), 16-byte chunks ((col0%64)/8)..+3 of row r
+        const uint32_t atom = (uint32_t)(col0 >> 6), ch0 = (uint32_t)((col0 & 63) >> 3);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t off = atom * 16384 + sw128_offset((uint32_t)r, ch0 + q4);
+          *reinterpret_cast<uint4*>(smem + L::kPOff + off) =
+              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(smem + L::kDSOff + off) =
+              make_uint4(dsk[4 * q4], dsk[4 * q4 + 1], dsk[4 * q4 + 2], dsk[4 * q4 + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(pds_full));
+      // drain the dQ partial of this (key block, query block)
+      ok = mbar_wait(smem_u32(dq_full), it & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        const int q = q0 + r;
+        float* dst = p.dq_acc + (((long long)b * p.Lq + q) * p.H + h) * D + wg * (D / 2);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + lane_off + kDQCol + wg * (D / 2) + c * 32, v);
+          tmem_wait_ld();
+          if (q < p.Lq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              red_add_v4(dst + c * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                         __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));   // dS already carries the scale
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(dq_empty));
+    }
+    // dK, dV of this key block
+    if (total_iters > 0 && ok) {
+      ok = mbar_wait(smem_u32(dkv_full), 0, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dk_dst = p.dk + (long long)b * p.dk_sb + (long long)key * p.dk_ss + (long long)hkv * p.dk_sh + wg * (D / 2);
+      __nv_bfloat16* dv_dst = p.dv + (long long)b * p.dv_sb + (long long)key * p.dv_ss + (long long)hkv * p.dv_sh + wg * (D / 2);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t a[32], v[32];
+        if (total_iters > 0) {
+          tmem_ld32(tmem_base + lane_off + kDKCol + wg * (D / 2) + c * 32, a);
+          tmem_ld32(tmem_base + lane_off + kDVCol + wg * (D / 2) + c * 32, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { a[i] = 0u; v[i] = 0u; }
+        }
+        if (key < p.Lk) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 wk, wv;
+            // dS^T was already multiplied by the softmax scale
+            wk.x = pack_bf16x2(__uint_as_float(a[8 * q4]), __uint_as_float(a[8 * q4 + 1]));
+            wk.y = pack_bf16x2(__uint_as_float(a[8 * q4 + 2]), __uint_as_float(a[8 * q4 + 3]));
+            wk.z = pack_bf16x2(__uint_as_float(a[8 * q4 + 4]), __uint_as_float(a[8 * q4 + 5]));
+            wk.w = pack_bf16x2(__uint_as_float(a[8 * q4 + 6]), __uint_as_float(a[8 * q4 + 7]));
+            wv.x = pack_bf16x2(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
+            wv.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+            wv.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+            wv.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+            reinterpret_cast<uint4*>(dk_dst + c * 32)[q4] = wk;
+            reinterpret_cast<uint4*>(dv_dst + c * 32)[q4] = wv;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]; also zeroes the fp32 dQ accumulator row.
+template <int D>
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ delta, float* __restrict__ dq_acc, int B, int H, int Lq,
+                                     long long o_sb, long long o_ss, long long o_sh, long long do_sb,
+                                     long long do_ss, long long do_sh) {
+  // one warp per (b, q, h) row
+  const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const long long total = (long long)B * Lq * H;
+  if (row >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int h = (int)(row % H);
+  const long long bq = row / H;
+  const int q = (int)(bq % Lq);
+  const int b = (int)(bq / Lq);
+  const __nv_bfloat16* po = o + b * o_sb + q * o_ss + h * o_sh;
+  const __nv_bfloat16* pd = dout + b * do_sb + q * do_ss + h * do_sh;
+  float acc = 0.f;
+  constexpr int kPer = D / 32;   // 2 or 4 elements per lane
+  if (kPer == 2) {
+    const float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(po)[lane]);
+    const float2 c = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(pd)[lane]);
+    acc = a.x * c.x + a.y * c.y;
+  } else {
+    const uint2 ua = reinterpret_cast<const uint2*>(po)[lane];
+    const uint2 uc = reinterpret_cast<const uint2*>(pd)[lane];
+    const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y), c0 = unpack_bf16x2(uc.x), c1 = unpack_bf16x2(uc.y);
+    acc = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[((long long)b * H + h) * Lq + q] = acc;
+  float* z = dq_acc + row * D;
+  if (kPer == 2) reinterpret_cast<float2*>(z)[lane] = make_float2(0.f, 0.f);
+  else           reinterpret_cast<float4*>(z)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+// dq (bf16, strided [B,Lq,H,D]) = dq_acc (fp32 contiguous)
+__global__ void attn_bwd_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int H, int Lq,
+                                        int D, long long total_vec, long long sb, long long ss, long long sh) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one 8-element vector each
+  if (i >= total_vec) return;
+  const int vec_per_row = D / 8;
+  const long long row = i / vec_per_row;
+  const int vc = (int)(i % vec_per_row);
+  const int h = (int)(row % H);
+  const long long bq = row / H;
+  const int q = (int)(bq % Lq);
+  const long long b = bq / Lq;
+  const float4 x = reinterpret_cast<const float4*>(acc)[2 * i], y = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+  uint4 w = make_uint4(pack_bf16x2(x.x, x.y), pack_bf16x2(x.z, x.w), pack_bf16x2(y.x, y.y), pack_bf16x2(y.z, y.w));
+  *reinterpret_cast<uint4*>(dq + b * sb + q * ss + h * sh + vc * 8) = w;
+}
+
+template <int D>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const AttnBwdParams& p, cudaStream_t stream) {
+  using L = AttnBwdSmem<D>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MRK_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MRK_CUDA_OK(cudaFuncSetAttribute(attn_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured[dev & 63] = true;
+  }
+  dim3 grid((p.Lk + 127) / 128, p.Hkv, p.B);
+  attn_bwd_kernel<D><<<grid, kBwdThreads, L::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  MRK_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace mrk
+
+using namespace mrk;
+
+MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                         const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                         const long long* strides /* q,k,v,o,do,dq,dk,dv: (sb,ss,sh) each = 24 values */,
+                         int causal, float scale, void* stream) {
+  MRK_REQUIRE(D == 64 || D == 128, "attention backward: head dim %d not supported (64 or 128)", D);
+  MRK_REQUIRE(B > 0 && H > 0 && Hkv > 0 && Lq > 0 && Lk > 0 && H % Hkv == 0, "attention backward: bad sizes");
+  const long long* sq = strides, *sk = strides + 3, *sv = strides + 6, *so = strides + 9, *sdo = strides + 12,
+                 *sdq = strides + 15, *sdk = strides + 18, *sdv = strides + 21;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_bshd_tmap(&tq, q, D, Lq, H, B, sq[0], sq[1], sq[2], 128))) return rc;
+  if ((rc = make_bshd_tmap(&tk, k, D, Lk, Hkv, B, sk[0], sk[1], sk[2], 128))) return rc;
+  if ((rc = make_bshd_tmap(&tv, v, D, Lk, Hkv, B, sv[0], sv[1], sv[2], 128))) return rc;
+  if ((rc = make_bshd_tmap(&tdo, dout, D, Lq, H, B, sdo[0], sdo[1], sdo[2], 128))) return rc;
+  const long long rows = (long long)B * Lq * H;
+  {
+    const int warps_per_block = 8;
+    const long long blocks = (rows + warps_per_block - 1) / warps_per_block;
+    if (D == 64)
+      attn_bwd_prep_kernel<64><<<(unsigned)blocks, warps_per_block * 32, 0, s>>>(
+          (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, dq_acc, B, H, Lq, so[0], so[1], so[2], sdo[0],
+          sdo[1], sdo[2]);
+    else
+      attn_bwd_prep_kernel<128><<<(unsigned)blocks, warps_per_block * 32, 0, s>>>(
+          (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, dq_acc, B, H, Lq, so[0], so[1], so[2], sdo[0],
+          sdo[1], sdo[2]);
+    MRK_CUDA_OK(cudaGetLastError());
+  }
+  AttnBwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.dk_sb = sdk[0]; p.dk_ss = sdk[1]; p.dk_sh = sdk[2];
+  p.dv_sb = sdv[0]; p.dv_ss = sdv[1]; p.dv_sh = sdv[2];
+  p.key_bias = key_bias;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Lq = Lq; p.Lk = Lk; p.causal = causal;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word_device();
+  MRK_REQUIRE(p.status != nullptr, "attention backward: status word unavailable");
+  rc = (D == 64) ? launch_bwd<64>(tq, tk, tv, tdo, p, s) : launch_bwd<128>(tq, tk, tv, tdo, p, s);
+  if (rc) return rc;
+  {
+    const long long total_vec = rows * (D / 8);
+    const int threads = 256;
+    attn_bwd_dq_cast_kernel<<<(unsigned)((total_vec + threads - 1) / threads), threads, 0, s>>>(
+        dq_acc, (__nv_bfloat16*)dq, H, Lq, D, total_vec, sdq[0], sdq[1], sdq[2]);
+    MRK_CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}

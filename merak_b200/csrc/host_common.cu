@@ -53,8 +53,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// The encode call is a driver-API function: it needs the primary context bound to the calling
+// thread, which a thread that has only seen cudaSetDevice (autograd worker threads) may lack.
+static void bind_context_once() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 static EncodeTiledFn encode_fn() {
   static EncodeTiledFn fn = nullptr;
+  bind_context_once();
   if (fn) return fn;
   void* p = nullptr;
   cudaDriverEntryPointQueryResult q;
@@ -120,6 +131,28 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of(swizzle),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   MRK_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(3d) failed with %d", (int)r);
+  return 0;
+}
+
+int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[4],
+                 const uint64_t strides_elems[3], const uint32_t box[4], int swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  MRK_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled entry point not found");
+  MRK_REQUIRE(((uintptr_t)base & 15) == 0, "tensor map base %p is not 16-byte aligned", base);
+  cuuint64_t d[4], st[3];
+  cuuint32_t bx[4], estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 4; ++i) { d[i] = dims[i]; bx[i] = box[i]; }
+  for (int i = 0; i < 3; ++i) {
+    st[i] = strides_elems[i] * (uint64_t)elem_bytes;
+    MRK_REQUIRE(st[i] % 16 == 0, "tensor map stride %d (%llu elements) is not a multiple of 16 bytes", i,
+                (unsigned long long)strides_elems[i]);
+  }
+  CUresult r = fn(out, dtype_of(elem_bytes, true), 4, const_cast<void*>(base), d, st, bx, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of(swizzle), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MRK_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(4d) failed with %d dims=(%llu,%llu,%llu,%llu)", (int)r,
+              (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+              (unsigned long long)dims[3]);
   return 0;
 }
 

@@ -41,6 +41,10 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
                  uint64_t outer, uint64_t stride_mid_elems, uint64_t stride_outer_elems,
                  uint32_t box_inner, uint32_t box_mid, uint32_t box_outer, int swizzle);
 
+// 4-D variant used for [batch, seq, head, dim] tensors: dims (d0..d3), strides for d1..d3 in elements.
+int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[4],
+                 const uint64_t strides_elems[3], const uint32_t box[4], int swizzle);
+
 int sm_count();
 
 }  // namespace mrk

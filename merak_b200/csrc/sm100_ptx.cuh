@@ -22,7 +22,8 @@ enum StatusBits : unsigned {
   kStatusBadArgument = 1u << 2,    // a kernel rejected its arguments
 };
 
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s (peer-flag waits, globaltimer)
+constexpr long long kWaitBudgetCycles = 4000000000ll;          // 2-4 s of SM cycles (mbarrier waits)
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -94,12 +95,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  long long t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
+    if ((it & 255u) == 0u) {
+      // The SM cycle counter is cheap to read; the budget is a few seconds at any SM clock.
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      const long long now = clock64();
+      if (it == 256u) {
+        t0 = now;
+      } else if (now - t0 > kWaitBudgetCycles) {
         *abort_flag = 1;
         raise_status(status, kStatusMbarTimeout);
         return false;
@@ -130,6 +135,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
       " [%0], [%1, {%3, %4, %5}], [%2];"
       :
       : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap* m, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src_smem, int32_t x,

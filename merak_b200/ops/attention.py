@@ -1,0 +1,126 @@
+"""Fused scaled-dot-product attention (flash attention) with a hand-written backward.
+
+Tensors use the ``[batch, seq, heads, head_dim]`` layout so that Q/K/V can be strided views of a
+fused QKV projection and the output feeds the next GEMM without a transpose.  On CUDA the
+tcgen05 kernels in ``csrc/attention_{fwd,bwd}.cu`` run; on CPU the same math is evaluated with
+PyTorch (fp32), which is also the oracle of the GPU tests.
+
+Stands in for the eager ``matmul -> softmax -> dropout -> matmul`` attention of the models the
+reference trains (examples/models/gpt2/config.py:28) and for the SDPA / FlashAttention-2 branch
+of Merak/core/sequence_parallel/modeling/llama.py:24-160.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_declared = False
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    lib = _lib.kernels()
+    c = ctypes
+    lib.mrk_attn_fwd.restype = c.c_int
+    lib.mrk_attn_fwd.argtypes = [c.c_void_p] * 6 + [c.c_int] * 6 + [c.c_longlong] * 12 + [
+        c.c_int, c.c_float, c.c_void_p]
+    lib.mrk_attn_bwd.restype = c.c_int
+    lib.mrk_attn_bwd.argtypes = [c.c_void_p] * 12 + [c.c_int] * 6 + [c.c_void_p, c.c_int, c.c_float, c.c_void_p]
+    _declared = True
+
+
+def attention_reference(q, k, v, key_bias=None, causal=False, scale=None):
+    """fp32 evaluation of softmax(scale * q k^T + bias + causal mask) v on [B, L, H, D] tensors."""
+    B, Lq, H, D = q.shape
+    Lk, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    if Hkv != H:
+        kf = kf.repeat_interleave(H // Hkv, dim=1)
+        vf = vf.repeat_interleave(H // Hkv, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if key_bias is not None:
+        s = s + key_bias.float()[:, None, None, :]
+    if causal:
+        keep = torch.ones(Lq, Lk, dtype=torch.bool, device=q.device).tril(Lk - Lq)
+        s = s.masked_fill(~keep, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def _strides3(t):
+    return (t.stride(0), t.stride(1), t.stride(2))
+
+
+def _tma_ok(t) -> bool:
+    return (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all((s * t.element_size()) % 16 == 0
+                                                                  for s in _strides3(t)))
+
+
+class _FlashAttention(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, key_bias, causal, scale):
+        _declare()
+        B, Lq, H, D = q.shape
+        Lk, Hkv = k.shape[1], k.shape[2]
+        q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
+        out = torch.empty((B, Lq, H, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        kb = key_bias.float().contiguous() if key_bias is not None else None
+        rc = _lib.kernels().mrk_attn_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(kb),
+            B, H, Hkv, Lq, Lk, D, *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
+            int(causal), float(scale), _lib.stream_ptr())
+        _lib.check(rc, "mrk_attn_fwd")
+        ctx.save_for_backward(q, k, v, out, lse, kb)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, kb = ctx.saved_tensors
+        B, Lq, H, D = q.shape
+        Lk, Hkv = k.shape[1], k.shape[2]
+        if not _tma_ok(dout):
+            dout = dout.contiguous()
+        dq = torch.empty((B, Lq, H, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
+        delta = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+        dq_acc = torch.empty((B, Lq, H, D), dtype=torch.float32, device=q.device)
+        strides = []
+        for t in (q, k, v, out, dout, dq, dk, dv):
+            strides.extend(_strides3(t))
+        arr = (ctypes.c_longlong * 24)(*strides)
+        rc = _lib.kernels().mrk_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(kb),
+            B, H, Hkv, Lq, Lk, D, ctypes.cast(arr, ctypes.c_void_p), int(ctx.causal), float(ctx.scale),
+            _lib.stream_ptr())
+        _lib.check(rc, "mrk_attn_bwd")
+        return dq, dk, dv, None, None, None
+
+
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                    key_bias: Optional[torch.Tensor] = None, causal: bool = False,
+                    scale: Optional[float] = None) -> torch.Tensor:
+    """``softmax(scale * q k^T + key_bias + causal mask) v``.
+
+    q ``[B, Lq, H, D]``; k, v ``[B, Lk, Hkv, D]`` with ``H % Hkv == 0`` (grouped-query attention);
+    ``key_bias`` ``[B, Lk]`` additive (0 / large negative for padding).  ``D`` is 64 or 128 on CUDA.
+    """
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _lib.use_kernels(q, k, v):
+        return attention_reference(q, k, v, key_bias, causal, scale)
+    assert q.dtype == torch.bfloat16, "tcgen05 attention takes bf16"
+    assert D in (64, 128), "head_dim must be 64 or 128 on the sm_100a path"
+    return _FlashAttention.apply(q, k, v, key_bias, causal, scale)
