@@ -1,0 +1,295 @@
+// Fused (dropout +) residual-add + LayerNorm / RMSNorm, forward and backward.
+//
+//   z = dropout(x, p) + residual            (both optional)
+//   y = (z - mean) * rstd * gamma + beta    (LayerNorm)     or     z * rstd * gamma   (RMSNorm)
+//
+// One pass over HBM per direction: the row lives in registers between the statistics and the
+// normalisation; the dropout mask is regenerated from a counter-based generator in the backward
+// pass instead of being stored.  Replaces torch.nn.LayerNorm / LlamaRMSNorm and the separate
+// dropout + residual kernels of the reference's blocks
+// (Merak/core/tensor_parallel/transformer_blocks.py:34-42).
+#include "elementwise.h"
+#include "host_common.h"
+#include "philox.cuh"
+#include "sm100_ptx.cuh"
+
+namespace mrk {
+
+constexpr int kMaxVecPerThread = 4;   // 8 elements per vector
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w) t += red[w];
+  return t;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                            pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+// gamma/beta may be bf16 or fp32
+__device__ __forceinline__ void load8p(const void* p, int idx, bool f32, float (&f)[8]) {
+  if (f32) load8f(reinterpret_cast<const float*>(p) + idx, f);
+  else load8(reinterpret_cast<const __nv_bfloat16*>(p) + idx, f);
+}
+
+struct NormFwdParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* residual;   // optional
+  const void* gamma;
+  const void* beta;                // optional (nullptr for RMSNorm)
+  __nv_bfloat16* y;
+  __nv_bfloat16* z;                // optional: pre-norm sum (needed when residual/dropout is used)
+  float* mean;                     // optional (LayerNorm)
+  float* rstd;
+  const unsigned long long* rng;   // [seed, offset] on device; nullptr = no dropout
+  unsigned long long call_id;
+  float p_drop;
+  float eps;
+  long long M;
+  int H;
+  int rms;
+  int params_f32;
+};
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const NormFwdParams p) {
+  __shared__ float red[THREADS / 32];
+  const int nvec = p.H / 8;
+  const bool drop = p.rng != nullptr && p.p_drop > 0.f;
+  const float keep_scale = drop ? 1.f / (1.f - p.p_drop) : 1.f;
+  unsigned long long seed = 0, offset = 0;
+  if (drop) { seed = p.rng[0]; offset = p.rng[1]; }
+  for (long long row = blockIdx.x; row < p.M; row += gridDim.x) {
+    float v[kMaxVecPerThread][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVecPerThread; ++it) {
+      const int vi = threadIdx.x + it * THREADS;
+      if (vi < nvec) {
+        load8(p.x + row * p.H + vi * 8, v[it]);
+        if (drop) {
+          const unsigned long long e = (unsigned long long)row * p.H + (unsigned long long)vi * 8;
+          float r[8];
+          philox_uniform8(seed, offset + p.call_id, e, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[it][i] = r[i] < p.p_drop ? 0.f : v[it][i] * keep_scale;
+        }
+        if (p.residual) {
+          float r[8];
+          load8(p.residual + row * p.H + vi * 8, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[it][i] += r[i];
+        }
+        if (p.z) {
+          store8(p.z + row * p.H + vi * 8, v[it]);
+          // statistics are taken on the rounded values the backward pass will read
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[it][i] = __bfloat162float(__float2bfloat16(v[it][i]));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += p.rms ? v[it][i] * v[it][i] : v[it][i];
+      }
+    }
+    float mean = 0.f, rstd;
+    if (p.rms) {
+      const float ms = block_sum<THREADS>(sum, red) / p.H;
+      rstd = rsqrtf(ms + p.eps);
+    } else {
+      mean = block_sum<THREADS>(sum, red) / p.H;
+      float sq = 0.f;
+#pragma unroll
+      for (int it = 0; it < kMaxVecPerThread; ++it) {
+        const int vi = threadIdx.x + it * THREADS;
+        if (vi < nvec) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { const float d = v[it][i] - mean; sq += d * d; }
+        }
+      }
+      const float var = block_sum<THREADS>(sq, red) / p.H;
+      rstd = rsqrtf(var + p.eps);
+    }
+    if (threadIdx.x == 0) {
+      if (p.mean) p.mean[row] = mean;
+      if (p.rstd) p.rstd[row] = rstd;
+    }
+#pragma unroll
+    for (int it = 0; it < kMaxVecPerThread; ++it) {
+      const int vi = threadIdx.x + it * THREADS;
+      if (vi < nvec) {
+        float g[8], o[8];
+        load8p(p.gamma, vi * 8, p.params_f32, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (v[it][i] - mean) * rstd * g[i];
+        if (p.beta) {
+          float bb[8];
+          load8p(p.beta, vi * 8, p.params_f32, bb);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += bb[i];
+        }
+        store8(p.y + row * p.H + vi * 8, o);
+      }
+    }
+  }
+}
+
+struct NormBwdParams {
+  const __nv_bfloat16* dy;
+  const __nv_bfloat16* z;          // input of the norm (x + residual after dropout)
+  const __nv_bfloat16* dz_extra;   // optional gradient arriving on the residual stream
+  const void* gamma;
+  const float* mean;               // nullptr for RMSNorm
+  const float* rstd;
+  __nv_bfloat16* dres;             // gradient wrt z (residual branch); may alias dx when no dropout
+  __nv_bfloat16* dx;               // optional: gradient wrt x (through dropout)
+  float* dgamma;                   // fp32 [H], accumulated with atomics
+  float* dbeta;                    // optional
+  const unsigned long long* rng;
+  unsigned long long call_id;
+  float p_drop;
+  long long M;
+  int H;
+  int rms;
+  int params_f32;
+};
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p) {
+  __shared__ float red[THREADS / 32];
+  const int nvec = p.H / 8;
+  const bool drop = p.rng != nullptr && p.p_drop > 0.f && p.dx != nullptr;
+  const float keep_scale = drop ? 1.f / (1.f - p.p_drop) : 1.f;
+  unsigned long long seed = 0, offset = 0;
+  if (drop) { seed = p.rng[0]; offset = p.rng[1]; }
+  float dg[kMaxVecPerThread][8], db[kMaxVecPerThread][8];
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dg[it][i] = 0.f; db[it][i] = 0.f; }
+
+  for (long long row = blockIdx.x; row < p.M; row += gridDim.x) {
+    const float mean = p.mean ? p.mean[row] : 0.f;
+    const float rstd = p.rstd[row];
+    float xh[kMaxVecPerThread][8], dxh[kMaxVecPerThread][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVecPerThread; ++it) {
+      const int vi = threadIdx.x + it * THREADS;
+      if (vi < nvec) {
+        float dyv[8], g[8];
+        load8(p.dy + row * p.H + vi * 8, dyv);
+        load8(p.z + row * p.H + vi * 8, xh[it]);
+        load8p(p.gamma, vi * 8, p.params_f32, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[it][i] = (xh[it][i] - mean) * rstd;
+          dxh[it][i] = dyv[i] * g[i];
+          dg[it][i] += dyv[i] * xh[it][i];
+          db[it][i] += dyv[i];
+          s1 += dxh[it][i];
+          s2 += dxh[it][i] * xh[it][i];
+        }
+      }
+    }
+    if (p.rms) s1 = 0.f; else s1 = block_sum<THREADS>(s1, red) / p.H;
+    s2 = block_sum<THREADS>(s2, red) / p.H;
+#pragma unroll
+    for (int it = 0; it < kMaxVecPerThread; ++it) {
+      const int vi = threadIdx.x + it * THREADS;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (dxh[it][i] - s1 - xh[it][i] * s2);
+        if (p.dz_extra) {
+          float e[8];
+          load8(p.dz_extra + row * p.H + vi * 8, e);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += e[i];
+        }
+        if (p.dres) store8(p.dres + row * p.H + vi * 8, o);
+        if (p.dx && p.dx != p.dres) {
+          if (drop) {
+            const unsigned long long e = (unsigned long long)row * p.H + (unsigned long long)vi * 8;
+            float r[8];
+            philox_uniform8(seed, offset + p.call_id, e, r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = r[i] < p.p_drop ? 0.f : o[i] * keep_scale;
+          }
+          store8(p.dx + row * p.H + vi * 8, o);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < kMaxVecPerThread; ++it) {
+    const int vi = threadIdx.x + it * THREADS;
+    if (vi < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(p.dgamma + vi * 8 + i, dg[it][i]);
+        if (p.dbeta) atomicAdd(p.dbeta + vi * 8 + i, db[it][i]);
+      }
+    }
+  }
+}
+
+}  // namespace mrk
+
+using namespace mrk;
+
+MRK_API int mrk_norm_fwd(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                         void* z, float* mean, float* rstd, const void* rng, unsigned long long call_id,
+                         float p_drop, float eps, long long M, int H, int rms, int params_f32, void* stream) {
+  MRK_REQUIRE(H % 8 == 0 && H <= 256 * 8 * kMaxVecPerThread, "norm: hidden size %d unsupported", H);
+  MRK_REQUIRE(M > 0, "norm: empty input");
+  NormFwdParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, gamma, beta, (__nv_bfloat16*)y,
+                  (__nv_bfloat16*)z, mean, rstd, (const unsigned long long*)rng, call_id, p_drop, eps, M, H, rms,
+                  params_f32};
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long cap = (long long)sm_count() * 16;
+  const unsigned grid = (unsigned)(M < cap ? M : cap);
+  if (H <= 128 * 8 * kMaxVecPerThread) norm_fwd_kernel<128><<<grid, 128, 0, s>>>(p);
+  else norm_fwd_kernel<256><<<grid, 256, 0, s>>>(p);
+  MRK_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, const void* gamma, const float* mean,
+                         const float* rstd, void* dres, void* dx, float* dgamma, float* dbeta, const void* rng,
+                         unsigned long long call_id, float p_drop, long long M, int H, int rms, int params_f32,
+                         void* stream) {
+  MRK_REQUIRE(H % 8 == 0 && H <= 256 * 8 * kMaxVecPerThread, "norm: hidden size %d unsupported", H);
+  MRK_REQUIRE(M > 0, "norm: empty input");
+  NormBwdParams p{(const __nv_bfloat16*)dy, (const __nv_bfloat16*)z, (const __nv_bfloat16*)dz_extra, gamma, mean,
+                  rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, (const unsigned long long*)rng,
+                  call_id, p_drop, M, H, rms, params_f32};
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long cap = (long long)sm_count() * 4;
+  const unsigned grid = (unsigned)(M < cap ? M : cap);
+  if (H <= 128 * 8 * kMaxVecPerThread) norm_bwd_kernel<128><<<grid, 128, 0, s>>>(p);
+  else norm_bwd_kernel<256><<<grid, 256, 0, s>>>(p);
+  MRK_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -54,6 +54,26 @@ def _declare(lib):
     sig("mrk_abi_version", c_int)
     sig("mrk_gemm_bf16", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll,
         c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p)
+    c_ull = ctypes.c_ulonglong
+    P = c_void_p
+    sig("mrk_attn_fwd", c_int, *([P] * 6 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, P]))
+    sig("mrk_attn_bwd", c_int, *([P] * 12 + [c_int] * 6 + [P, c_int, c_float, P]))
+    sig("mrk_norm_fwd", c_int, P, P, P, P, P, P, P, P, P, c_ull, c_float, c_float, c_ll, c_int, c_int, c_int, P)
+    sig("mrk_norm_bwd", c_int, P, P, P, P, P, P, P, P, P, P, P, c_ull, c_float, c_ll, c_int, c_int, c_int, P)
+    sig("mrk_ce_stats", c_int, P, P, P, c_ll, c_int, c_ll, c_int, c_int, c_int, P)
+    sig("mrk_ce_finalize", c_int, P, c_int, c_ll, P, P, P, P, P, c_ll, c_int, P)
+    sig("mrk_ce_grad", c_int, P, P, P, P, P, c_ll, c_int, c_ll, c_ll, c_int, c_int, c_int, P)
+    sig("mrk_adamw", c_int, P, P, P, P, P, P, P, P, c_ll, c_int, c_int, P)
+    sig("mrk_sumsq", c_int, P, c_ll, P, c_int, P)
+    sig("mrk_clip_coef", c_int, P, c_float, c_float, P, P, P, P)
+    sig("mrk_embedding_fwd", c_int, P, P, P, P, c_int, P, c_ll, c_int, P)
+    sig("mrk_embedding_bwd", c_int, P, P, P, c_ll, c_int, c_int, c_int, c_int, P)
+    sig("mrk_rope", c_int, P, P, P, P, P, c_ll, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, P)
+    sig("mrk_swiglu_fwd", c_int, P, P, c_ll, c_int, c_ll, P)
+    sig("mrk_swiglu_bwd", c_int, P, P, P, c_ll, c_int, c_ll, P)
+    sig("mrk_colsum", c_int, P, P, c_ll, c_int, c_ll, P)
+    sig("mrk_dropout", c_int, P, P, c_ll, c_float, P, c_ull, P)
+    sig("mrk_scaled_cast", c_int, P, P, c_ll, P, c_float, c_int, c_int, c_int, P)
     return lib
 
 

@@ -19,21 +19,8 @@ import torch
 
 from . import _lib
 
-_declared = False
-
-
 def _declare():
-    global _declared
-    if _declared:
-        return
-    lib = _lib.kernels()
-    c = ctypes
-    lib.mrk_attn_fwd.restype = c.c_int
-    lib.mrk_attn_fwd.argtypes = [c.c_void_p] * 6 + [c.c_int] * 6 + [c.c_longlong] * 12 + [
-        c.c_int, c.c_float, c.c_void_p]
-    lib.mrk_attn_bwd.restype = c.c_int
-    lib.mrk_attn_bwd.argtypes = [c.c_void_p] * 12 + [c.c_int] * 6 + [c.c_void_p, c.c_int, c.c_float, c.c_void_p]
-    _declared = True
+    _lib.kernels()
 
 
 def attention_reference(q, k, v, key_bias=None, causal=False, scale=None):

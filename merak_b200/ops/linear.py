@@ -1,0 +1,127 @@
+"""Linear layers on the tcgen05 GEMM with hand-written backward passes.
+
+* ``linear(x, weight, bias, residual)``: ``y = x W^T + b (+ residual)``.
+* ``mlp(x, w1, b1, w2, b2, act, residual)``: ``act(x W1^T + b1) W2^T + b2 (+ residual)`` with the
+  activation applied in the first GEMM's epilogue and its derivative applied in the epilogue of
+  the backward data-gradient GEMM, so no elementwise kernel runs between the four GEMMs.
+
+Weight gradients are produced by transposed-operand GEMMs straight from the row-major
+activations (no transposes are materialised).  When a parameter carries an fp32 ``main_grad``
+buffer (set up by the optimizer), the gradient is accumulated into it by the GEMM epilogue and
+autograd sees ``None`` - the "gradient accumulation fusion" that replaces the reference's
+flatten/cast/accumulate pass (Merak/core/merak_engine.py:552-574).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from . import gemm as G
+from .elementwise import colsum
+from .norm import _param_grad
+
+
+def _as2d(x, K):
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+def _weight_grad(dy2, x2, weight):
+    """dW[N,K] = dy2^T x2, accumulated into ``weight.main_grad`` when present."""
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        G.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg.view(weight.shape), accumulate=True)
+        return None
+    dw, _ = G.gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+    return dw
+
+
+def _bias_grad(dy2, bias):
+    if bias is None or not bias.requires_grad:
+        return None
+    mg = getattr(bias, "main_grad", None)
+    if mg is not None:
+        colsum(dy2, mg.view(-1))
+        return None
+    return colsum(dy2).to(bias.dtype)
+
+
+class _Linear(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        N, K = weight.shape
+        x2 = _as2d(x, K)
+        r2 = _as2d(residual, N) if residual is not None else None
+        y, _ = G.gemm(x2, weight, bias=bias, aux_in=r2, aux_mode=G.AUX_ADD if r2 is not None else G.AUX_NONE)
+        ctx.save_for_backward(x2, weight, bias)
+        ctx.in_shape = x.shape
+        ctx.has_res = residual is not None
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, bias = ctx.saved_tensors
+        N, K = weight.shape
+        dy2 = _as2d(dy, N)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx2, _ = G.gemm(dy2, weight, b_mn=True)
+            dx = dx2.view(ctx.in_shape)
+        dw = _weight_grad(dy2, x2, weight) if weight.requires_grad else None
+        db = _bias_grad(dy2, bias)
+        return dx, dw, db, (dy if ctx.has_res else None)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not _lib.use_kernels(x, weight) or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        y = F.linear(x, weight, bias)
+        return y + residual if residual is not None else y
+    return _Linear.apply(x, weight, bias, residual)
+
+
+class _MLP(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, act, residual):
+        F1, K = w1.shape
+        N = w2.shape[0]
+        x2 = _as2d(x, K)
+        r2 = _as2d(residual, N) if residual is not None else None
+        a, h = G.gemm(x2, w1, bias=b1, act=act, want_preact=True)
+        y, _ = G.gemm(a, w2, bias=b2, aux_in=r2, aux_mode=G.AUX_ADD if r2 is not None else G.AUX_NONE)
+        ctx.save_for_backward(x2, w1, b1, w2, b2, h, a)
+        ctx.act, ctx.in_shape, ctx.has_res = act, x.shape, residual is not None
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1, b1, w2, b2, h, a = ctx.saved_tensors
+        N = w2.shape[0]
+        dy2 = _as2d(dy, N)
+        # dh = (dy W2) * act'(h): derivative applied in the GEMM epilogue
+        dh, _ = G.gemm(dy2, w2, b_mn=True, act=ctx.act, aux_in=h, aux_mode=G.AUX_DACT)
+        dw2 = _weight_grad(dy2, a, w2) if w2.requires_grad else None
+        db2 = _bias_grad(dy2, b2)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx2, _ = G.gemm(dh, w1, b_mn=True)
+            dx = dx2.view(ctx.in_shape)
+        dw1 = _weight_grad(dh, x2, w1) if w1.requires_grad else None
+        db1 = _bias_grad(dh, b1)
+        return dx, dw1, db1, dw2, db2, None, (dy if ctx.has_res else None)
+
+
+def mlp(x, w1, b1, w2, b2, act: int = G.ACT_GELU_ERF, residual=None):
+    """``act(x w1^T + b1) w2^T + b2 (+ residual)``."""
+    if not _lib.use_kernels(x, w1, w2) or x.dtype != torch.bfloat16:
+        hdn = G.act_forward(act, F.linear(x, w1, b1))
+        y = F.linear(hdn, w2, b2)
+        return y + residual if residual is not None else y
+    return _MLP.apply(x, w1, b1, w2, b2, act, residual)
