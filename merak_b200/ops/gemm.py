@@ -118,8 +118,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         a = _pad_pitch(a)
         b = _pad_pitch(b)
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         assert not accumulate
+        if N % 8 != 0:      # keep rows 16-byte aligned so the epilogue can use vector stores
+            out = torch.empty((M, (N + 7) // 8 * 8), dtype=out_dtype, device=a.device)[:, :N]
+        else:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     else:
         assert out.shape == (M, N) and out.stride(1) == 1
     assert out.dtype in (torch.bfloat16, torch.float32)
@@ -140,7 +143,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         flags |= _F_B_MN
     pre = None
     if want_preact:
-        pre = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        pre = torch.empty((M, (N + 7) // 8 * 8), dtype=torch.bfloat16, device=a.device)[:, :N]
     if aux_mode != AUX_NONE:
         assert aux_in is not None and aux_in.shape == (M, N) and aux_in.dtype == torch.bfloat16
         assert aux_in.stride(1) == 1
