@@ -8,8 +8,10 @@ int mrk_norm_fwd(const void* x, const void* residual, const void* gamma, const v
                  float* mean, float* rstd, const void* rng, unsigned long long call_id, float p_drop, float eps,
                  long long M, int H, int rms, int params_f32, void* stream);
 int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, const void* gamma, const float* mean,
-                 const float* rstd, void* dres, void* dx, float* dgamma, float* dbeta, const void* rng,
-                 unsigned long long call_id, float p_drop, long long M, int H, int rms, int params_f32, void* stream);
+                 const float* rstd, void* dres, void* dx, float* dgamma, float* dbeta, float* workspace,
+                 const void* rng, unsigned long long call_id, float p_drop, long long M, int H, int rms,
+                 int params_f32, void* stream);
+int mrk_norm_bwd_workspace_rows();
 int mrk_ce_stats(const void* logits, const long long* labels, float* stats, long long M, int V, long long ld,
                  int vocab_start, int ignore_index, int logits_f32, void* stream);
 int mrk_ce_finalize(const float* stats, int tp_parts, long long part_stride, const long long* labels, float* lse,

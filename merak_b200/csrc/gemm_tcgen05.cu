@@ -45,6 +45,7 @@ struct GemmParams {
   float alpha;
   unsigned* status;
   int num_m_blocks, num_n_blocks, num_k_blocks;
+  int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
 };
 
 template <int BN>
@@ -159,7 +160,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int num_units = p.num_m_blocks * p.num_n_blocks * p.num_splits;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -167,11 +168,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
         const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full_bar[stage]);
@@ -205,14 +208,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
@@ -222,7 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             const uint64_t da = a_mn ? desc_mnmajor(sa, k, kBlockK) : desc_kmajor(sa, k);
             const uint64_t db = b_mn ? desc_mnmajor(sb, k, kBlockK) : desc_kmajor(sb, k);
-            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty_bar[stage]));
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -243,9 +248,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         ((reinterpret_cast<uintptr_t>(p.aux_out) & 15) == 0);
     int iter = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++iter) {
       int m_blk, n_blk;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      const bool split_k = p.num_splits > 1;
+      const bool first_split = (unit % p.num_splits) == 0;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status);
@@ -266,7 +273,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
         const bool full = (col0 + 32 <= p.N);
-        if (p.bias != nullptr) {
+        if (p.bias != nullptr && first_split) {
           if (bias_f32) {
             const float* b = reinterpret_cast<const float*>(p.bias) + col0;
 #pragma unroll
@@ -279,7 +286,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (full || col0 + j < p.N) v[j] += __bfloat162float(__ldg(b + j));
           }
         }
-        if (row_ok) {
+        if (row_ok && split_k) {
+          // partial sum of one K range: reduce into the fp32 output
+          float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+          if (full && vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),
+                           "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+          } else {
+#pragma unroll 1
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, v[j]);
+          }
+        } else if (row_ok) {
           if (full && vec_ok) {
             if (p.aux_out != nullptr) {
               uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
@@ -393,7 +412,22 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
   p.num_n_blocks = (p.N + BN - 1) / BN;
   p.num_k_blocks = (p.K + kBlockK - 1) / kBlockK;
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  // Split-K when the output has too few tiles to fill the SMs (weight gradients: small [N,K]
+  // outputs contracted over all tokens).  Only for fp32 accumulate outputs without an activation.
+  p.num_splits = 1;
+  const bool can_split = (p.flags & MRK_GEMM_OUT_F32) && (p.flags & MRK_GEMM_ACCUMULATE) &&
+                         p.act == MRK_ACT_NONE && p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr;
+  if (can_split && tiles * 2 <= sm_count() && p.num_k_blocks >= 16) {
+    int want = sm_count() / tiles;
+    const int max_by_k = p.num_k_blocks / 8;
+    if (want > max_by_k) want = max_by_k;
+    if (want > 32) want = 32;
+    if (want > 1) p.num_splits = want;
+  }
+  p.kb_per_split = (p.num_k_blocks + p.num_splits - 1) / p.num_splits;
+  p.num_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  const int units = tiles * p.num_splits;
+  const int grid = units < sm_count() ? units : sm_count();
   gemm_bf16_kernel<BN><<<grid, kNumThreads, L::kTotal, stream>>>(ta, tb, p);
   MRK_CUDA_OK(cudaGetLastError());
   return 0;
@@ -415,7 +449,9 @@ MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   if (bn == 0) {
     // Heuristic: widest tile that still fills the SMs reasonably; narrow tiles for small N.
     const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    bn = (N <= 128 || tiles256 < sm_count()) ? 128 : 256;
+    const bool splittable = (flags & MRK_GEMM_OUT_F32) && (flags & MRK_GEMM_ACCUMULATE) && act == MRK_ACT_NONE &&
+                            aux_mode == MRK_AUX_NONE && aux_out == nullptr && K >= 1024;
+    bn = (N <= 128 || (tiles256 < sm_count() && !splittable)) ? 128 : 256;
     if (N <= 64) bn = 64;
   }
   MRK_REQUIRE(bn == 64 || bn == 128 || bn == 256, "gemm: block_n must be 64, 128 or 256");

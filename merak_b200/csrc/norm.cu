@@ -15,7 +15,6 @@
 
 namespace mrk {
 
-constexpr int kMaxVecPerThread = 4;   // 8 elements per vector
 
 template <int THREADS>
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -74,7 +73,7 @@ struct NormFwdParams {
   int params_f32;
 };
 
-template <int THREADS>
+template <int THREADS, int kMaxVecPerThread>
 __global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const NormFwdParams p) {
   __shared__ float red[THREADS / 32];
   const int nvec = p.H / 8;
@@ -164,8 +163,9 @@ struct NormBwdParams {
   const float* rstd;
   __nv_bfloat16* dres;             // gradient wrt z (residual branch); may alias dx when no dropout
   __nv_bfloat16* dx;               // optional: gradient wrt x (through dropout)
-  float* dgamma;                   // fp32 [H], accumulated with atomics
+  float* dgamma;                   // fp32 [H]: written by the reduction over `partial`
   float* dbeta;                    // optional
+  float* partial;                  // workspace [gridDim.x][2][H]: per-block partial sums
   const unsigned long long* rng;
   unsigned long long call_id;
   float p_drop;
@@ -175,7 +175,7 @@ struct NormBwdParams {
   int params_f32;
 };
 
-template <int THREADS>
+template <int THREADS, int kMaxVecPerThread>
 __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p) {
   __shared__ float red[THREADS / 32];
   const int nvec = p.H / 8;
@@ -242,16 +242,38 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p
       }
     }
   }
+  // every thread owns distinct columns: store this block's partial sums, reduced by a second kernel
+  float* pg = p.partial + (long long)blockIdx.x * 2 * p.H;
 #pragma unroll
   for (int it = 0; it < kMaxVecPerThread; ++it) {
     const int vi = threadIdx.x + it * THREADS;
     if (vi < nvec) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        atomicAdd(p.dgamma + vi * 8 + i, dg[it][i]);
-        if (p.dbeta) atomicAdd(p.dbeta + vi * 8 + i, db[it][i]);
-      }
+      reinterpret_cast<float4*>(pg + vi * 8)[0] = make_float4(dg[it][0], dg[it][1], dg[it][2], dg[it][3]);
+      reinterpret_cast<float4*>(pg + vi * 8)[1] = make_float4(dg[it][4], dg[it][5], dg[it][6], dg[it][7]);
+      reinterpret_cast<float4*>(pg + p.H + vi * 8)[0] = make_float4(db[it][0], db[it][1], db[it][2], db[it][3]);
+      reinterpret_cast<float4*>(pg + p.H + vi * 8)[1] = make_float4(db[it][4], db[it][5], db[it][6], db[it][7]);
     }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ partial, int blocks, int H, float* __restrict__ dgamma,
+                       float* __restrict__ dbeta) {
+  // grid.y = 0: gamma, 1: beta; 8 row-lanes x 32 columns per block
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int rl = threadIdx.x >> 5;
+  const int which = blockIdx.y;
+  float* out = which == 0 ? dgamma : dbeta;
+  if (out == nullptr) return;
+  float acc = 0.f;
+  if (col < H)
+    for (int b = rl; b < blocks; b += 8) acc += partial[((long long)b * 2 + which) * H + col];
+  __shared__ float sm[8][33];
+  sm[rl][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (rl == 0 && col < H) {
+    for (int k = 1; k < 8; ++k) acc += sm[k][threadIdx.x & 31];
+    out[col] = acc;
   }
 }
 
@@ -259,37 +281,56 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p
 
 using namespace mrk;
 
+template <int T, int V>
+static void launch_norm_fwd(const NormFwdParams& p, unsigned grid, cudaStream_t s) {
+  norm_fwd_kernel<T, V><<<grid, T, 0, s>>>(p);
+}
+template <int T, int V>
+static void launch_norm_bwd(const NormBwdParams& p, unsigned grid, cudaStream_t s) {
+  norm_bwd_kernel<T, V><<<grid, T, 0, s>>>(p);
+}
+
 MRK_API int mrk_norm_fwd(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
                          void* z, float* mean, float* rstd, const void* rng, unsigned long long call_id,
                          float p_drop, float eps, long long M, int H, int rms, int params_f32, void* stream) {
-  MRK_REQUIRE(H % 8 == 0 && H <= 256 * 8 * kMaxVecPerThread, "norm: hidden size %d unsupported", H);
+  MRK_REQUIRE(H % 8 == 0 && H <= 8192, "norm: hidden size %d unsupported", H);
   MRK_REQUIRE(M > 0, "norm: empty input");
   NormFwdParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, gamma, beta, (__nv_bfloat16*)y,
                   (__nv_bfloat16*)z, mean, rstd, (const unsigned long long*)rng, call_id, p_drop, eps, M, H, rms,
                   params_f32};
   cudaStream_t s = (cudaStream_t)stream;
-  const long long cap = (long long)sm_count() * 16;
+  const long long cap = (long long)sm_count() * 32;
   const unsigned grid = (unsigned)(M < cap ? M : cap);
-  if (H <= 128 * 8 * kMaxVecPerThread) norm_fwd_kernel<128><<<grid, 128, 0, s>>>(p);
-  else norm_fwd_kernel<256><<<grid, 256, 0, s>>>(p);
+  if (H <= 1024) launch_norm_fwd<128, 1>(p, grid, s);
+  else if (H <= 2048) launch_norm_fwd<128, 2>(p, grid, s);
+  else if (H <= 4096) launch_norm_fwd<256, 2>(p, grid, s);
+  else launch_norm_fwd<256, 4>(p, grid, s);
   MRK_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
+// Number of workspace rows (each 2*H floats) mrk_norm_bwd may use.
+MRK_API int mrk_norm_bwd_workspace_rows() { return sm_count() * 8; }
+
 MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, const void* gamma, const float* mean,
-                         const float* rstd, void* dres, void* dx, float* dgamma, float* dbeta, const void* rng,
-                         unsigned long long call_id, float p_drop, long long M, int H, int rms, int params_f32,
-                         void* stream) {
-  MRK_REQUIRE(H % 8 == 0 && H <= 256 * 8 * kMaxVecPerThread, "norm: hidden size %d unsupported", H);
-  MRK_REQUIRE(M > 0, "norm: empty input");
+                         const float* rstd, void* dres, void* dx, float* dgamma, float* dbeta, float* workspace,
+                         const void* rng, unsigned long long call_id, float p_drop, long long M, int H, int rms,
+                         int params_f32, void* stream) {
+  MRK_REQUIRE(H % 8 == 0 && H <= 8192, "norm: hidden size %d unsupported", H);
+  MRK_REQUIRE(M > 0 && workspace != nullptr, "norm: empty input or missing workspace");
   NormBwdParams p{(const __nv_bfloat16*)dy, (const __nv_bfloat16*)z, (const __nv_bfloat16*)dz_extra, gamma, mean,
-                  rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, (const unsigned long long*)rng,
-                  call_id, p_drop, M, H, rms, params_f32};
+                  rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, workspace,
+                  (const unsigned long long*)rng, call_id, p_drop, M, H, rms, params_f32};
   cudaStream_t s = (cudaStream_t)stream;
-  const long long cap = (long long)sm_count() * 4;
+  const long long cap = (long long)sm_count() * 8;
   const unsigned grid = (unsigned)(M < cap ? M : cap);
-  if (H <= 128 * 8 * kMaxVecPerThread) norm_bwd_kernel<128><<<grid, 128, 0, s>>>(p);
-  else norm_bwd_kernel<256><<<grid, 256, 0, s>>>(p);
+  if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
+  else if (H <= 2048) launch_norm_bwd<128, 2>(p, grid, s);
+  else if (H <= 4096) launch_norm_bwd<256, 2>(p, grid, s);
+  else launch_norm_bwd<256, 4>(p, grid, s);
+  MRK_CUDA_OK(cudaGetLastError());
+  dim3 rgrid((H + 31) / 32, 2);
+  norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(workspace, (int)grid, H, dgamma, dbeta);
   MRK_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -20,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from ..ops import gemm as G
-from ..ops.attention import flash_attention
+from ..ops.attention import flash_attention, flash_attention_packed
 from ..ops.cross_entropy import softmax_cross_entropy
 from ..ops.elementwise import dropout, embedding_sum
 from ..ops.linear import linear as k_linear, mlp as k_mlp
@@ -79,8 +79,9 @@ class BertSelfAttention(nn.Module):
         B, L, _ = x.shape
         qkv = self.qkv(x)
         local = qkv.shape[-1] // 3
-        qkv = qkv.view(B, L, 3, local // self.attention_head_size, self.attention_head_size)
-        ctx = flash_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], key_bias=key_bias, causal=False)
+        heads = local // self.attention_head_size
+        qkv = qkv.view(B, L, 3 * heads, self.attention_head_size)
+        ctx = flash_attention_packed(qkv, heads, heads, key_bias=key_bias, causal=False)
         return ctx.reshape(B, L, local)
 
 

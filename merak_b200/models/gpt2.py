@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 
 from ..ops import gemm as G
-from ..ops.attention import flash_attention
+from ..ops.attention import flash_attention, flash_attention_packed
 from ..ops.cross_entropy import softmax_cross_entropy
 from ..ops.elementwise import dropout, embedding_sum
 from ..ops.linear import linear as k_linear, mlp as k_mlp
@@ -75,8 +75,8 @@ class GPT2Attention(nn.Module):
         B, L, _ = x.shape
         qkv = self.c_attn(x)
         local = qkv.shape[-1] // 3
-        qkv = qkv.view(B, L, 3, local // self.head_dim, self.head_dim)
-        ctx = flash_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal=True)
+        heads = local // self.head_dim
+        ctx = flash_attention_packed(qkv.view(B, L, 3 * heads, self.head_dim), heads, heads, causal=True)
         ctx = ctx.reshape(B, L, local)
         if residual is not None and not (self.training and self.resid_pdrop > 0):
             return self.c_proj(ctx, residual)

@@ -96,6 +96,66 @@ class _FlashAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class _FlashAttentionPacked(torch.autograd.Function):
+    """Attention on a packed projection output ``[B, L, Hq + 2*Hkv, D]`` (query heads first, then key
+    heads, then value heads).  The backward writes dQ, dK and dV straight into one packed gradient
+    tensor, so no per-slice gradient tensors are materialised and summed."""
+
+    @staticmethod
+    def forward(ctx, qkv, hq, hkv, key_bias, causal, scale):
+        if not _tma_ok(qkv):
+            qkv = qkv.contiguous()
+        B, L, _, D = qkv.shape
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+        out = torch.empty((B, L, hq, D), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((B, hq, L), dtype=torch.float32, device=qkv.device)
+        kb = key_bias.float().contiguous() if key_bias is not None else None
+        rc = _lib.kernels().mrk_attn_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(kb),
+            B, hq, hkv, L, L, D, *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
+            int(causal), float(scale), _lib.stream_ptr())
+        _lib.check(rc, "mrk_attn_fwd")
+        ctx.save_for_backward(qkv, out, lse, kb)
+        ctx.meta = (hq, hkv, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, kb = ctx.saved_tensors
+        hq, hkv, causal, scale = ctx.meta
+        B, L, _, D = qkv.shape
+        if not _tma_ok(dout):
+            dout = dout.contiguous()
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :hq], dqkv[:, :, hq:hq + hkv], dqkv[:, :, hq + hkv:]
+        delta = torch.empty((B, hq, L), dtype=torch.float32, device=qkv.device)
+        dq_acc = torch.empty((B, L, hq, D), dtype=torch.float32, device=qkv.device)
+        strides = []
+        for t in (q, k, v, out, dout, dq, dk, dv):
+            strides.extend(_strides3(t))
+        arr = (ctypes.c_longlong * 24)(*strides)
+        rc = _lib.kernels().mrk_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(kb),
+            B, hq, hkv, L, L, D, ctypes.cast(arr, ctypes.c_void_p), int(causal), float(scale), _lib.stream_ptr())
+        _lib.check(rc, "mrk_attn_bwd")
+        return dqkv, None, None, None, None, None
+
+
+def flash_attention_packed(qkv: torch.Tensor, num_q_heads: int, num_kv_heads: int,
+                           key_bias: Optional[torch.Tensor] = None, causal: bool = False,
+                           scale: Optional[float] = None) -> torch.Tensor:
+    """Self-attention on ``qkv`` of shape ``[B, L, Hq + 2*Hkv, D]``; returns ``[B, L, Hq, D]``."""
+    D = qkv.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _lib.use_kernels(qkv) or qkv.dtype != torch.bfloat16 or D not in (64, 128):
+        q, k, v = (qkv[:, :, :num_q_heads], qkv[:, :, num_q_heads:num_q_heads + num_kv_heads],
+                   qkv[:, :, num_q_heads + num_kv_heads:])
+        return attention_reference(q, k, v, key_bias, causal, scale)
+    return _FlashAttentionPacked.apply(qkv, num_q_heads, num_kv_heads, key_bias, causal, scale)
+
+
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                     key_bias: Optional[torch.Tensor] = None, causal: bool = False,
                     scale: Optional[float] = None) -> torch.Tensor:

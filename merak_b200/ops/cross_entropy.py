@@ -72,7 +72,7 @@ class _SoftmaxCrossEntropy(torch.autograd.Function):
         _lib.check(_lib.kernels().mrk_ce_grad(lg.data_ptr(), lab.data_ptr(), lse.data_ptr(), gscale.data_ptr(),
                                               dl.data_ptr(), M, V, lg.stride(0), pitch, int(vocab_start),
                                               int(ignore_index), f32, _lib.stream_ptr()), "mrk_ce_grad")
-        return dl[:, :V].view(shape) if pitch == V else dl[:, :V].reshape(shape), None, None, None, None, None
+        return dl[:, :V].unflatten(0, shape[:-1]), None, None, None, None, None
 
 
 def softmax_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,

@@ -86,11 +86,13 @@ class _FusedNorm(torch.autograd.Function):
                 e2 = e2.contiguous()
         dres = torch.empty_like(dy2)
         dx = torch.empty_like(dy2) if p_drop > 0.0 else dres
-        dgamma = torch.zeros(H, dtype=torch.float32, device=dy.device)
-        dbeta = torch.zeros(H, dtype=torch.float32, device=dy.device) if has_bias else None
-        rc = _lib.kernels().mrk_norm_bwd(
+        dgamma = torch.empty(H, dtype=torch.float32, device=dy.device)
+        dbeta = torch.empty(H, dtype=torch.float32, device=dy.device) if has_bias else None
+        lib = _lib.kernels()
+        ws = torch.empty((lib.mrk_norm_bwd_workspace_rows(), 2, H), dtype=torch.float32, device=dy.device)
+        rc = lib.mrk_norm_bwd(
             dy2.data_ptr(), z.data_ptr(), _lib.ptr(e2), weight.data_ptr(), _lib.ptr(mean), rstd.data_ptr(),
-            dres.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), _lib.ptr(dbeta), _lib.ptr(rng), call_id,
+            dres.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), _lib.ptr(dbeta), ws.data_ptr(), _lib.ptr(rng), call_id,
             float(p_drop), M, H, int(rms), int(params_f32), _lib.stream_ptr())
         _lib.check(rc, "mrk_norm_bwd")
         dw = _param_grad(weight, dgamma)

@@ -64,3 +64,22 @@ def test_attention_strided_qkv():
     torch.cuda.synchronize()
     _lib.assert_status_ok("attention")
     assert (out.float() - ref.float()).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("hq,hkv,D,causal", [(4, 4, 64, False), (8, 2, 64, True), (4, 4, 128, True)])
+def test_attention_packed(hq, hkv, D, causal):
+    from merak_b200.ops.attention import flash_attention_packed
+    B, L = 2, 256
+    torch.manual_seed(2)
+    qkv = torch.randn(B, L, hq + 2 * hkv, D, device="cuda").bfloat16().requires_grad_()
+    out = flash_attention_packed(qkv, hq, hkv, causal=causal)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok("attention")
+    r = qkv.detach().float().requires_grad_()
+    ref = attention_reference(r[:, :, :hq], r[:, :, hq:hq + hkv], r[:, :, hq + hkv:], None, causal, None)
+    ref.backward(dout.float())
+    assert (out.float() - ref).abs().max().item() < 3e-2
+    err = (qkv.grad.float() - r.grad).abs().max().item() / (r.grad.abs().max().item() + 1e-6)
+    assert err < 3e-2, err

@@ -78,3 +78,18 @@ def test_gemm_accumulate(out_dtype):
     _lib.assert_status_ok("gemm")
     ref = base.float().cpu() + 0.5 * (a.float().cpu().t() @ b.float().cpu())
     _check(out.cpu(), ref, K, "accumulate")
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 16384), (1024, 4096, 16384), (3072, 1024, 8192), (256, 256, 4096)])
+def test_gemm_split_k_wgrad(shape):
+    """Small fp32-accumulate outputs with a long contraction take the split-K path."""
+    M, N, K = shape
+    torch.manual_seed(4)
+    a, b = _rand((K, M), 0.1), _rand((K, N), 0.1)
+    out = torch.randn(M, N, device="cuda")
+    base = out.clone()
+    G.gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok("gemm")
+    ref = base + a.float().t() @ b.float()
+    _check(out, ref, K, "split-k")
