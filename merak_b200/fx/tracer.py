@@ -1,0 +1,125 @@
+"""Symbolic tracing front-ends.
+
+``trace_model`` turns an ``nn.Module`` into a ``torch.fx.GraphModule`` whose ``call_module``
+nodes are the coarse blocks the sharder works with:
+
+* ``method='fx'``: a ``torch.fx.Tracer`` subclass with a leaf-module policy (every ``torch.nn``
+  builtin, every class the user lists, and the framework's own block classes are leaves).  This
+  replaces the Hugging Face tracer the reference depends on
+  (Merak/core/fx/tracer/_symbolic_trace.py:32-127), which no longer exists in transformers 5.x.
+* ``method='dynamo'``: ``torch.export`` (Merak/core/fx/tracer/_dynamo_trace.py:22-60); the flat
+  ATen graph has no module nodes, so only tensor-parallel degree 1 is supported on that path.
+
+``make_dummy_inputs`` builds small CPU inputs from a model config for tracing
+(Merak/core/fx/tracer/utils.py:62-191).
+"""
+from __future__ import annotations
+
+import inspect
+from typing import Dict, Iterable, Optional, Sequence, Tuple, Type
+
+import torch
+import torch.fx as fx
+import torch.nn as nn
+
+
+def framework_leaf_classes() -> Tuple[type, ...]:
+    from ..models import bert, gpt2, llama
+    from ..ops import modules as km
+    from ..parallel import layers as pl
+    classes = [gpt2.GPT2Block, bert.BertLayer, bert.BertEmbeddings, bert.BertOnlyMLMHead,
+               llama.LlamaDecoderLayer, km.Linear, km.LayerNorm, km.RMSNorm, km.Embedding, km.Dropout,
+               pl.ColumnParallelLinear, pl.RowParallelLinear, pl.VocabParallelEmbedding, pl.ColParallelConv2d]
+    try:
+        from ..models import moe
+        classes.append(moe.MoEDecoderLayer)
+    except Exception:
+        pass
+    return tuple(classes)
+
+
+class MerakTracer(fx.Tracer):
+    """fx tracer whose leaves are whole blocks (Merak/core/fx/tracer/tracers.py:20-35)."""
+
+    def __init__(self, leaf_modules: Iterable[type] = (), leaf_names: Iterable[str] = ()):
+        super().__init__()
+        self.leaf_classes = tuple(leaf_modules) + framework_leaf_classes()
+        self.leaf_names = set(leaf_names)
+
+    def is_leaf_module(self, m: nn.Module, qualname: str) -> bool:
+        if isinstance(m, self.leaf_classes) or qualname in self.leaf_names:
+            return True
+        return super().is_leaf_module(m, qualname)
+
+
+def get_concrete_args(model: nn.Module, input_names: Sequence[str]) -> Dict[str, object]:
+    """Defaults for every forward() parameter that is not a traced input."""
+    sig = inspect.signature(model.forward)
+    out = {}
+    for name, p in sig.parameters.items():
+        if name in input_names or p.kind in (p.VAR_POSITIONAL, p.VAR_KEYWORD):
+            continue
+        out[name] = p.default if p.default is not inspect.Parameter.empty else None
+    return out
+
+
+def fx_trace(model: nn.Module, input_names: Sequence[str], leaf_modules: Iterable[type] = ()) -> fx.GraphModule:
+    tracer = MerakTracer(leaf_modules)
+    concrete = get_concrete_args(model, input_names)
+    if "use_cache" in concrete:
+        concrete["use_cache"] = False
+    graph = tracer.trace(model, concrete_args=concrete)
+    # concrete args leave placeholders (plus an assertion on their value) behind; remove both
+    for node in list(graph.nodes):
+        if node.op == "placeholder" and node.target not in input_names:
+            for user in list(node.users):
+                if user.op == "call_function" and "assert" in getattr(user.target, "__name__", ""):
+                    graph.erase_node(user)
+            if not node.users:
+                graph.erase_node(node)
+    gm = fx.GraphModule(model, graph, class_name=type(model).__name__)
+    return gm
+
+
+def dynamo_trace(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor]) -> fx.GraphModule:
+    """``torch.export`` based tracing for models plain fx cannot handle."""
+    exported = torch.export.export(model, args=(), kwargs=dict(dummy_inputs), strict=False)
+    return exported.module()
+
+
+def trace_model(model: nn.Module, input_names: Sequence[str], method: str = "fx",
+                leaf_modules: Iterable[type] = (), dummy_inputs: Optional[Dict[str, torch.Tensor]] = None):
+    if method == "fx":
+        return fx_trace(model, input_names, leaf_modules)
+    if method == "dynamo":
+        if dummy_inputs is None:
+            raise ValueError("trace_method='dynamo' needs dummy inputs")
+        return dynamo_trace(model, dummy_inputs)
+    raise ValueError("unknown trace method %r" % method)
+
+
+def make_dummy_inputs(config, input_names: Sequence[str], batch_size: int = 2, seq_length: Optional[int] = None,
+                      device="cpu") -> Dict[str, torch.Tensor]:
+    """Small random inputs keyed by the names a forward() expects."""
+    seq = seq_length or min(int(getattr(config, "max_position_embeddings", 128) or 128), 128)
+    vocab = int(getattr(config, "vocab_size", 1000) or 1000)
+    out = {}
+    for name in input_names:
+        if name in ("input_ids", "decoder_input_ids", "labels"):
+            out[name] = torch.randint(0, vocab, (batch_size, seq), device=device)
+        elif name in ("attention_mask", "decoder_attention_mask"):
+            out[name] = torch.ones(batch_size, seq, dtype=torch.long, device=device)
+        elif name == "token_type_ids":
+            out[name] = torch.zeros(batch_size, seq, dtype=torch.long, device=device)
+        elif name == "position_ids":
+            out[name] = torch.arange(seq, device=device)[None].expand(batch_size, seq)
+        elif name == "pixel_values":
+            ch = int(getattr(config, "num_channels", 3))
+            size = getattr(config, "image_size", 224)
+            size = size if isinstance(size, (tuple, list)) else (size, size)
+            out[name] = torch.randn(batch_size, ch, *size, device=device)
+        elif name in ("input_features", "input_values"):
+            out[name] = torch.randn(batch_size, int(getattr(config, "num_mel_bins", 80)), 3000, device=device)
+        else:
+            out[name] = torch.randn(batch_size, seq, int(getattr(config, "hidden_size", 64)), device=device)
+    return out

@@ -21,7 +21,7 @@ from ..ops.attention import flash_attention, flash_attention_packed
 from ..ops.cross_entropy import softmax_cross_entropy
 from ..ops.elementwise import dropout, embedding_sum
 from ..ops.linear import linear as k_linear, mlp as k_mlp
-from ..ops.modules import LayerNorm, Linear
+from ..ops.modules import Dropout, Embedding, LayerNorm, Linear
 
 
 @dataclass
@@ -122,36 +122,19 @@ class GPT2Block(nn.Module):
         return self.mlp(self.ln_2(a), a)
 
 
-class GPT2Embeddings(nn.Module):
-    """wte + wpe + dropout as one module so the tracer sees a single node producing the stream."""
-
-    def __init__(self, wte, wpe, p):
-        super().__init__()
-        self.wte, self.wpe, self.p = wte, wpe, p
-
-    def forward(self, input_ids):
-        pos = torch.arange(input_ids.shape[1], device=input_ids.device).unsqueeze(0)
-        h = embedding_sum([input_ids, pos.expand_as(input_ids)], [self.wte.weight, self.wpe.weight])
-        return dropout(h, self.p, self.training)
-
-
 class GPT2Model(nn.Module):
     def __init__(self, config: GPT2Config):
         super().__init__()
         self.config = config
-        self.wte = nn.Embedding(config.vocab_size, config.n_embd)
-        self.wpe = nn.Embedding(config.n_positions, config.n_embd)
-        self.embd_pdrop = config.embd_pdrop
+        self.wte = Embedding(config.vocab_size, config.n_embd)
+        self.wpe = Embedding(config.n_positions, config.n_embd)
+        self.drop = Dropout(config.embd_pdrop)
         self.h = nn.ModuleList([GPT2Block(config) for _ in range(config.n_layer)])
         self.ln_f = LayerNorm(config.n_embd, eps=config.layer_norm_epsilon)
 
-    def embed(self, input_ids):
-        pos = torch.arange(input_ids.shape[1], device=input_ids.device).unsqueeze(0).expand_as(input_ids)
-        h = embedding_sum([input_ids, pos], [self.wte.weight, self.wpe.weight])
-        return dropout(h, self.embd_pdrop, self.training)
-
     def forward(self, input_ids):
-        h = self.embed(input_ids)
+        pos = torch.arange(input_ids.size(1), device=input_ids.device).unsqueeze(0)
+        h = self.drop(self.wte(input_ids) + self.wpe(pos))
         for blk in self.h:
             h = blk(h)
         return self.ln_f(h)

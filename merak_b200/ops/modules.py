@@ -50,6 +50,14 @@ class Embedding(nn.Embedding):
         return embedding_sum([ids], [self.weight])
 
 
+class Dropout(nn.Dropout):
+    """Dropout whose mask comes from the framework's counter-based generator on CUDA."""
+
+    def forward(self, x):
+        from .elementwise import dropout
+        return dropout(x, self.p, self.training)
+
+
 def inject_kernels(module: nn.Module) -> nn.Module:
     """Re-classes ``nn.Linear`` / ``nn.LayerNorm`` / ``nn.Embedding`` instances (exact types only)
     to the kernel-backed subclasses above.  Parameters are untouched, so state dicts, optimizers
@@ -61,6 +69,8 @@ def inject_kernels(module: nn.Module) -> nn.Module:
             m.__class__ = LayerNorm
         elif type(m) is nn.Embedding:
             m.__class__ = Embedding
+        elif type(m) is nn.Dropout:
+            m.__class__ = Dropout
     return module
 
 
