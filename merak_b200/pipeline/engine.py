@@ -1,0 +1,676 @@
+"""``PipelineEngine``: executes a pipeline schedule instruction by instruction for one stage.
+
+Responsibilities (Merak/core/merak_engine.py:1047-1487 and its Communication / NetCalculation
+helper engines): micro-batch loading, stage forward / backward (incl. early recompute), activation
+and gradient p2p with a one-time metadata handshake, tied-weight and data-parallel gradient
+reduction, optimizer step with clipping / loss scaling, loss aggregation over dp and pp.
+
+B200-specific choices:
+* parameters live in one flat buffer with an fp32 gradient buffer the wgrad GEMMs accumulate into
+  (``ops.optim.FlatBuffers``); DP reduction and the fused AdamW work on those flat buffers, ZeRO-1
+  is "each dp rank owns a contiguous slice of them";
+* p2p transfers run on a side stream ordered by events (no device-wide synchronisation);
+* nothing in the step reads a device value on the host except the loss that is logged.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops.optim import FlatBuffers, FusedAdamW
+from ..ops.rng import dropout_state
+from ..parallel import mpu, p2p
+from ..printer import SynchronizedWallClockTimer, log_dist, see_memory_usage, set_timer_log_rank
+from ..recompute import RNGManager, checkpoint, pre_checkpoint, run_pending_recomputes
+from . import schedules as S
+from .module import PipelineModule
+
+
+class DynamicLossScaler:
+    """fp16 loss scaling with hysteresis (Merak/core/zero/utils.py:232-384)."""
+
+    def __init__(self, init_scale=2.0 ** 16, scale_factor=2.0, scale_window=1000, min_scale=1.0, hysteresis=2,
+                 static: bool = False):
+        self.cur_scale = float(init_scale)
+        self.scale_factor, self.scale_window, self.min_scale = scale_factor, scale_window, min_scale
+        self.delayed_shift, self.cur_hysteresis = hysteresis, hysteresis
+        self.last_overflow_iter, self.cur_iter = -1, 0
+        self.static = static
+
+    def update_scale(self, overflow: bool):
+        if self.static:
+            return
+        if overflow:
+            if self.delayed_shift == 1 or self.cur_hysteresis == 1:
+                self.cur_scale = max(self.cur_scale / self.scale_factor, self.min_scale)
+            else:
+                self.cur_hysteresis -= 1
+            self.last_overflow_iter = self.cur_iter
+        else:
+            if (self.cur_iter - self.last_overflow_iter) % self.scale_window == 0:
+                self.cur_hysteresis = self.delayed_shift
+                self.cur_scale *= self.scale_factor
+        self.cur_iter += 1
+
+    def state_dict(self):
+        return dict(self.__dict__)
+
+    def load_state_dict(self, sd):
+        self.__dict__.update(sd)
+
+
+def _as_dict(batch, names: Sequence[str]) -> Dict[str, torch.Tensor]:
+    if isinstance(batch, dict):
+        return dict(batch)
+    if isinstance(batch, torch.Tensor):
+        batch = (batch,)
+    return {n: t for n, t in zip(names, batch)}
+
+
+class PipelineEngine:
+
+    def __init__(self, model: PipelineModule, args, optimizer=None, lr_scheduler=None, loss_fn: Optional[Callable] = None,
+                 tuning_params=None, optimizer_factory: Optional[Callable] = None,
+                 lr_scheduler_factory: Optional[Callable] = None):
+        self.module = model
+        self.args = args
+        self.loss_fn = loss_fn or model.loss_fn
+        self.device = args.device
+        self.stage_id = mpu.get_pipe_parallel_rank()
+        self.num_stages = mpu.get_pipe_parallel_world_size()
+        self.is_first = self.stage_id == 0
+        self.is_last = self.stage_id == self.num_stages - 1
+        self.dp_size = mpu.get_data_parallel_world_size()
+        self.dp_rank = mpu.get_data_parallel_rank()
+        self.micro_batches = args.gradient_accumulation_steps
+        self.micro_batch_size = args.per_device_train_batch_size
+        self.global_steps = 0
+        self.timers = SynchronizedWallClockTimer()
+        self.rng_manager = RNGManager()
+        self.wall_clock_breakdown = bool(args.wall_clock_breakdown)
+        grid = mpu.get_grid()
+        if grid is not None:
+            topo = grid.topology
+            set_timer_log_rank([topo.get_rank(pipe=s, data=0, sequence=0, model=0) for s in range(self.num_stages)])
+
+        # names of everything a micro-batch carries, in tuple order
+        self.input_names = list(args.input_names or sorted(model.input_to_shard, key=lambda n: model.input_to_shard[n]))
+        self.batch_names = self.input_names + ["labels"]
+        self.stage_inputs = model.input_to_stage_dic.get(self.stage_id, [])
+
+        model.configure_distributed_model(self.device)
+        model.tie_modules()
+        self._configure_precision()
+        self._configure_optimizer(optimizer, lr_scheduler, optimizer_factory, lr_scheduler_factory, tuning_params)
+
+        if args.train_schedule == "last_no_recompute_1f1b" and self.is_last:
+            model._force_no_recompute = True
+            model.act_ckpt_interval = 0
+        if args.train_schedule == "full_critical_path_1f1b":
+            if self.is_last:
+                model._force_no_recompute = True
+                model.act_ckpt_interval = 0
+
+        self._meta_sent = {"act": False, "grad": False}
+        self._recv_act_meta = None
+        self._recv_grad_meta = None
+        self._reset_buffers(2)
+        self.total_loss = None
+        self.agg_loss = None
+        self._warned_unused = False
+        n_params = sum(p.numel() for p in model.parameters())
+        log_dist("stage %d/%d: %d shards [%d,%d), %.2fM parameters" % (
+            self.stage_id, self.num_stages, len(model.local_layers), model.local_start, model.local_stop,
+            n_params / 1e6), ranks=[-1] if self.dp_rank == 0 and mpu.get_model_parallel_rank() == 0 else [])
+
+    # ------------------------------------------------------------------------------------------
+    # set-up
+    # ------------------------------------------------------------------------------------------
+    def _configure_precision(self):
+        a = self.args
+        self.loss_scaler = None
+        if a.fp16:
+            if a.loss_scale and a.loss_scale > 0:
+                self.loss_scaler = DynamicLossScaler(init_scale=a.loss_scale, static=True)
+            else:
+                self.loss_scaler = DynamicLossScaler(init_scale=2.0 ** min(a.initial_scale_power, 24),
+                                                     scale_window=a.loss_scale_window, min_scale=a.min_loss_scale,
+                                                     hysteresis=a.hysteresis)
+
+    def _unique_params(self) -> List[nn.Parameter]:
+        seen, out = set(), []
+        for p in self.module.parameters():
+            if id(p) not in seen and p.requires_grad:
+                seen.add(id(p))
+                out.append(p)
+        return out
+
+    def _configure_optimizer(self, optimizer, lr_scheduler, optimizer_factory, lr_scheduler_factory, tuning_params):
+        a = self.args
+        params = tuning_params if tuning_params is not None else self._unique_params()
+        self.flat: Optional[FlatBuffers] = None
+        self.zero = a.zero_stage == 1 and self.dp_size > 1
+        if optimizer is None and optimizer_factory is None:
+            # framework optimizer: flat buffers + fused AdamW (+ ZeRO-1 shard)
+            no_decay = set()
+            for m in self.module.modules():
+                if isinstance(m, nn.LayerNorm) or type(m).__name__.endswith("Norm"):
+                    no_decay.update(id(p) for p in m.parameters(recurse=False))
+            for p in params:
+                p._no_weight_decay = id(p) in no_decay or p.dim() <= 1
+            pad = 64 * self.dp_size
+            self.flat = FlatBuffers(params, grad_dtype=torch.float32, pad_to=pad)
+            shard = None
+            if self.zero:
+                per = self.flat.numel // self.dp_size
+                shard = (self.dp_rank * per, (self.dp_rank + 1) * per)
+            self.optimizer = FusedAdamW(self.flat, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
+                                        eps=a.adam_epsilon, weight_decay=a.weight_decay, shard=shard,
+                                        max_grad_norm=a.max_grad_norm)
+        else:
+            self.optimizer = optimizer if optimizer is not None else optimizer_factory(params)
+            self.zero = False
+        self.lr_scheduler = lr_scheduler
+        if self.lr_scheduler is None and lr_scheduler_factory is not None:
+            self.lr_scheduler = lr_scheduler_factory(self.optimizer)
+
+    # ------------------------------------------------------------------------------------------
+    # buffers
+    # ------------------------------------------------------------------------------------------
+    def _reset_buffers(self, n: int):
+        self.num_buffers = n
+        self.buf_inputs: List[Optional[Tuple[torch.Tensor, ...]]] = [None] * n      # carried from prev stage
+        self.buf_externals: List[Dict[str, torch.Tensor]] = [dict() for _ in range(n)]
+        self.buf_labels: List[Optional[torch.Tensor]] = [None] * n
+        self.buf_outputs: List[Optional[Tuple[torch.Tensor, ...]]] = [None] * n
+        self.buf_out_grads: List[Optional[List[torch.Tensor]]] = [None] * n
+        self.buf_in_grads: List[Optional[List[torch.Tensor]]] = [None] * n
+        self.buf_loss: List[Optional[torch.Tensor]] = [None] * n
+
+    # ------------------------------------------------------------------------------------------
+    # public API
+    # ------------------------------------------------------------------------------------------
+    def train(self):
+        self.module.train()
+        return self
+
+    def eval(self):
+        self.module.eval()
+        return self
+
+    def train_batch(self, data_iter: Iterator):
+        """One optimizer step over ``gradient_accumulation_steps`` micro-batches.  Returns the loss
+        averaged over micro-batches and data-parallel ranks (a device tensor on every rank)."""
+        self.module.train()
+        self.data_iter = data_iter
+        self.total_loss = None
+        self._grads_reduced = False
+        sched = S.make_schedule(self.args.train_schedule, self.micro_batches, self.num_stages, self.stage_id)
+        if sched.num_pipe_buffers() != self.num_buffers:
+            self._reset_buffers(sched.num_pipe_buffers())
+        if self.wall_clock_breakdown:
+            self.timers("train_batch").start()
+        self._exec_schedule(sched)
+        self.agg_loss = self._aggregate_total_loss()
+        if self.wall_clock_breakdown:
+            self.timers("train_batch").stop()
+        self.global_steps += 1
+        dropout_state().advance_step()
+        if self.args.logging_steps and self.global_steps % self.args.logging_steps == 0:
+            self._log_step()
+        return self.agg_loss
+
+    def eval_batch(self, data_iter: Iterator, compute_loss: bool = True, reduce_output: Optional[str] = "avg",
+                   num_micro_batches: Optional[int] = None, batch_fn: Optional[Callable] = None):
+        """Forward-only pass over ``num_micro_batches`` micro-batches.  Returns the averaged loss, or
+        the list of last-stage outputs when ``compute_loss=False`` / ``return_logits`` is set."""
+        self.module.eval()
+        self.data_iter = data_iter if batch_fn is None else (batch_fn(b) for b in data_iter)
+        n = num_micro_batches or self.micro_batches
+        self.total_loss = None
+        self._eval_outputs: List[torch.Tensor] = []
+        self._compute_loss = compute_loss
+        sched = S.InferenceSchedule(n, self.num_stages, self.stage_id)
+        if sched.num_pipe_buffers() != self.num_buffers:
+            self._reset_buffers(sched.num_pipe_buffers())
+        # receive shapes may differ from training (e.g. generation): redo the handshake
+        saved = (self._meta_sent, self._recv_act_meta)
+        self._meta_sent, self._recv_act_meta = {"act": False, "grad": False}, None
+        mb_saved = self.micro_batches
+        self.micro_batches = n
+        with torch.no_grad():
+            self._exec_schedule(sched, training=False)
+        self.micro_batches = mb_saved
+        self._meta_sent, self._recv_act_meta = saved
+        self._compute_loss = True
+        if not compute_loss or self.args.return_logits:
+            return self._eval_outputs
+        if reduce_output is None:
+            return self.total_loss
+        return self._aggregate_total_loss(n)
+
+    # ------------------------------------------------------------------------------------------
+    # schedule execution
+    # ------------------------------------------------------------------------------------------
+    def _exec_schedule(self, sched, training: bool = True):
+        self._training_pass = training
+        table = {
+            S.LoadMicroBatch: self._exec_load_micro_batch, S.ForwardPass: self._exec_forward_pass,
+            S.BackwardPass: self._exec_backward_pass, S.SendActivation: self._exec_send_activations,
+            S.RecvActivation: self._exec_recv_activations, S.SendGrad: self._exec_send_grads,
+            S.RecvGrad: self._exec_recv_grads, S.SendActivationRecvGrad: self._exec_send_activations_recv_grads,
+            S.SendGradRecvActivation: self._exec_send_grads_recv_activations,
+            S.PreCheckpointForwardPass: self._exec_precheckpoint_forward_pass,
+            S.RecomputeRecvGrad: self._exec_recompute_recv_grads,
+            S.RestoreRecomputeStatus: self._exec_restore_recompute_status,
+            S.ReduceTiedGrads: self._exec_reduce_tied_grads, S.ReduceGrads: self._exec_reduce_grads,
+            S.OptimizerStep: self._exec_optimizer_step,
+        }
+        for step_cmds in sched.steps():
+            for cmd in step_cmds:
+                fn = table[type(cmd)]
+                if "buffer_id" in cmd.kwargs:
+                    fn(cmd.buffer_id)
+                else:
+                    fn()
+
+    # -- data ------------------------------------------------------------------------------------
+    def _exec_load_micro_batch(self, buf: int):
+        if self.wall_clock_breakdown:
+            self.timers("batch_input").start()
+        batch = _as_dict(next(self.data_iter), self.batch_names)
+        moved = {}
+        for k, v in batch.items():
+            if isinstance(v, torch.Tensor):
+                moved[k] = v.to(self.device, non_blocking=True)
+        self.buf_externals[buf] = {k: moved[k] for k in self.stage_inputs if k in moved}
+        if self.is_last:
+            labels = {k: v for k, v in moved.items() if k not in self.input_names}
+            self.buf_labels[buf] = labels.get("labels", next(iter(labels.values())) if labels else None)
+            if len(labels) > 1:
+                self.buf_labels[buf] = labels
+        if self.wall_clock_breakdown:
+            self.timers("batch_input").stop()
+
+    def _load_middle_stage_inputs(self, buf: int):
+        """Stages that are neither first nor last but read a model input themselves."""
+        if self.stage_inputs and not self.is_first and not self.is_last:
+            batch = _as_dict(next(self.data_iter), self.batch_names)
+            self.buf_externals[buf] = {k: batch[k].to(self.device, non_blocking=True) for k in self.stage_inputs
+                                       if k in batch}
+
+    # -- compute ---------------------------------------------------------------------------------
+    def _exec_forward_pass(self, buf: int):
+        if self.wall_clock_breakdown:
+            self.timers("forward").start()
+        carried = self.buf_inputs[buf] if not self.is_first else ()
+        carried = tuple(carried or ())
+        self.module.current_buffer = buf
+        out = self.module(carried, self.buf_externals[buf])
+        if self.is_last:
+            if not getattr(self, "_compute_loss", True) or (not self._training_pass and self.args.return_logits):
+                self._eval_outputs.append(out.detach() if isinstance(out, torch.Tensor) else out)
+                if not getattr(self, "_compute_loss", True):
+                    if self.wall_clock_breakdown:
+                        self.timers("forward").stop()
+                    return
+            loss = self.loss_fn(out, self.buf_labels[buf]) if self.loss_fn is not None else out
+            if isinstance(loss, (tuple, list)):
+                loss = loss[0]
+            self.buf_loss[buf] = loss
+            det = loss.detach().float()
+            self.total_loss = det if self.total_loss is None else self.total_loss + det
+        else:
+            self.buf_outputs[buf] = out if isinstance(out, tuple) else (out,)
+        if self.wall_clock_breakdown:
+            self.timers("forward").stop()
+
+    def _exec_precheckpoint_forward_pass(self, buf: int):
+        """Forward under ``pre_checkpoint``: every recompute segment registers a record that
+        ``RecomputeRecvGrad`` can replay before the backward pass."""
+        self.module.pending_records[buf] = []
+        self.module.set_recompute(func=pre_checkpoint, interval=max(1, self.module.act_ckpt_interval or 1))
+        self.rng_manager.store_fwd_rng_state(buf, self.device.type)
+        self._exec_forward_pass(buf)
+
+    def _exec_restore_recompute_status(self):
+        self.module.restore_recompute()
+
+    def _exec_recompute_recv_grads(self, buf: int):
+        """Post the receive of the output gradient, replay the forward of the pre-checkpointed
+        segments of this buffer while it is in flight, then wait."""
+        work = self._post_recv_grads(buf)
+        if self.wall_clock_breakdown:
+            self.timers("recompute").start()
+        recs = self.module.pending_records.pop(buf, [])
+        if recs:
+            run_pending_recomputes(recs)
+        if self.wall_clock_breakdown:
+            self.timers("recompute").stop()
+        if work is not None:
+            work.wait()
+
+    def _exec_backward_pass(self, buf: int):
+        if self.wall_clock_breakdown:
+            self.timers("backward").start()
+        if self.is_last:
+            loss = self.buf_loss[buf]
+            scale = 1.0 / self.micro_batches
+            if self.loss_scaler is not None:
+                scale *= self.loss_scaler.cur_scale
+            (loss * scale).backward()
+            self.buf_loss[buf] = None
+        else:
+            outs = self.buf_outputs[buf]
+            grads = self.buf_out_grads[buf]
+            pairs = [(o, g) for o, g in zip(outs, grads or []) if isinstance(o, torch.Tensor) and o.requires_grad]
+            if pairs:
+                torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+            self.buf_outputs[buf] = None
+            self.buf_out_grads[buf] = None
+        if not self.is_first:
+            ins = self.buf_inputs[buf] or ()
+            self.buf_in_grads[buf] = [t.grad if (isinstance(t, torch.Tensor) and t.grad is not None) else
+                                      (torch.zeros_like(t) if t.is_floating_point() else None) for t in ins]
+            self.buf_inputs[buf] = None
+        self._collect_main_grads()
+        self.module.pending_records.pop(buf, None)
+        if self.wall_clock_breakdown:
+            self.timers("backward").stop()
+
+    def _collect_main_grads(self):
+        """Gradients autograd produced as ``p.grad`` (PyTorch-path ops) move into the flat buffer."""
+        if self.flat is None:
+            return
+        for p in self.flat.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = None
+
+    # -- p2p ---------------------------------------------------------------------------------------
+    def _alloc_from_meta(self, meta, requires_grad_ok: bool):
+        bufs = []
+        for dtype, rg, shape in meta:
+            t = torch.empty(shape, dtype=dtype, device=self.device)
+            if requires_grad_ok and rg and t.is_floating_point():
+                t.requires_grad_(True)
+            bufs.append(t)
+        return bufs
+
+    def _exec_send_activations(self, buf: int):
+        if self.is_last:
+            return
+        outs = [o.detach() if isinstance(o, torch.Tensor) else o for o in self.buf_outputs[buf]]
+        self._ensure_act_meta_sent(outs)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_output").start()
+        p2p.send_forward(outs)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_output").stop()
+
+    def _ensure_act_meta_sent(self, outs):
+        if not self._meta_sent["act"]:
+            p2p.send_meta(outs, mpu.get_pipeline_model_parallel_next_rank(), self.device)
+            self._meta_sent["act"] = True
+
+    def _ensure_act_meta_recv(self):
+        if self._recv_act_meta is None:
+            self._recv_act_meta = p2p.recv_meta(mpu.get_pipeline_model_parallel_prev_rank(), self.device)
+
+    def _exec_recv_activations(self, buf: int):
+        if self.is_first:
+            return
+        self._load_middle_stage_inputs(buf)
+        self._ensure_act_meta_recv()
+        bufs = self._alloc_from_meta(self._recv_act_meta, self._training_pass)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_recv_input").start()
+        p2p.recv_forward(bufs)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_recv_input").stop()
+        self.buf_inputs[buf] = tuple(bufs)
+
+    def _grad_meta(self, buf: int):
+        return [(o.dtype, False, tuple(o.shape)) for o in self.buf_outputs[buf] if isinstance(o, torch.Tensor)]
+
+    def _exec_send_grads(self, buf: int):
+        if self.is_first:
+            return
+        grads = [g for g in (self.buf_in_grads[buf] or []) if g is not None]
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_grad").start()
+        p2p.send_backward(grads)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_grad").stop()
+        self.buf_in_grads[buf] = None
+
+    def _post_recv_grads(self, buf: int):
+        if self.is_last:
+            return None
+        outs = self.buf_outputs[buf]
+        bufs = [torch.empty_like(o) for o in outs if isinstance(o, torch.Tensor) and o.is_floating_point()]
+        work = p2p.recv_backward(bufs, wait=False)
+        it = iter(bufs)
+        self.buf_out_grads[buf] = [next(it) if (isinstance(o, torch.Tensor) and o.is_floating_point()) else None
+                                   for o in outs]
+        return work
+
+    def _exec_recv_grads(self, buf: int):
+        if self.wall_clock_breakdown:
+            self.timers("pipe_recv_grad").start()
+        work = self._post_recv_grads(buf)
+        if work is not None:
+            work.wait()
+        if self.wall_clock_breakdown:
+            self.timers("pipe_recv_grad").stop()
+
+    def _exec_send_activations_recv_grads(self, bufs):
+        send_buf, recv_buf = bufs
+        if self.is_last:
+            return
+        outs = [o.detach() for o in self.buf_outputs[send_buf]]
+        self._ensure_act_meta_sent(outs)
+        routs = self.buf_outputs[recv_buf]
+        gb = [torch.empty_like(o) for o in routs if isinstance(o, torch.Tensor) and o.is_floating_point()]
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_output_recv_grad").start()
+        p2p.send_forward_recv_backward(outs, gb)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_output_recv_grad").stop()
+        it = iter(gb)
+        self.buf_out_grads[recv_buf] = [next(it) if (isinstance(o, torch.Tensor) and o.is_floating_point()) else None
+                                        for o in routs]
+
+    def _exec_send_grads_recv_activations(self, bufs):
+        send_buf, recv_buf = bufs
+        if self.is_first:
+            return
+        self._load_middle_stage_inputs(recv_buf)
+        self._ensure_act_meta_recv()
+        grads = [g for g in (self.buf_in_grads[send_buf] or []) if g is not None]
+        rb = self._alloc_from_meta(self._recv_act_meta, self._training_pass)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_grad_recv_input").start()
+        p2p.send_backward_recv_forward(grads, rb)
+        if self.wall_clock_breakdown:
+            self.timers("pipe_send_grad_recv_input").stop()
+        self.buf_in_grads[send_buf] = None
+        self.buf_inputs[recv_buf] = tuple(rb)
+
+    # -- reductions --------------------------------------------------------------------------------
+    def _exec_reduce_tied_grads(self):
+        if self.wall_clock_breakdown:
+            self.timers("backward_tied_allreduce").start()
+        self.module.allreduce_tied_weight_gradients()
+        self._reduce_sequence_parallel_grads()
+        if self.wall_clock_breakdown:
+            self.timers("backward_tied_allreduce").stop()
+
+    def _reduce_sequence_parallel_grads(self):
+        """Norm parameters inside a Megatron sequence-parallel region see only their rank's tokens."""
+        if mpu.get_model_parallel_world_size() == 1:
+            return
+        group = mpu.get_model_parallel_group()
+        for p in self.module.parameters():
+            if getattr(p, "sequence_parallel", False):
+                g = getattr(p, "main_grad", None)
+                g = g if g is not None else p.grad
+                if g is not None:
+                    dist.all_reduce(g, group=group)
+
+    def _exec_reduce_grads(self):
+        if self.wall_clock_breakdown:
+            self.timers("backward_allreduce").start()
+        self.allreduce_gradients()
+        if self.wall_clock_breakdown:
+            self.timers("backward_allreduce").stop()
+
+    def allreduce_gradients(self, bucket_elems: Optional[int] = None):
+        """DP gradient reduction: all-reduce (or, under ZeRO-1, reduce-scatter to the owning rank) of
+        the flat fp32 gradient buffer in buckets; ``1/dp`` is folded into the optimizer's gradient
+        scale instead of a separate pass (Merak/core/merak_engine.py:552-621)."""
+        if self.dp_size == 1 or self._grads_reduced:
+            return
+        group = mpu.get_data_parallel_group()
+        if self.flat is not None:
+            from ..parallel import dp_fused
+            if dp_fused.try_fused_reduce(self, group):
+                self._grads_reduced = True
+                return
+            g = self.flat.grad
+            if self.zero:
+                self._reduce_scatter_inplace(g, g.numel() // self.dp_size, group)
+            else:
+                bucket = int(bucket_elems or self.args.zero_reduce_bucket_size or 5e8)
+                for lo in range(0, g.numel(), bucket):
+                    dist.all_reduce(g[lo:lo + bucket], group=group)
+        else:
+            grads = [p.grad for p in self._unique_params() if p.grad is not None]
+            bucket, size = [], 0
+            limit = int(bucket_elems or 5e8)
+            for gr in grads + [None]:
+                if gr is None or size + gr.numel() > limit:
+                    if bucket:
+                        flat = torch.cat([b.reshape(-1) for b in bucket])
+                        flat.div_(self.dp_size)
+                        dist.all_reduce(flat, group=group)
+                        off = 0
+                        for b in bucket:
+                            b.copy_(flat[off:off + b.numel()].view_as(b))
+                            off += b.numel()
+                    bucket, size = [], 0
+                if gr is not None:
+                    bucket.append(gr)
+                    size += gr.numel()
+        self._grads_reduced = True
+
+    def _reduce_scatter_inplace(self, g: torch.Tensor, per: int, group):
+        out = torch.empty(per, dtype=g.dtype, device=g.device)
+        dist.reduce_scatter_tensor(out, g, group=group)
+        g[self.dp_rank * per:(self.dp_rank + 1) * per].copy_(out)
+
+    # -- optimizer ---------------------------------------------------------------------------------
+    def _global_grad_sumsq(self) -> torch.Tensor:
+        """Squared gradient norm over the whole model: tensor-parallel duplicates counted once, then
+        summed over the tensor- and pipeline-parallel groups (and dp under ZeRO)."""
+        opt = self.optimizer
+        ss = opt.grad_sumsq().clone()
+        tp = mpu.get_model_parallel_world_size()
+        if tp > 1 and mpu.get_model_parallel_rank() != 0:
+            # replicated (non model-parallel) parameters are counted by tp rank 0 only
+            dup = torch.zeros_like(ss)
+            for p in self.flat.params:
+                if not getattr(p, "model_parallel", False):
+                    dup[0] += p.main_grad.float().pow(2).sum()
+            ss[0] = ss[0] - dup[0]
+        # a weight shared between stages (tied embeddings) is counted by its first owner only
+        for spec in self.module.tied_local.values():
+            if self.stage_id != spec["stages"][0] and not self.zero:
+                mg = getattr(spec["param"], "main_grad", None)
+                if mg is not None:
+                    ss[0] = ss[0] - mg.float().pow(2).sum()
+        if self.zero:
+            dist.all_reduce(ss, group=mpu.get_data_parallel_group())
+        if tp > 1:
+            dist.all_reduce(ss, group=mpu.get_model_parallel_group())
+        if self.num_stages > 1:
+            dist.all_reduce(ss, group=mpu.get_pipe_parallel_group())
+        return ss
+
+    def _exec_optimizer_step(self):
+        if self.wall_clock_breakdown:
+            self.timers("step").start()
+        a = self.args
+        grad_scale = 1.0 / self.dp_size if (self.dp_size > 1 and not getattr(self, "_fused_dp_applied_scale", False)) else 1.0
+        if self.loss_scaler is not None:
+            grad_scale /= self.loss_scaler.cur_scale
+        if self.flat is not None:
+            if getattr(self, "_fused_step_done", False):
+                self._fused_step_done = False       # the fused DP kernel already updated the parameters
+            else:
+                distributed_norm = (mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1 or self.zero)
+                sumsq = self._global_grad_sumsq() if distributed_norm else None
+                self.optimizer.step(grad_scale=grad_scale, sumsq=sumsq)
+                if self.zero:
+                    dist.all_gather_into_tensor(self.flat.model, self.flat.model[self.optimizer.start:self.optimizer.end]
+                                                .clone(), group=mpu.get_data_parallel_group())
+            if self.loss_scaler is not None:
+                self.loss_scaler.update_scale(bool(self.optimizer.skipped().item()))
+            self.flat.zero_grad()
+        else:
+            params = self._unique_params()
+            if grad_scale != 1.0 and self.dp_size == 1:
+                for p in params:
+                    if p.grad is not None:
+                        p.grad.mul_(grad_scale)
+            if a.max_grad_norm and a.max_grad_norm > 0:
+                torch.nn.utils.clip_grad_norm_(params, a.max_grad_norm)
+            self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=True)
+        if self.lr_scheduler is not None:
+            self.lr_scheduler.step()
+        if self.wall_clock_breakdown:
+            self.timers("step").stop()
+
+    # -- loss --------------------------------------------------------------------------------------
+    def _aggregate_total_loss(self, n_micro: Optional[int] = None) -> torch.Tensor:
+        n = n_micro or self.micro_batches
+        if self.is_last and self.total_loss is not None:
+            loss = (self.total_loss / n).reshape(1).to(self.device)
+            if self.dp_size > 1:
+                dist.all_reduce(loss, group=mpu.get_data_parallel_group())
+                loss /= self.dp_size
+        else:
+            loss = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.num_stages > 1:
+            src = mpu.get_grid().stage_to_global(self.num_stages - 1)
+            dist.broadcast(loss, src, group=mpu.get_pipe_parallel_group())
+        return loss.squeeze(0)
+
+    def _log_step(self):
+        lr = self.get_lr()
+        elapsed = self.timers("train_batch").elapsed(reset=True) / 1000.0 if self.wall_clock_breakdown else float("nan")
+        steps = self.args.logging_steps
+        iter_time = elapsed / steps if steps else float("nan")
+        tput = self.micro_batch_size * self.micro_batches * self.dp_size / iter_time if iter_time and iter_time > 0 else 0.0
+        log_dist("steps: %d loss: %.4f iter time (s): %.3f total samples/sec: %.3f learning rate: %.3e" % (
+            self.global_steps, float(self.agg_loss), iter_time, tput, lr),
+            ranks=[-1] if (self.is_last and self.dp_rank == 0 and mpu.get_model_parallel_rank() == 0) else [])
+        if self.wall_clock_breakdown:
+            self.timers.log(["batch_input", "forward", "backward", "recompute", "backward_allreduce",
+                             "backward_tied_allreduce", "step", "pipe_send_output", "pipe_send_grad",
+                             "pipe_recv_input", "pipe_recv_grad", "pipe_send_grad_recv_input",
+                             "pipe_send_output_recv_grad"], normalizer=max(1, steps))
+        see_memory_usage("after step %d" % self.global_steps, force=False)
+
+    def get_lr(self) -> float:
+        groups = getattr(self.optimizer, "param_groups", None)
+        return groups[0]["lr"] if groups else float("nan")
+
+    def set_lr(self, lr: float):
+        for g in self.optimizer.param_groups:
+            g["lr"] = lr

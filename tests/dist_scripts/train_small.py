@@ -1,0 +1,115 @@
+"""Trains a small model for a few steps under a given parallel layout and writes the loss curve.
+Launched by the tests through torch.distributed.run (gloo on CPU, nccl on GPUs)."""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+os.environ.setdefault("MERAK_QUIET", "1")
+
+import torch
+
+import merak_b200 as Merak
+from merak_b200.models.bert import BertForMaskedLM, bert_config
+from merak_b200.models.gpt2 import GPT2LMHeadModel, gpt2_config
+from merak_b200.models.llama import LlamaForCausalLM, llama_config
+from merak_b200.utils.datasets import SyntheticTokenDataset
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--dp", type=int, default=1)
+    ap.add_argument("--model", default="gpt2")
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--mbs", type=int, default=2)
+    ap.add_argument("--gas", type=int, default=4)
+    ap.add_argument("--schedule", default="1f1b")
+    ap.add_argument("--recompute", type=int, default=0)
+    ap.add_argument("--ratio", default=None)
+    ap.add_argument("--zero", type=int, default=0)
+    ap.add_argument("--parallel_vocab", type=int, default=0)
+    ap.add_argument("--megatron_sp", type=int, default=0)
+    ap.add_argument("--split", default="nearest_min_deps")
+    ap.add_argument("--dtype", default="fp32")
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--save_dir", default=None)
+    ap.add_argument("--resume", default=None)
+    ap.add_argument("--out", required=True)
+    o = ap.parse_args()
+
+    Merak.init(o.pp, o.tp, o.dp, backend="gloo" if o.device == "cpu" else "nccl")
+    torch.manual_seed(1234)
+    V, L = 512, 32
+    if o.model == "gpt2":
+        model = GPT2LMHeadModel(gpt2_config("gpt2-tiny", vocab_size=V, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0))
+        task = "causal"
+    elif o.model == "bert":
+        model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=0.0))
+        task = "mlm"
+    else:
+        model = LlamaForCausalLM(llama_config("llama-tiny", vocab_size=V))
+        task = "causal"
+    args = Merak.MerakArguments(
+        output_dir=o.save_dir or "/tmp/merak_b200_test", per_device_train_batch_size=o.mbs,
+        gradient_accumulation_steps=o.gas, max_steps=o.steps, logging_steps=0, learning_rate=1e-3 if o.model == "gpt2" else 3e-3,
+        lr_scheduler_type="constant", weight_decay=0.01, wall_clock_breakdown=False, report_to="none",
+        no_cuda=(o.device == "cpu"), train_schedule=o.schedule, activation_checkpointing=bool(o.recompute),
+        activation_checkpoint_ratio=[o.ratio] if o.ratio else None, zero_stage=1 if o.zero else None,
+        parallel_vocab=bool(o.parallel_vocab), megatron_sequence_parallel=bool(o.megatron_sp),
+        split_method=o.split, bf16=(o.dtype == "bf16"), seed=1234, save=bool(o.save_dir), save_steps=o.steps,
+        resume_from_checkpoint=o.resume, comm_mode="nccl")
+    # every data-parallel layout must see the same global batch per step: dataset order is by index
+    ds = SyntheticTokenDataset(V, L, 16, task=task, seed=7)      # two global batches, revisited
+    trainer = FixedOrderTrainer(model, args, train_dataset=ds)
+    losses = []
+    engine = trainer.init_engine()
+    if o.resume:
+        it = trainer.load_checkpoint(o.resume)
+        trainer.params.resume(it)
+    data_iter = trainer._batch_iter(trainer.train_dataloader)
+    for _ in range(o.steps):
+        losses.append(float(engine.train_batch(data_iter)))
+        trainer.params.step()
+    if o.save_dir:
+        trainer.save_checkpoint()
+    if torch.distributed.get_rank() == 0:
+        with open(o.out, "w") as f:
+            json.dump({"losses": losses}, f)
+    torch.distributed.barrier()
+    Merak.initialize.destroy()
+
+
+class _SequentialSampler:
+    """Global micro-batch g of step s goes to dp rank (g % dp): any dp degree consumes the same
+    samples per optimizer step."""
+
+    def __init__(self, n, mbs, gas, dp_rank, dp_size):
+        self.n, self.mbs, self.gas, self.r, self.d = n, mbs, gas, dp_rank, dp_size
+
+    def __len__(self):
+        return 1 << 30
+
+    def __iter__(self):
+        per_step = self.gas * self.d                  # micro-batches per optimizer step, globally
+        step = 0
+        while True:
+            for k in range(self.gas):
+                g = step * per_step + k * self.d + self.r
+                yield [i % self.n for i in range(g * self.mbs, (g + 1) * self.mbs)]
+            step += 1
+
+
+class FixedOrderTrainer(Merak.MerakTrainer):
+    def create_dataloader(self, dataset, batch_size, train=True):
+        from torch.utils.data import DataLoader
+        from merak_b200.parallel import mpu
+        s = _SequentialSampler(len(dataset), batch_size, self.args.gradient_accumulation_steps,
+                               mpu.get_data_parallel_rank(), mpu.get_data_parallel_world_size())
+        return DataLoader(dataset, batch_sampler=s, collate_fn=self.data_collator)
+
+
+if __name__ == "__main__":
+    main()

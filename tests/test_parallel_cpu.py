@@ -1,0 +1,86 @@
+"""End-to-end equivalence on CPU/gloo: every parallel layout reproduces the single-process loss
+curve of the same model, data and optimizer (fp32)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SCRIPT = os.path.join(HERE, "dist_scripts", "train_small.py")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def run_layout(tmp_path, name, world, extra, timeout=600):
+    out = os.path.join(str(tmp_path), name + ".json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), SCRIPT, "--out", out] + extra
+    env = dict(os.environ, OMP_NUM_THREADS="1", MERAK_QUIET="1")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert res.returncode == 0, "layout %s failed:\n%s\n%s" % (name, res.stdout[-3000:], res.stderr[-3000:])
+    with open(out) as f:
+        return json.load(f)["losses"]
+
+
+def assert_close(a, b, tol=2e-4):
+    assert len(a) == len(b)
+    for x, y in zip(a, b):
+        assert abs(x - y) < tol * max(1.0, abs(y)), (a, b)
+
+
+@pytest.fixture(scope="module")
+def baseline(tmp_path_factory):
+    d = tmp_path_factory.mktemp("base")
+    return {m: run_layout(d, "single_" + m, 1, ["--model", m]) for m in ("gpt2", "bert", "llama")}
+
+
+def test_loss_decreases(baseline):
+    for m, l in baseline.items():
+        assert l[-1] < l[0], (m, l)
+
+
+@pytest.mark.parametrize("schedule", ["1f1b", "ds_default", "pre_recompute_1f1b", "last_no_recompute_1f1b",
+                                      "full_critical_path_1f1b"])
+def test_pp2_matches_single(tmp_path, baseline, schedule):
+    extra = ["--pp", "2", "--schedule", schedule]
+    if schedule != "1f1b" and schedule != "ds_default":
+        extra += ["--recompute", "1"]
+    if schedule == "full_critical_path_1f1b":
+        extra += ["--ratio", "0.5"]
+    assert_close(run_layout(tmp_path, "pp2_" + schedule, 2, extra), baseline["gpt2"])
+
+
+def test_dp2_matches_single(tmp_path, baseline):
+    assert_close(run_layout(tmp_path, "dp2", 2, ["--dp", "2", "--gas", "2"]), baseline["gpt2"])
+
+
+def test_dp2_zero1_matches_single(tmp_path, baseline):
+    assert_close(run_layout(tmp_path, "dp2z", 2, ["--dp", "2", "--gas", "2", "--zero", "1"]), baseline["gpt2"])
+
+
+@pytest.mark.parametrize("model", ["gpt2", "bert", "llama"])
+def test_tp2_matches_single(tmp_path, baseline, model):
+    assert_close(run_layout(tmp_path, "tp2_" + model, 2, ["--tp", "2", "--model", model]), baseline[model])
+
+
+def test_tp2_vocab_parallel_and_sequence_parallel(tmp_path, baseline):
+    got = run_layout(tmp_path, "tp2_vp_sp", 2, ["--tp", "2", "--model", "llama", "--parallel_vocab", "1",
+                                                 "--megatron_sp", "1"])
+    assert_close(got, baseline["llama"])
+
+
+def test_pp2_tp2_recompute_4ranks(tmp_path, baseline):
+    got = run_layout(tmp_path, "pp2tp2", 4, ["--pp", "2", "--tp", "2", "--recompute", "1"])
+    assert_close(got, baseline["gpt2"])
+
+
+def test_pp2_dp2_layer_split_4ranks(tmp_path, baseline):
+    got = run_layout(tmp_path, "pp2dp2", 4, ["--pp", "2", "--dp", "2", "--gas", "2", "--split", "layer_split"])
+    assert_close(got, baseline["gpt2"])
