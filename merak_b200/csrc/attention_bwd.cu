@@ -423,7 +423,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   }
   dim3 grid((p.Lk + 127) / 128, p.Hkv, p.B);
   attn_bwd_kernel<D><<<grid, kBwdThreads, L::kTotal, stream>>>(tq, tk, tv, tdo, p);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -459,7 +459,7 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
       attn_bwd_prep_kernel<128><<<(unsigned)blocks, warps_per_block * 32, 0, s>>>(
           (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, dq_acc, B, H, Lq, so[0], so[1], so[2], sdo[0],
           sdo[1], sdo[2]);
-    MRK_CUDA_OK(cudaGetLastError());
+    MRK_CHECK_LAUNCH();
   }
   AttnBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
@@ -478,7 +478,7 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
     const int threads = 256;
     attn_bwd_dq_cast_kernel<<<(unsigned)((total_vec + threads - 1) / threads), threads, 0, s>>>(
         dq_acc, (__nv_bfloat16*)dq, H, Lq, D, total_vec, sdq[0], sdq[1], sdq[2]);
-    MRK_CUDA_OK(cudaGetLastError());
+    MRK_CHECK_LAUNCH();
   }
   return 0;
 }

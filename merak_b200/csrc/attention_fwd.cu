@@ -332,7 +332,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   }
   dim3 grid((p.Lq + kQ - 1) / kQ, p.H, p.B);
   attn_fwd_kernel<D><<<grid, kAttnThreads, L::kTotal, stream>>>(tq, tk, tv, p);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 

@@ -504,7 +504,7 @@ MRK_API int mrk_ce_stats(const void* logits, const long long* labels, float* sta
   cudaStream_t s = (cudaStream_t)stream;
   if (logits_f32) ce_stats_kernel<true><<<(unsigned)M, kCeThreads, 0, s>>>(logits, labels, stats, M, V, ld, vocab_start, ignore_index);
   else ce_stats_kernel<false><<<(unsigned)M, kCeThreads, 0, s>>>(logits, labels, stats, M, V, ld, vocab_start, ignore_index);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -514,7 +514,7 @@ MRK_API int mrk_ce_finalize(const float* stats, int tp_parts, long long part_str
   cudaStream_t s = (cudaStream_t)stream;
   ce_finalize_kernel<<<(unsigned)((M + 255) / 256), 256, 0, s>>>(stats, tp_parts, part_stride, labels, lse, loss_rows,
                                                                   loss_sum, valid_count, M, ignore_index);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -525,7 +525,7 @@ MRK_API int mrk_ce_grad(const void* logits, const long long* labels, const float
   cudaStream_t s = (cudaStream_t)stream;
   if (logits_f32) ce_grad_kernel<true><<<(unsigned)M, kCeThreads, 0, s>>>(logits, labels, lse, grad_scale, dlogits, M, V, ld, ldd, vocab_start, ignore_index);
   else ce_grad_kernel<false><<<(unsigned)M, kCeThreads, 0, s>>>(logits, labels, lse, grad_scale, dlogits, M, V, ld, ldd, vocab_start, ignore_index);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -541,7 +541,7 @@ MRK_API int mrk_adamw(float* master, float* m, float* v, const void* grad, void*
   else if (grad_f32) adamw_kernel<true, false><<<grid, 256, 0, s>>>(master, m, v, grad, model_out, hp, grad_scale, skip, n);
   else if (out_f32) adamw_kernel<false, true><<<grid, 256, 0, s>>>(master, m, v, grad, model_out, hp, grad_scale, skip, n);
   else adamw_kernel<false, false><<<grid, 256, 0, s>>>(master, m, v, grad, model_out, hp, grad_scale, skip, n);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -551,14 +551,14 @@ MRK_API int mrk_sumsq(const void* x, long long n, float* out2, int is_f32, void*
   const unsigned grid = grid_for(n / 8 + 1, 256, 4);
   if (is_f32) sumsq_kernel<true><<<grid, 256, 0, s>>>(x, n, out2);
   else sumsq_kernel<false><<<grid, 256, 0, s>>>(x, n, out2);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
 MRK_API int mrk_clip_coef(const float* sumsq2, float base_scale, float max_norm, float* scale_out, int* skip_out,
                           float* norm_out, void* stream) {
   clip_coef_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(sumsq2, base_scale, max_norm, scale_out, skip_out, norm_out);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -575,7 +575,7 @@ MRK_API int mrk_embedding_fwd(const void* const* tables, const long long* const*
   }
   const long long cap = (long long)sm_count() * 16;
   embedding_fwd_kernel<<<(unsigned)(T < cap ? T : cap), 128, 0, (cudaStream_t)stream>>>(t, (__nv_bfloat16*)out, T, H);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -586,7 +586,7 @@ MRK_API int mrk_embedding_bwd(const void* dout, const long long* idx, void* dtab
   const unsigned grid = (unsigned)(T < cap ? T : cap);
   if (grad_f32) embedding_bwd_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dout, idx, dtable, T, H, rows, start);
   else embedding_bwd_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dout, idx, dtable, T, H, rows, start);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -597,21 +597,21 @@ MRK_API int mrk_rope(const void* x, void* y, const float* cosb, const float* sin
   const long long total = B * L * H * (long long)(D / 4);
   rope_kernel<<<grid_for(total, 256, 8), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (__nv_bfloat16*)y, cosb, sinb, pos, B, L, H, D, sb, ss, sh, ysb, yss, ysh, inverse);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
 MRK_API int mrk_swiglu_fwd(const void* gu, void* out, long long M, int F, long long ld, void* stream) {
   MRK_REQUIRE(F % 8 == 0 && ld % 8 == 0, "swiglu: sizes must be multiples of 8");
   swiglu_fwd_kernel<<<grid_for(M * (F / 8), 256, 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, M, F, ld);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
 MRK_API int mrk_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long M, int F, long long ld, void* stream) {
   MRK_REQUIRE(F % 8 == 0 && ld % 8 == 0, "swiglu: sizes must be multiples of 8");
   swiglu_bwd_kernel<<<grid_for(M * (F / 8), 256, 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dgu, M, F, ld);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -625,14 +625,14 @@ MRK_API int mrk_colsum(const void* x, float* out, long long M, int N, long long 
   row_blocks = (int)((M + rpb - 1) / rpb);
   dim3 grid(col_blocks, row_blocks);
   colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, out, M, N, ld, (int)rpb);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
 MRK_API int mrk_dropout(const void* x, void* y, long long n, float p, const void* rng, unsigned long long call_id, void* stream) {
   MRK_REQUIRE(n % 8 == 0, "dropout: element count must be a multiple of 8");
   dropout_kernel<<<grid_for(n / 8, 256, 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, p, (const unsigned long long*)rng, call_id);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -644,6 +644,6 @@ MRK_API int mrk_scaled_cast(const void* x, void* y, long long n, const float* sc
   else if (in_f32) scaled_cast_kernel<true, false><<<grid, 256, 0, s>>>(x, y, n, scale_ptr, scale, accumulate);
   else if (out_f32) scaled_cast_kernel<false, true><<<grid, 256, 0, s>>>(x, y, n, scale_ptr, scale, accumulate);
   else scaled_cast_kernel<false, false><<<grid, 256, 0, s>>>(x, y, n, scale_ptr, scale, accumulate);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }

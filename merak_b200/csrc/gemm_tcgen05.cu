@@ -429,7 +429,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
   const int units = tiles * p.num_splits;
   const int grid = units < sm_count() ? units : sm_count();
   gemm_bf16_kernel<BN><<<grid, kNumThreads, L::kTotal, stream>>>(ta, tb, p);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 

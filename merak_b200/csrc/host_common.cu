@@ -7,6 +7,9 @@
 namespace mrk {
 
 static thread_local char g_last_error[512] = {0};
+static unsigned long long g_launches = 0;
+
+void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -174,3 +177,6 @@ MRK_API unsigned mrk_status_read(int clear) {
 }
 
 MRK_API int mrk_abi_version() { return 1; }
+
+// Number of kernels this library has launched in this process (all devices, all threads).
+MRK_API unsigned long long mrk_launch_count() { return mrk::g_launches; }

@@ -21,6 +21,13 @@ int fail(int code, const char* fmt, ...);
                          cudaGetErrorString(_e), __FILE__, __LINE__);                    \
   } while (0)
 
+// After every kernel launch: count it (mrk_launch_count) and surface launch errors.
+#define MRK_CHECK_LAUNCH()                                                               \
+  do {                                                                                   \
+    ::mrk::count_launch();                                                               \
+    MRK_CUDA_OK(cudaGetLastError());                                                     \
+  } while (0)
+
 #define MRK_REQUIRE(cond, ...)                                                           \
   do {                                                                                   \
     if (!(cond)) return ::mrk::fail(2, __VA_ARGS__);                                     \
@@ -46,5 +53,7 @@ int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, const uint6
                  const uint64_t strides_elems[3], const uint32_t box[4], int swizzle);
 
 int sm_count();
+
+void count_launch();
 
 }  // namespace mrk

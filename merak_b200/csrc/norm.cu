@@ -305,7 +305,7 @@ MRK_API int mrk_norm_fwd(const void* x, const void* residual, const void* gamma,
   else if (H <= 2048) launch_norm_fwd<128, 2>(p, grid, s);
   else if (H <= 4096) launch_norm_fwd<256, 2>(p, grid, s);
   else launch_norm_fwd<256, 4>(p, grid, s);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }
 
@@ -328,9 +328,9 @@ MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, co
   else if (H <= 2048) launch_norm_bwd<128, 2>(p, grid, s);
   else if (H <= 4096) launch_norm_bwd<256, 2>(p, grid, s);
   else launch_norm_bwd<256, 4>(p, grid, s);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   dim3 rgrid((H + 31) / 32, 2);
   norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(workspace, (int)grid, H, dgamma, dbeta);
-  MRK_CUDA_OK(cudaGetLastError());
+  MRK_CHECK_LAUNCH();
   return 0;
 }

@@ -27,9 +27,11 @@ def framework_leaf_classes() -> Tuple[type, ...]:
     from ..models import bert, gpt2, llama
     from ..ops import modules as km
     from ..parallel import layers as pl
+    from ..parallel import tp_transform as tt
     classes = [gpt2.GPT2Block, bert.BertLayer, bert.BertEmbeddings, bert.BertOnlyMLMHead,
                llama.LlamaDecoderLayer, km.Linear, km.LayerNorm, km.RMSNorm, km.Embedding, km.Dropout,
-               pl.ColumnParallelLinear, pl.RowParallelLinear, pl.VocabParallelEmbedding, pl.ColParallelConv2d]
+               pl.ColumnParallelLinear, pl.RowParallelLinear, pl.VocabParallelEmbedding, pl.ColParallelConv2d,
+               tt.ColPara, tt.RowPara, tt._SeqScatter, tt._GatherThenLinear]
     try:
         from ..models import moe
         classes.append(moe.MoEDecoderLayer)

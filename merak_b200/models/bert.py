@@ -76,8 +76,8 @@ class BertSelfAttention(nn.Module):
         expose_fused_projection(self, "qkv", ("query", "key", "value"))
 
     def forward(self, x, key_bias=None):
-        B, L, _ = x.shape
         qkv = self.qkv(x)
+        B, L = qkv.shape[0], qkv.shape[1]     # the projection may have gathered the sequence
         local = qkv.shape[-1] // 3
         heads = local // self.attention_head_size
         qkv = qkv.view(B, L, 3 * heads, self.attention_head_size)

@@ -72,8 +72,8 @@ class GPT2Attention(nn.Module):
         self.resid_pdrop = config.resid_pdrop
 
     def forward(self, x, residual=None):
-        B, L, _ = x.shape
         qkv = self.c_attn(x)
+        B, L = qkv.shape[0], qkv.shape[1]     # the projection may have gathered the sequence
         local = qkv.shape[-1] // 3
         heads = local // self.head_dim
         ctx = flash_attention_packed(qkv.view(B, L, 3 * heads, self.head_dim), heads, heads, causal=True)

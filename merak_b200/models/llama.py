@@ -64,8 +64,8 @@ class LlamaAttention(nn.Module):
         return self._rope
 
     def forward(self, x, residual=None, position_ids=None):
-        B, L, _ = x.shape
         qkv = self.qkv_proj(x)
+        B, L = qkv.shape[0], qkv.shape[1]     # the projection may have gathered the sequence
         ratio = self.num_heads // self.num_key_value_heads
         kv_local = qkv.shape[-1] // ((ratio + 2) * self.head_dim)      # local kv heads under TP
         q_local = kv_local * ratio

@@ -52,6 +52,7 @@ def _declare(lib):
     sig("mrk_last_error", ctypes.c_char_p)
     sig("mrk_status_read", ctypes.c_uint, c_int)
     sig("mrk_abi_version", c_int)
+    sig("mrk_launch_count", ctypes.c_ulonglong)
     sig("mrk_gemm_bf16", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll,
         c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p)
     c_ull = ctypes.c_ulonglong
@@ -132,6 +133,11 @@ def assert_status_ok(what: str = ""):
     if s != 0:
         raise KernelError("device status word is 0x%x after %s (1=mbarrier timeout, 2=peer-flag "
                           "timeout, 4=bad argument)" % (s, what or "kernel"))
+
+
+def launch_count() -> int:
+    """Kernels launched by the library so far in this process."""
+    return int(kernels().mrk_launch_count())
 
 
 def ptr(t) -> int:

@@ -46,7 +46,7 @@ class _SoftmaxCrossEntropy(torch.autograd.Function):
                                     int(vocab_start), int(ignore_index), f32, stream), "mrk_ce_stats")
         if tp > 1:
             import torch.distributed as dist
-            allstats = torch.empty((tp, M, 3), dtype=torch.float32, device=lg.device)
+            allstats = torch.empty((tp * M, 3), dtype=torch.float32, device=lg.device)
             dist.all_gather_into_tensor(allstats, stats, group=tp_group)
         else:
             allstats = stats

@@ -38,6 +38,15 @@ def _reduce(x):
     return x
 
 
+def _all_gather_stacked(x, group, n):
+    """All-gather into a ``[n, *x.shape]`` tensor (allocated as the flat concatenation every
+    backend accepts)."""
+    x = x.contiguous()
+    flat = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(flat, x, group=group)
+    return flat.view((n,) + tuple(x.shape))
+
+
 def _split_last(x):
     _, n, r = _tp()
     if n == 1:
@@ -50,18 +59,16 @@ def _gather_last(x):
     group, n, _ = _tp()
     if n == 1:
         return x
-    x = x.contiguous()
-    out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(out, x, group=group)
+    out = _all_gather_stacked(x, group, n)
     return torch.cat(list(out.unbind(0)), dim=-1)
 
 
 def _gather_dim(x, dim, group, n):
     if n == 1:
         return x
-    x = x.contiguous()
-    out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(out, x, group=group)
+    out = _all_gather_stacked(x, group, n)
+    if dim == 0:
+        return out.view((n * x.shape[0],) + tuple(x.shape[1:]))
     return torch.cat(list(out.unbind(0)), dim=dim)
 
 
@@ -76,8 +83,8 @@ def _reduce_scatter_dim(x, dim, group, n):
     if n == 1:
         return x
     assert x.shape[dim] % n == 0
-    parts = torch.stack([c.contiguous() for c in x.chunk(n, dim=dim)], 0)
-    out = torch.empty_like(parts[0])
+    parts = torch.cat([c.contiguous() for c in x.chunk(n, dim=dim)], 0)     # [n*chunk0, ...]
+    out = torch.empty((parts.shape[0] // n,) + tuple(parts.shape[1:]), dtype=x.dtype, device=x.device)
     dist.reduce_scatter_tensor(out, parts, group=group)
     return out
 
@@ -211,10 +218,10 @@ def _all_to_all(x, scatter_dim, gather_dim, group, n):
     if n == 1:
         return x
     parts = [c.contiguous() for c in x.chunk(n, dim=scatter_dim)]
-    send = torch.stack(parts, 0)
+    send = torch.cat(parts, 0)
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
-    return torch.cat(list(recv.unbind(0)), dim=gather_dim)
+    return torch.cat(list(recv.chunk(n, dim=0)), dim=gather_dim)
 
 
 class _AllToAll(torch.autograd.Function):

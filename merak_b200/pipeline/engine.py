@@ -589,7 +589,9 @@ class PipelineEngine:
             ss[0] = ss[0] - dup[0]
         # a weight shared between stages (tied embeddings) is counted by its first owner only
         for spec in self.module.tied_local.values():
-            if self.stage_id != spec["stages"][0] and not self.zero:
+            already_excluded = tp > 1 and mpu.get_model_parallel_rank() != 0 and \
+                not getattr(spec["param"], "model_parallel", False)
+            if self.stage_id != spec["stages"][0] and not self.zero and not already_excluded:
                 mg = getattr(spec["param"], "main_grad", None)
                 if mg is not None:
                     ss[0] = ss[0] - mg.float().pow(2).sum()
