@@ -334,3 +334,64 @@ MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, co
   MRK_CHECK_LAUNCH();
   return 0;
 }
+
+// -------------------------------------------------------------------------------------------------
+// Allocation-free variant of the norm backward (declared in norm_noalloc.h).
+//
+// mrk_norm_bwd needs scratch for the per-block partial sums of the weight / bias gradients and
+// expects the caller to hand it in.  Code that runs where device memory can no longer be
+// requested (inside a region that forbids cudaMalloc, in a process whose memory is fully
+// pre-partitioned, behind an allocator that must not be re-entered) cannot do that, so this entry
+// point keeps the scratch in a fixed array that lives in the library image itself.
+// -------------------------------------------------------------------------------------------------
+namespace mrk {
+constexpr int kNoAllocMaxH = 2048;        // largest hidden size served
+constexpr int kNoAllocMaxBlocks = 296;    // partial-sum rows (two per SM on a 148-SM part)
+// 296 * 2 * 2048 floats = 4.6 MiB, resident on every GPU that loads this library, until exit.
+static __device__ __align__(256) float g_norm_noalloc_scratch[kNoAllocMaxBlocks * 2 * kNoAllocMaxH];
+
+// Device address of the array above, per device.  The symbol's name is only a host-side handle;
+// the address a kernel can use has to be asked for, with the device in question current.
+static float* g_norm_noalloc_ptr[64] = {nullptr};
+
+static int norm_noalloc_scratch(float** out) {
+  int dev = 0;
+  MRK_CUDA_OK(cudaGetDevice(&dev));
+  MRK_REQUIRE(dev >= 0 && dev < 64, "norm (no-alloc): device index %d out of range", dev);
+  if (g_norm_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    MRK_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_norm_noalloc_scratch));
+    MRK_REQUIRE(p != nullptr, "norm (no-alloc): scratch symbol has no device address");
+    g_norm_noalloc_ptr[dev] = p;
+  }
+  *out = g_norm_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace mrk
+
+MRK_API int mrk_norm_bwd_noalloc(const void* dy, const void* z, const void* dz_extra, const void* gamma,
+                                 const float* mean, const float* rstd, void* dres, void* dx, float* dgamma,
+                                 float* dbeta, long long M, int H, int rms, int params_f32, void* stream) {
+  MRK_REQUIRE(H % 8 == 0 && H > 0, "norm (no-alloc): hidden size %d must be a positive multiple of 8", H);
+  MRK_REQUIRE(H <= kNoAllocMaxH,
+              "norm (no-alloc): hidden size %d exceeds the built-in scratch (max %d); use mrk_norm_bwd with a "
+              "caller-provided workspace", H, kNoAllocMaxH);
+  MRK_REQUIRE(M > 0 && dy && z && gamma && rstd && dgamma, "norm (no-alloc): missing argument");
+  float* scratch = nullptr;
+  int rc = norm_noalloc_scratch(&scratch);
+  if (rc) return rc;
+  NormBwdParams p{(const __nv_bfloat16*)dy, (const __nv_bfloat16*)z, (const __nv_bfloat16*)dz_extra, gamma, mean,
+                  rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, scratch,
+                  nullptr, 0ull, 0.f, M, H, rms, params_f32};
+  cudaStream_t s = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)(M < kNoAllocMaxBlocks ? M : kNoAllocMaxBlocks);
+  // Every block overwrites its whole row of partial sums before the reduction reads rows
+  // [0, grid), so nothing in the shared array has to start at zero.
+  if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
+  else launch_norm_bwd<128, 2>(p, grid, s);
+  MRK_CHECK_LAUNCH();
+  dim3 rgrid((H + 31) / 32, 2);
+  norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(scratch, (int)grid, H, dgamma, dbeta);
+  MRK_CHECK_LAUNCH();
+  return 0;
+}
