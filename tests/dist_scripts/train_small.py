@@ -70,6 +70,9 @@ def main():
         it = trainer.load_checkpoint(o.resume)
         trainer.params.resume(it)
     data_iter = trainer._batch_iter(trainer.train_dataloader)
+    if o.resume:
+        for _ in range(it * o.gas):        # the fixed-order loader restarts at 0: skip what was consumed
+            next(data_iter)
     for _ in range(o.steps):
         losses.append(float(engine.train_batch(data_iter)))
         trainer.params.step()
