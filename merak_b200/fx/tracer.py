@@ -33,6 +33,11 @@ def framework_leaf_classes() -> Tuple[type, ...]:
                pl.ColumnParallelLinear, pl.RowParallelLinear, pl.VocabParallelEmbedding, pl.ColParallelConv2d,
                tt.ColPara, tt.RowPara, tt._SeqScatter, tt._GatherThenLinear]
     try:
+        from ..parallel import ulysses
+        classes += [ulysses.SplitSequence, ulysses.GatherSequence]
+    except Exception:
+        pass
+    try:
         from ..models import moe
         classes.append(moe.MoEDecoderLayer)
     except Exception:

@@ -507,6 +507,7 @@ class PipelineEngine:
             self.timers("backward_tied_allreduce").start()
         self.module.allreduce_tied_weight_gradients()
         self._reduce_sequence_parallel_grads()
+        self._reduce_ulysses_grads()
         if self.wall_clock_breakdown:
             self.timers("backward_tied_allreduce").stop()
 
@@ -521,6 +522,25 @@ class PipelineEngine:
                 g = g if g is not None else p.grad
                 if g is not None:
                     dist.all_reduce(g, group=group)
+
+    def _reduce_ulysses_grads(self):
+        """Under Ulysses sequence parallelism every rank of the sequence group saw a different slice
+        of the tokens: parameter gradients are summed over that group."""
+        n = mpu.get_sequence_parallel_world_size()
+        if n == 1:
+            return
+        group = mpu.get_sequence_parallel_group()
+        if self.flat is not None:
+            dist.all_reduce(self.flat.grad, group=group)
+            for p in self.flat.params:
+                if getattr(p, "ulysses_replicated", False):
+                    p.main_grad.div_(n)
+        else:
+            for p in self._unique_params():
+                if p.grad is not None:
+                    dist.all_reduce(p.grad, group=group)
+                    if getattr(p, "ulysses_replicated", False):
+                        p.grad.div_(n)
 
     def _exec_reduce_grads(self):
         if self.wall_clock_breakdown:

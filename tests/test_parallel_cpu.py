@@ -84,3 +84,8 @@ def test_pp2_tp2_recompute_4ranks(tmp_path, baseline):
 def test_pp2_dp2_layer_split_4ranks(tmp_path, baseline):
     got = run_layout(tmp_path, "pp2dp2", 4, ["--pp", "2", "--dp", "2", "--gas", "2", "--split", "layer_split"])
     assert_close(got, baseline["gpt2"])
+
+
+def test_ulysses_sp2_matches_single(tmp_path, baseline):
+    got = run_layout(tmp_path, "sp2", 2, ["--sp", "2", "--model", "llama"])
+    assert_close(got, baseline["llama"])
