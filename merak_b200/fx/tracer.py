@@ -33,6 +33,12 @@ def framework_leaf_classes() -> Tuple[type, ...]:
                pl.ColumnParallelLinear, pl.RowParallelLinear, pl.VocabParallelEmbedding, pl.ColParallelConv2d,
                tt.ColPara, tt.RowPara, tt._SeqScatter, tt._GatherThenLinear]
     try:
+        from ..parallel import tp_overlap
+        classes += [tp_overlap.PipedRowParallelLinear, tp_overlap.PipedColumnParallelLinear,
+                    tp_overlap.ChunkPipelinedBlock]
+    except Exception:
+        pass
+    try:
         from ..parallel import ulysses
         classes += [ulysses.SplitSequence, ulysses.GatherSequence]
     except Exception:

@@ -65,6 +65,11 @@ class PipelineModule(nn.Module):
         if tp > 1 and model is not None:
             apply_tensor_parallel(model, megatron_sp=getattr(args, "megatron_sequence_parallel", False),
                                   seq_dim=args.sequence_dim, vocab_parallel=args.parallel_vocab)
+        if tp > 1 and model is not None and getattr(args, "tp_overlapping_level", 0) > 0:
+            from ..fx.tracer import framework_leaf_classes
+            from ..parallel.tp_overlap import apply_tp_overlap
+            blocks = tuple(c for c in framework_leaf_classes() if c.__name__.endswith(("Block", "DecoderLayer", "BertLayer")))
+            apply_tp_overlap(model, args.tp_overlapping_level, getattr(args, "comm_mode", "nccl"), blocks)
         if getattr(args, "sequence_parallel", False) and mpu.get_sequence_parallel_world_size() > 1:
             from ..parallel.ulysses import replace_to_sp_module
             replace_to_sp_module(model, args)

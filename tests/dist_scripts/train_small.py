@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--dp", type=int, default=1)
     ap.add_argument("--sp", type=int, default=1)
+    ap.add_argument("--tp_overlap", type=int, default=0)
     ap.add_argument("--model", default="gpt2")
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--mbs", type=int, default=2)
@@ -59,7 +60,7 @@ def main():
         lr_scheduler_type="constant", weight_decay=0.01, wall_clock_breakdown=False, report_to="none",
         no_cuda=(o.device == "cpu"), train_schedule=o.schedule, activation_checkpointing=bool(o.recompute),
         activation_checkpoint_ratio=[o.ratio] if o.ratio else None, zero_stage=1 if o.zero else None,
-        parallel_vocab=bool(o.parallel_vocab), sequence_parallel=o.sp > 1, megatron_sequence_parallel=bool(o.megatron_sp),
+        parallel_vocab=bool(o.parallel_vocab), sequence_parallel=o.sp > 1, tp_overlapping_level=o.tp_overlap, megatron_sequence_parallel=bool(o.megatron_sp),
         split_method=o.split, bf16=(o.dtype == "bf16"), seed=1234, save=bool(o.save_dir), save_steps=o.steps,
         resume_from_checkpoint=o.resume, comm_mode="nccl")
     # every data-parallel layout must see the same global batch per step: dataset order is by index

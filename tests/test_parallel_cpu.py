@@ -89,3 +89,9 @@ def test_pp2_dp2_layer_split_4ranks(tmp_path, baseline):
 def test_ulysses_sp2_matches_single(tmp_path, baseline):
     got = run_layout(tmp_path, "sp2", 2, ["--sp", "2", "--model", "llama"])
     assert_close(got, baseline["llama"])
+
+
+@pytest.mark.parametrize("level", [1, 2, 3])
+def test_tp2_sub_pipelined_overlap_levels(tmp_path, baseline, level):
+    got = run_layout(tmp_path, "tp2_ov%d" % level, 2, ["--tp", "2", "--tp_overlap", str(level)])
+    assert_close(got, baseline["gpt2"])
