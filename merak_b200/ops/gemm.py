@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from . import _lib
+from . import _lib, flop_counter
 
 ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_RELU, ACT_SILU = 0, 1, 2, 3, 4
 AUX_NONE, AUX_ADD, AUX_DACT = 0, 1, 2
@@ -105,6 +105,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     assert K == Kb, "inner dimensions differ: %d vs %d" % (K, Kb)
+    if flop_counter.enabled():
+        flop_counter.add(2 * M * N * K)
     if not _lib.use_kernels(a, b):
         return _reference(a, b, a_mn, b_mn, bias, act, aux_in, aux_mode, alpha, out, accumulate,
                           out.dtype if out is not None else out_dtype, want_preact)

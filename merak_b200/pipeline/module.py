@@ -99,7 +99,19 @@ class PipelineModule(nn.Module):
         elif a.partition_method == "custom":
             kw["custom"] = a.custom_partition
         elif a.partition_method == "autopipe":
-            fwd = [max(1, c // 1000) for c in self.param_counts]
+            # per-shard forward MFLOPs from the profiler (backward = 3x), like the reference's
+            # autopipe path; parameter counts stand in when the model cannot be run here (meta weights)
+            fwd = None
+            dummy = getattr(self.all_layers[0], "dummy_inputs", None)
+            if dummy is not None:
+                try:
+                    from ..fx.split import run_shards
+                    from .profiler import profile_layer_costs
+                    fwd = profile_layer_costs(self.all_layers, lambda: run_shards(self.all_layers, dummy))
+                except Exception:
+                    fwd = None
+            if fwd is None:
+                fwd = [max(1, c // 1000) for c in self.param_counts]
             kw["fwd_costs"], kw["bwd_costs"] = fwd, [3 * f for f in fwd]
         parts = partition_layers(a.partition_method, self.num_layers_total, self.num_stages, **kw)
         if any(parts[i] == parts[i + 1] for i in range(self.num_stages)) and self.num_layers_total >= self.num_stages:
