@@ -43,7 +43,8 @@ struct AttnFwdSmem {
   static constexpr int kKVOff = kTile;
   static constexpr int kPOff = kKVOff + kStages * 2 * kTile;
   static constexpr int kBarOff = kPOff + kPBytes;
-  static constexpr int kTotal = kBarOff + 256 + 1024;
+  static constexpr int kBiasOff = kBarOff + 256;             // 2 x 128 floats: key bias of the current / next block
+  static constexpr int kTotal = kBiasOff + 1024 + 1024;
 };
 
 template <int D>
@@ -189,6 +190,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     const float* kb = p.key_bias ? p.key_bias + (long long)b * p.Lk : nullptr;
+    float* kbs_base = reinterpret_cast<float*>(smem + L::kBiasOff);
 
     for (int j = 0; j < n_blocks && ok; ++j) {
       ok = mbar_wait(smem_u32(&s_full[j & 1]), (j >> 1) & 1, abort_flag, p.status);
@@ -197,7 +199,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
       const uint32_t s_tmem = tmem_base + lane_off + (j & 1) * 128;
       const int k0 = j * kKV;
-      const bool need_mask = (k0 + kKV > p.Lk) || (p.causal && (k0 + kKV - 1 > q0 + causal_shift)) || kb;
+      // Key bias of this block goes to shared memory once (thread r stages key k0+r); blocks whose
+      // bias is all zero (no padding) take the unbiased path.
+      bool has_bias = false;
+      float* kbs = kbs_base + (j & 1) * 128;   // double buffered: a fast thread may already stage block j+1
+      if (kb != nullptr) {
+        const float bv = (k0 + r < p.Lk) ? __ldg(kb + k0 + r) * 1.4426950408889634f : 0.f;
+        uint32_t any_nz;
+        kbs[r] = bv;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.f32 q, %1, 0f00000000;\n\t"
+            "bar.red.or.pred p, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(any_nz) : "f"(bv) : "memory");
+        has_bias = any_nz != 0;
+      }
+      const bool need_mask = (k0 + kKV > p.Lk) || (p.causal && (k0 + kKV - 1 > q0 + causal_shift)) || has_bias;
       // pass 1: row maximum
       float m_blk = -INFINITY;
 #pragma unroll 1
@@ -210,7 +228,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           for (int i = 0; i < 32; ++i) {
             const int col = k0 + c * 32 + i;
             float v = __uint_as_float(s[i]) * p.scale_log2;
-            if (kb && col < p.Lk) v += __ldg(kb + col) * 1.4426950408889634f;
+            if (has_bias) v += kbs[c * 32 + i];
             if (col >= p.Lk || (p.causal && col > row + causal_shift)) v = -INFINITY;
             m_blk = fmaxf(m_blk, v);
           }
@@ -250,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           float v = __uint_as_float(s[i]) * p.scale_log2;
           if (need_mask) {
             const int col = k0 + c * 32 + i;
-            if (kb && col < p.Lk) v += __ldg(kb + col) * 1.4426950408889634f;
+            if (has_bias) v += kbs[c * 32 + i];
             if (col >= p.Lk || (p.causal && col > row + causal_shift)) v = -INFINITY;
           }
           pr[i] = exp2f(v - m_use);

@@ -209,12 +209,15 @@ class PipelineEngine:
         self.data_iter = data_iter
         self.total_loss = None
         self._grads_reduced = False
-        sched = S.make_schedule(self.args.train_schedule, self.micro_batches, self.num_stages, self.stage_id)
-        if sched.num_pipe_buffers() != self.num_buffers:
-            self._reset_buffers(sched.num_pipe_buffers())
         if self.wall_clock_breakdown:
             self.timers("train_batch").start()
-        self._exec_schedule(sched)
+        if self._graph_capable():
+            self._train_batch_graphed()
+        else:
+            sched = S.make_schedule(self.args.train_schedule, self.micro_batches, self.num_stages, self.stage_id)
+            if sched.num_pipe_buffers() != self.num_buffers:
+                self._reset_buffers(sched.num_pipe_buffers())
+            self._exec_schedule(sched)
         self.agg_loss = self._aggregate_total_loss()
         if self.wall_clock_breakdown:
             self.timers("train_batch").stop()
@@ -252,6 +255,86 @@ class PipelineEngine:
         if reduce_output is None:
             return self.total_loss
         return self._aggregate_total_loss(n)
+
+    # ------------------------------------------------------------------------------------------
+    # CUDA-graph path (single pipeline stage): forward + backward of a micro-batch is captured once
+    # and replayed, so the several hundred kernel launches of a step cost one graph launch
+    # ------------------------------------------------------------------------------------------
+    def _graph_capable(self) -> bool:
+        return (bool(getattr(self.args, "cuda_graph", False)) and self.device.type == "cuda" and self.num_stages == 1
+                and self.flat is not None and self.loss_scaler is None and not getattr(self, "_graph_failed", False))
+
+    def _graph_step_body(self):
+        out = self.module((), self._g_ext)
+        loss = self.loss_fn(out, self._g_labels)
+        loss = loss[0] if isinstance(loss, (tuple, list)) else loss
+        (loss * (1.0 / self.micro_batches)).backward()
+        self._collect_main_grads()
+        return loss.detach()
+
+    def _graph_build(self, batch: Dict[str, torch.Tensor]):
+        from ..ops import _lib
+        self._g_ext = {k: torch.empty_like(batch[k], device=self.device) for k in self.stage_inputs if k in batch}
+        label_keys = [k for k in batch if k not in self.input_names]
+        lab = batch[label_keys[0]] if label_keys else None
+        self._g_label_key = label_keys[0] if label_keys else None
+        self._g_labels = torch.empty_like(lab, device=self.device) if lab is not None else None
+        self._graph_copy_in(batch)
+        self.module.current_buffer = 0
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):                      # eager warm-up: lazy initialisations happen here
+                dropout_state().set_call_id(0)
+                self._graph_step_body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.flat.zero_grad()
+        dropout_state().set_call_id(0)
+        graph = torch.cuda.CUDAGraph()
+        before = _lib.launch_count()
+        try:
+            with torch.cuda.graph(graph):
+                self._g_loss = self._graph_step_body()
+        except Exception as exc:        # capture is an optimisation: fall back to eager execution
+            log_dist("CUDA graph capture failed (%s); running eagerly" % str(exc).splitlines()[0], ranks=[-1])
+            self._graph_failed = True
+            self._graph = None
+            torch.cuda.synchronize()
+            self.flat.zero_grad()
+            return False
+        self._graph = graph
+        self._graph_launches = _lib.launch_count() - before
+        self.flat.zero_grad()
+        return True
+
+    def _graph_copy_in(self, batch: Dict[str, torch.Tensor]):
+        for k, dst in self._g_ext.items():
+            dst.copy_(batch[k], non_blocking=True)
+        if self._g_labels is not None:
+            self._g_labels.copy_(batch[self._g_label_key], non_blocking=True)
+
+    def _train_batch_graphed(self):
+        for mb in range(self.micro_batches):
+            batch = _as_dict(next(self.data_iter), self.batch_names)
+            if getattr(self, "_graph", None) is None:
+                if not self._graph_build(batch):
+                    # eager fallback for this and later steps
+                    sched = S.make_schedule(self.args.train_schedule, self.micro_batches, 1, 0)
+                    self._reset_buffers(sched.num_pipe_buffers())
+                    import itertools
+                    self.data_iter = itertools.chain([batch], self.data_iter)
+                    self._exec_schedule(sched)
+                    return
+            self._graph_copy_in(batch)
+            self._graph.replay()
+            self.graph_replay_launches = getattr(self, "graph_replay_launches", 0) + self._graph_launches
+            det = self._g_loss.float().clone()
+            self.total_loss = det if self.total_loss is None else self.total_loss + det
+        self._training_pass = True
+        self._exec_reduce_tied_grads()
+        self._exec_reduce_grads()
+        self._exec_optimizer_step()
 
     # ------------------------------------------------------------------------------------------
     # schedule execution
