@@ -1,0 +1,218 @@
+// Pieces shared by the single-CTA and the CTA-pair GEMM kernels: parameter block, activation
+// functions, tile rasterisation and the accumulator epilogue (TMEM -> registers -> global).
+#pragma once
+#include "gemm_tcgen05.h"
+#include "sm100_ptx.cuh"
+
+namespace mrk {
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* bias;
+  const __nv_bfloat16* aux_in;
+  long long ld_aux_in;
+  __nv_bfloat16* aux_out;
+  long long ld_aux_out;
+  int act;        // MrkAct
+  int aux_mode;   // MrkAuxMode
+  int flags;      // MrkGemmFlags
+  float alpha;
+  unsigned* status;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
+};
+
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+}
+__device__ __forceinline__ float gelu_erf_grad(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_grad(float x) {
+  const float s = 1.0f / (1.0f + __expf(-x));
+  return s * (1.0f + x * (1.0f - s));
+}
+
+__device__ __forceinline__ float apply_act(int act, float v) {
+  switch (act) {
+    case MRK_ACT_GELU_ERF: return gelu_erf(v);
+    case MRK_ACT_GELU_TANH: return gelu_tanh(v);
+    case MRK_ACT_RELU: return v > 0.f ? v : 0.f;
+    case MRK_ACT_SILU: return silu(v);
+    default: return v;
+  }
+}
+__device__ __forceinline__ float apply_act_grad(int act, float x) {
+  switch (act) {
+    case MRK_ACT_GELU_ERF: return gelu_erf_grad(x);
+    case MRK_ACT_GELU_TANH: return gelu_tanh_grad(x);
+    case MRK_ACT_RELU: return x > 0.f ? 1.f : 0.f;
+    case MRK_ACT_SILU: return silu_grad(x);
+    default: return 1.f;
+  }
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
+  // Grouped raster: 8 row-blocks share their B panel in L2 before the next group starts.
+  constexpr int kGroup = 8;
+  const int per_group = kGroup * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * kGroup;
+  const int gsz = min(num_m - first_m, kGroup);
+  const int r = tile - g * per_group;
+  m_blk = first_m + r % gsz;
+  n_blk = r / gsz;
+}
+
+// Epilogue of one accumulator tile for one thread: `row` is this thread's output row, `t_row` the
+// TMEM address of its lane at the tile's first column, `col_base` the first output column of the
+// tile and `ncols` its width.  All 32 lanes of the warp call this together.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
+                                              int col_base, int ncols, bool split_k, bool first_split) {
+  const bool out_f32 = (p.flags & MRK_GEMM_OUT_F32) != 0;
+  const bool accumulate = (p.flags & MRK_GEMM_ACCUMULATE) != 0;
+  const bool bias_f32 = (p.flags & MRK_GEMM_BIAS_F32) != 0;
+  const bool vec_ok = ((p.ldc & 7) == 0) && ((p.ld_aux_in & 7) == 0) && ((p.ld_aux_out & 7) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.aux_in) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.aux_out) & 15) == 0);
+#pragma unroll 1
+for (int c = 0; c < ncols / 32; ++c) {
+  const int col0 = col_base + c * 32;
+  if (col0 >= p.N) break;  // uniform across the warp
+  uint32_t r[32];
+  tmem_ld32(t_row + c * 32, r);
+  tmem_wait_ld();
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+  const bool full = (col0 + 32 <= p.N);
+  if (p.bias != nullptr && first_split) {
+    if (bias_f32) {
+      const float* b = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || col0 + j < p.N) v[j] += __ldg(b + j);
+    } else {
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || col0 + j < p.N) v[j] += __bfloat162float(__ldg(b + j));
+    }
+  }
+  if (row_ok && split_k) {
+    // partial sum of one K range: reduce into the fp32 output
+    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+    if (full && vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),
+                     "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+    } else {
+#pragma unroll 1
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, v[j]);
+    }
+  } else if (row_ok) {
+    if (full && vec_ok) {
+      if (p.aux_out != nullptr) {
+        uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                              pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+      }
+      if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_act(p.act, v[j]);
+      }
+      if (p.aux_mode != MRK_AUX_NONE) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 a = __ldg(src + q);
+          const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16x2(w[e]);
+            if (p.aux_mode == MRK_AUX_ADD) {
+              v[8 * q + 2 * e] += f.x;
+              v[8 * q + 2 * e + 1] += f.y;
+            } else {
+              v[8 * q + 2 * e] *= apply_act_grad(p.act, f.x);
+              v[8 * q + 2 * e + 1] *= apply_act_grad(p.act, f.y);
+            }
+          }
+        }
+      }
+      if (out_f32) {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + row * p.ldc + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          if (accumulate) {
+            const float4 old = dst[q];
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          dst[q] = o;
+        }
+      } else {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (accumulate) {
+            const uint4 old = dst[q];
+            const uint32_t w[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(w[e]);
+              v[8 * q + 2 * e] += f.x;
+              v[8 * q + 2 * e + 1] += f.y;
+            }
+          }
+          dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                              pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+        }
+      }
+    } else {
+      // ragged right edge or unaligned pitches: element-wise
+#pragma unroll 1
+      for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        if (col >= p.N) break;
+        float x = v[j];
+        if (p.aux_out != nullptr) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(x);
+        if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) x = apply_act(p.act, x);
+        if (p.aux_mode == MRK_AUX_ADD) {
+          x += __bfloat162float(p.aux_in[row * p.ld_aux_in + col]);
+        } else if (p.aux_mode == MRK_AUX_DACT) {
+          x *= apply_act_grad(p.act, __bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
+        }
+        if (out_f32) {
+          float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
+          *dst = accumulate ? (*dst + x) : x;
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+          *dst = __float2bfloat16(accumulate ? (__bfloat162float(*dst) + x) : x);
+        }
+      }
+    }
+  }
+}
+}
+
+}  // namespace mrk

@@ -17,10 +17,8 @@
 // Covers the GEMM call sites of the reference's Column/RowParallelLinear and lm_head
 // (Merak/core/mpu/layers.py:252,354) plus the bias/GELU/residual elementwise passes that
 // follow them there.
-#include "gemm_tcgen05.h"
-
+#include "gemm_common.cuh"
 #include "host_common.h"
-#include "sm100_ptx.cuh"
 
 namespace mrk {
 
@@ -28,25 +26,6 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kNumThreads = 192;
-constexpr int kFirstEpilogueWarp = 2;
-
-struct GemmParams {
-  int M, N, K;
-  void* C;
-  long long ldc;
-  const void* bias;
-  const __nv_bfloat16* aux_in;
-  long long ld_aux_in;
-  __nv_bfloat16* aux_out;
-  long long ld_aux_out;
-  int act;        // MrkAct
-  int aux_mode;   // MrkAuxMode
-  int flags;      // MrkGemmFlags
-  float alpha;
-  unsigned* status;
-  int num_m_blocks, num_n_blocks, num_k_blocks;
-  int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
-};
 
 template <int BN>
 struct SmemLayout {
@@ -57,61 +36,6 @@ struct SmemLayout {
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 alignment slack
 };
-
-__device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
-}
-__device__ __forceinline__ float gelu_erf_grad(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
-}
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
-}
-__device__ __forceinline__ float gelu_tanh_grad(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = tanhf(u);
-  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
-  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
-}
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
-__device__ __forceinline__ float silu_grad(float x) {
-  const float s = 1.0f / (1.0f + __expf(-x));
-  return s * (1.0f + x * (1.0f - s));
-}
-
-__device__ __forceinline__ float apply_act(int act, float v) {
-  switch (act) {
-    case MRK_ACT_GELU_ERF: return gelu_erf(v);
-    case MRK_ACT_GELU_TANH: return gelu_tanh(v);
-    case MRK_ACT_RELU: return v > 0.f ? v : 0.f;
-    case MRK_ACT_SILU: return silu(v);
-    default: return v;
-  }
-}
-__device__ __forceinline__ float apply_act_grad(int act, float x) {
-  switch (act) {
-    case MRK_ACT_GELU_ERF: return gelu_erf_grad(x);
-    case MRK_ACT_GELU_TANH: return gelu_tanh_grad(x);
-    case MRK_ACT_RELU: return x > 0.f ? 1.f : 0.f;
-    case MRK_ACT_SILU: return silu_grad(x);
-    default: return 1.f;
-  }
-}
-
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-  // Grouped raster: 8 row-blocks share their B panel in L2 before the next group starts.
-  constexpr int kGroup = 8;
-  const int per_group = kGroup * num_n;
-  const int g = tile / per_group;
-  const int first_m = g * kGroup;
-  const int gsz = min(num_m - first_m, kGroup);
-  const int r = tile - g * per_group;
-  m_blk = first_m + r % gsz;
-  n_blk = r / gsz;
-}
 
 template <int BN>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -239,13 +163,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------- epilogue -------------------------------
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int row_in_tile = quad * 32 + lane;
-    const bool out_f32 = (p.flags & MRK_GEMM_OUT_F32) != 0;
-    const bool accumulate = (p.flags & MRK_GEMM_ACCUMULATE) != 0;
-    const bool bias_f32 = (p.flags & MRK_GEMM_BIAS_F32) != 0;
-    const bool vec_ok = ((p.ldc & 7) == 0) && ((p.ld_aux_in & 7) == 0) && ((p.ld_aux_out & 7) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.aux_in) & 15) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.aux_out) & 15) == 0);
     int iter = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++iter) {
@@ -262,128 +179,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const long long row = (long long)m_blk * kBlockM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n_blk * BN + c * 32;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        tmem_wait_ld();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full = (col0 + 32 <= p.N);
-        if (p.bias != nullptr && first_split) {
-          if (bias_f32) {
-            const float* b = reinterpret_cast<const float*>(p.bias) + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < p.N) v[j] += __ldg(b + j);
-          } else {
-            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < p.N) v[j] += __bfloat162float(__ldg(b + j));
-          }
-        }
-        if (row_ok && split_k) {
-          // partial sum of one K range: reduce into the fp32 output
-          float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
-          if (full && vec_ok) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),
-                           "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
-          } else {
-#pragma unroll 1
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, v[j]);
-          }
-        } else if (row_ok) {
-          if (full && vec_ok) {
-            if (p.aux_out != nullptr) {
-              uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                    pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-            }
-            if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = apply_act(p.act, v[j]);
-            }
-            if (p.aux_mode != MRK_AUX_NONE) {
-              const uint4* src = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint4 a = __ldg(src + q);
-                const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 f = unpack_bf16x2(w[e]);
-                  if (p.aux_mode == MRK_AUX_ADD) {
-                    v[8 * q + 2 * e] += f.x;
-                    v[8 * q + 2 * e + 1] += f.y;
-                  } else {
-                    v[8 * q + 2 * e] *= apply_act_grad(p.act, f.x);
-                    v[8 * q + 2 * e + 1] *= apply_act_grad(p.act, f.y);
-                  }
-                }
-              }
-            }
-            if (out_f32) {
-              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + row * p.ldc + col0);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                if (accumulate) {
-                  const float4 old = dst[q];
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                dst[q] = o;
-              }
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                if (accumulate) {
-                  const uint4 old = dst[q];
-                  const uint32_t w[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 f = unpack_bf16x2(w[e]);
-                    v[8 * q + 2 * e] += f.x;
-                    v[8 * q + 2 * e + 1] += f.y;
-                  }
-                }
-                dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                    pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-              }
-            }
-          } else {
-            // ragged right edge or unaligned pitches: element-wise
-#pragma unroll 1
-            for (int j = 0; j < 32; ++j) {
-              const int col = col0 + j;
-              if (col >= p.N) break;
-              float x = v[j];
-              if (p.aux_out != nullptr) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(x);
-              if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) x = apply_act(p.act, x);
-              if (p.aux_mode == MRK_AUX_ADD) {
-                x += __bfloat162float(p.aux_in[row * p.ld_aux_in + col]);
-              } else if (p.aux_mode == MRK_AUX_DACT) {
-                x *= apply_act_grad(p.act, __bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
-              }
-              if (out_f32) {
-                float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
-                *dst = accumulate ? (*dst + x) : x;
-              } else {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
-                *dst = __float2bfloat16(accumulate ? (__bfloat162float(*dst) + x) : x);
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile(p, row, row_ok, t_row, n_blk * BN, BN, split_k, first_split);
       tc_fence_before();
       mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
@@ -433,6 +229,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
   return 0;
 }
 
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream);
+
 }  // namespace mrk
 
 using namespace mrk;
@@ -446,6 +244,9 @@ MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   MRK_REQUIRE(aux_mode == MRK_AUX_NONE || aux_in != nullptr, "gemm: aux_mode set without aux_in");
   const bool a_mn = flags & MRK_GEMM_A_MN, b_mn = flags & MRK_GEMM_B_MN;
   int bn = block_n;
+  // block_n: 0 = choose; 64/128/256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel
+  // (256 x 256 tile per 2-CTA cluster).  The pair kernel is the default for anything wide enough.
+  if (bn == 0 && M > 128 && N > 128) bn = 512;
   if (bn == 0) {
     // Heuristic: widest tile that still fills the SMs reasonably; narrow tiles for small N.
     const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
@@ -454,13 +255,14 @@ MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
     bn = (N <= 128 || (tiles256 < sm_count() && !splittable)) ? 128 : 256;
     if (N <= 64) bn = 64;
   }
-  MRK_REQUIRE(bn == 64 || bn == 128 || bn == 256, "gemm: block_n must be 64, 128 or 256");
+  MRK_REQUIRE(bn == 64 || bn == 128 || bn == 256 || bn == 512, "gemm: block_n must be 64, 128, 256 or 512");
+  const int b_box_rows = bn == 512 ? 128 : bn;
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = make_tmap_2d(&ta, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBlockK, kBlockM, 3);
   else       rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, kBlockK, 3);
   if (rc) return rc;
-  if (!b_mn) rc = make_tmap_2d(&tb, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBlockK, (uint32_t)bn, 3);
+  if (!b_mn) rc = make_tmap_2d(&tb, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBlockK, (uint32_t)b_box_rows, 3);
   else       rc = make_tmap_2d(&tb, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, kBlockK, 3);
   if (rc) return rc;
   GemmParams p;
@@ -473,6 +275,7 @@ MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 512) return launch_gemm_pair(ta, tb, p, s);
   if (bn == 256) return launch<256>(ta, tb, p, s);
   if (bn == 128) return launch<128>(ta, tb, p, s);
   return launch<64>(ta, tb, p, s);

@@ -1,0 +1,241 @@
+// CTA-pair bf16 GEMM: the same computation as gemm_tcgen05.cu, executed by clusters of two CTAs.
+//
+// One cta_group::2 UMMA multiplies a 256 x 256 x 16 block: each CTA of the pair supplies its own
+// 128 rows of A and HALF of the B tile (128 of the 256 columns), and keeps its 128 accumulator rows
+// in its own TMEM.  Per SM and k-block that is 16 KB of A + 16 KB of B for the same 128x256x64
+// of math that costs the single-CTA kernel 48 KB, i.e. one third less L2->SM traffic, which is
+// what bounds the single-CTA kernel.  No multicast is used: every CTA loads exactly the bytes it
+// keeps.
+//
+//   warp 0   TMA producer (both CTAs; completion bytes are credited to the even CTA's barrier)
+//   warp 1   TMEM allocation (both CTAs); UMMA issue + commits (even CTA only)
+//   warps 2..5  epilogue of this CTA's 128 rows
+#include "gemm_common.cuh"
+#include "host_common.h"
+
+namespace mrk {
+
+constexpr int kPairBlockM = 256;      // rows per cluster tile (128 per CTA)
+constexpr int kPairBlockN = 256;
+constexpr int kPairBlockK = 64;
+constexpr int kPairThreads = 192;
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = 128 * kPairBlockK * 2;            // this CTA's rows of A
+constexpr int kPairBBytes = (kPairBlockN / 2) * kPairBlockK * 2;  // this CTA's half of B
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;    // 32 KB
+constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + 1024 + 1024;
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const GemmParams p) {
+  constexpr uint32_t kTmemCols = 512;   // two 256-column accumulator buffers
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_base = smem + kPairStages * kPairStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);       // used in the even CTA only
+  uint64_t* empty_bar = full_bar + kPairStages;                     // one per CTA
+  uint64_t* tmem_full_bar = empty_bar + kPairStages;                // one per CTA
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;                     // used in the even CTA only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();          // 0 = leader
+  const uint32_t peer = cta ^ 1u;
+  const bool leader = cta == 0;
+  const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
+  const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&tmem_full_bar[s]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * 4 * 32);   // epilogue threads of both CTAs
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();                  // both CTAs' barriers exist before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int num_units = p.num_m_blocks * p.num_n_blocks * p.num_splits;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+        int m_blk, n_blk;
+        tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        const int m0 = m_blk * kPairBlockM + (int)cta * 128;
+        const int n0 = n_blk * kPairBlockN + (int)cta * (kPairBlockN / 2);
+        const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint32_t sb = sa + kPairABytes;
+          if (leader) mbar_arrive_expect_tx(fb, 2 * kPairStageBytes);   // bytes of both CTAs
+          const int k0 = kb * kPairBlockK;
+          if (!a_mn) {
+            tma_load_2d_pair(sa, &tma_a, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int atom = 0; atom < 2; ++atom)
+              tma_load_2d_pair(sa + atom * (kPairBlockK * 128), &tma_a, fb, m0 + atom * 64, k0);
+          }
+          if (!b_mn) {
+            tma_load_2d_pair(sb, &tma_b, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int atom = 0; atom < 2; ++atom)
+              tma_load_2d_pair(sb + atom * (kPairBlockK * 128), &tma_b, fb, n0 + atom * 64, k0);
+          }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer (leader CTA) -------------------------------
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_bf16(kPairBlockM, kPairBlockN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kPairBlockN;
+        const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint32_t sb = sa + kPairABytes;
+#pragma unroll
+          for (int k = 0; k < kPairBlockK / 16; ++k) {
+            const uint64_t da = a_mn ? desc_mnmajor(sa, k, kPairBlockK) : desc_kmajor(sa, k);
+            const uint64_t db = b_mn ? desc_mnmajor(sb, k, kPairBlockK) : desc_kmajor(sb, k);
+            umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+          }
+          // release this stage in both CTAs once the UMMAs above have read it
+          umma_commit_pair(smem_u32(&empty_bar[stage]));
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), peer));
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&tmem_full_bar[acc]));
+          umma_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[acc]), peer));
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs) -------------------------------
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int iter = 0;
+    bool ok = true;
+    for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++iter) {
+      int m_blk, n_blk;
+      tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      const bool split_k = p.num_splits > 1;
+      const bool first_split = (unit % p.num_splits) == 0;
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const long long row = (long long)m_blk * kPairBlockM + (long long)cta * 128 + row_in_tile;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kPairBlockN;
+      epilogue_tile(p, row, row_ok, t_row, n_blk * kPairBlockN, kPairBlockN, split_k, first_split);
+      tc_fence_before();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();                  // nobody leaves while its partner may still touch it
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  MRK_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MRK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kPairSmemTotal));
+    configured[dev & 63] = true;
+  }
+  p.num_m_blocks = (p.M + kPairBlockM - 1) / kPairBlockM;
+  p.num_n_blocks = (p.N + kPairBlockN - 1) / kPairBlockN;
+  p.num_k_blocks = (p.K + kPairBlockK - 1) / kPairBlockK;
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int max_clusters = sm_count() / 2;
+  p.num_splits = 1;
+  const bool can_split = (p.flags & MRK_GEMM_OUT_F32) && (p.flags & MRK_GEMM_ACCUMULATE) &&
+                         p.act == MRK_ACT_NONE && p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr;
+  if (can_split && tiles * 2 <= max_clusters && p.num_k_blocks >= 16) {
+    int want = max_clusters / tiles;
+    const int max_by_k = p.num_k_blocks / 8;
+    if (want > max_by_k) want = max_by_k;
+    if (want > 32) want = 32;
+    if (want > 1) p.num_splits = want;
+  }
+  p.kb_per_split = (p.num_k_blocks + p.num_splits - 1) / p.num_splits;
+  p.num_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  const int units = tiles * p.num_splits;
+  const int clusters = units < max_clusters ? units : max_clusters;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, p));
+  count_launch();
+  return 0;
+}
+
+}  // namespace mrk

@@ -22,7 +22,7 @@ def _check(out, ref, K, what):
 @pytest.mark.parametrize("b_mn", [False, True])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 768, 320), (1024, 1024, 1024),
                                    (200, 264, 72), (77, 40, 24), (4096, 3072, 1024)])
-@pytest.mark.parametrize("block_n", [0, 128, 256])
+@pytest.mark.parametrize("block_n", [0, 128, 256, 512])
 def test_gemm_layouts(shape, a_mn, b_mn, block_n):
     M, N, K = shape
     torch.manual_seed(0)
