@@ -24,21 +24,44 @@ struct GemmParams {
   int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
 };
 
+// erf-GELU pieces from one exponential: with e = exp(-x^2/2), the normal pdf is e/sqrt(2 pi) and
+// erf(|x|/sqrt 2) = 1 - poly(t) * e, t = 1/(1 + p |x|/sqrt 2) (Abramowitz-Stegun 7.1.26, |error| < 1.5e-7).
+// About 20 instructions per element instead of the ~60 of erff + expf, which matters because the
+// epilogue warps evaluate it for every output element.
+__device__ __forceinline__ void gelu_erf_parts(float x, float& cdf, float& pdf) {
+  const float ax = fabsf(x) * 0.7071067811865476f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  const float e = __expf(-ax * ax);
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(t, poly, 1.421413741f);
+  poly = fmaf(t, poly, -0.284496736f);
+  poly = fmaf(t, poly, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.0f);
+  cdf = 0.5f * (1.0f + copysignf(erf_abs, x));
+  pdf = 0.3989422804014327f * e;
+}
 __device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+  float cdf, pdf;
+  gelu_erf_parts(x, cdf, pdf);
+  return x * cdf;
 }
 __device__ __forceinline__ float gelu_erf_grad(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float cdf, pdf;
+  gelu_erf_parts(x, cdf, pdf);
+  return fmaf(x, pdf, cdf);
+}
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  return 0.5f * x * (1.0f + fast_tanh(u));
 }
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = tanhf(u);
+  const float t = fast_tanh(u);
   const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
 }
@@ -48,7 +71,8 @@ __device__ __forceinline__ float silu_grad(float x) {
   return s * (1.0f + x * (1.0f - s));
 }
 
-__device__ __forceinline__ float apply_act(int act, float v) {
+template <int act>
+__device__ __forceinline__ float apply_act(float v) {
   switch (act) {
     case MRK_ACT_GELU_ERF: return gelu_erf(v);
     case MRK_ACT_GELU_TANH: return gelu_tanh(v);
@@ -57,7 +81,8 @@ __device__ __forceinline__ float apply_act(int act, float v) {
     default: return v;
   }
 }
-__device__ __forceinline__ float apply_act_grad(int act, float x) {
+template <int act>
+__device__ __forceinline__ float apply_act_grad(float x) {
   switch (act) {
     case MRK_ACT_GELU_ERF: return gelu_erf_grad(x);
     case MRK_ACT_GELU_TANH: return gelu_tanh_grad(x);
@@ -82,7 +107,8 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // Epilogue of one accumulator tile for one thread: `row` is this thread's output row, `t_row` the
 // TMEM address of its lane at the tile's first column, `col_base` the first output column of the
 // tile and `ncols` its width.  All 32 lanes of the warp call this together.
-__device__ __forceinline__ void epilogue_tile(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
+template <int kAct, int kAux>
+__device__ __noinline__ void epilogue_tile_t(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
                                               int col_base, int ncols, bool split_k, bool first_split) {
   const bool out_f32 = (p.flags & MRK_GEMM_OUT_F32) != 0;
   const bool accumulate = (p.flags & MRK_GEMM_ACCUMULATE) != 0;
@@ -124,8 +150,9 @@ for (int c = 0; c < ncols / 32; ++c) {
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),
                      "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
     } else {
-#pragma unroll 1
-      for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, v[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)      // unrolled with a guard: v[] must stay in registers
+        if (col0 + j < p.N) atomicAdd(dst + j, v[j]);
     }
   } else if (row_ok) {
     if (full && vec_ok) {
@@ -136,11 +163,11 @@ for (int c = 0; c < ncols / 32; ++c) {
           dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
                               pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
       }
-      if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) {
+      if (kAct != MRK_ACT_NONE && kAux != MRK_AUX_DACT) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = apply_act(p.act, v[j]);
+        for (int j = 0; j < 32; ++j) v[j] = apply_act<kAct>(v[j]);
       }
-      if (p.aux_mode != MRK_AUX_NONE) {
+      if (kAux != MRK_AUX_NONE) {
         const uint4* src = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -149,12 +176,12 @@ for (int c = 0; c < ncols / 32; ++c) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 f = unpack_bf16x2(w[e]);
-            if (p.aux_mode == MRK_AUX_ADD) {
+            if (kAux == MRK_AUX_ADD) {
               v[8 * q + 2 * e] += f.x;
               v[8 * q + 2 * e + 1] += f.y;
             } else {
-              v[8 * q + 2 * e] *= apply_act_grad(p.act, f.x);
-              v[8 * q + 2 * e + 1] *= apply_act_grad(p.act, f.y);
+              v[8 * q + 2 * e] *= apply_act_grad<kAct>(f.x);
+              v[8 * q + 2 * e + 1] *= apply_act_grad<kAct>(f.y);
             }
           }
         }
@@ -189,18 +216,19 @@ for (int c = 0; c < ncols / 32; ++c) {
         }
       }
     } else {
-      // ragged right edge or unaligned pitches: element-wise
-#pragma unroll 1
+      // ragged right edge or unaligned pitches: element-wise (unrolled with a guard, so that v[]
+      // is never indexed dynamically and stays in registers on the vector path too)
+#pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int col = col0 + j;
-        if (col >= p.N) break;
+        if (col >= p.N) continue;
         float x = v[j];
         if (p.aux_out != nullptr) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(x);
-        if (p.act != MRK_ACT_NONE && p.aux_mode != MRK_AUX_DACT) x = apply_act(p.act, x);
-        if (p.aux_mode == MRK_AUX_ADD) {
+        if (kAct != MRK_ACT_NONE && kAux != MRK_AUX_DACT) x = apply_act<kAct>(x);
+        if (kAux == MRK_AUX_ADD) {
           x += __bfloat162float(p.aux_in[row * p.ld_aux_in + col]);
-        } else if (p.aux_mode == MRK_AUX_DACT) {
-          x *= apply_act_grad(p.act, __bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
+        } else if (kAux == MRK_AUX_DACT) {
+          x *= apply_act_grad<kAct>(__bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
         }
         if (out_f32) {
           float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
@@ -213,6 +241,28 @@ for (int c = 0; c < ncols / 32; ++c) {
     }
   }
 }
+}
+
+// Picks the epilogue specialised for (activation, aux mode) once per tile, so the per-element code
+// has no run-time dispatch.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
+                                              int col_base, int ncols, bool split_k, bool first_split) {
+#define MRK_EPI(ACT, AUX) epilogue_tile_t<ACT, AUX>(p, row, row_ok, t_row, col_base, ncols, split_k, first_split)
+#define MRK_EPI_ACT(ACT)                                             \
+  do {                                                               \
+    if (p.aux_mode == MRK_AUX_ADD) MRK_EPI(ACT, MRK_AUX_ADD);        \
+    else if (p.aux_mode == MRK_AUX_DACT) MRK_EPI(ACT, MRK_AUX_DACT); \
+    else MRK_EPI(ACT, MRK_AUX_NONE);                                 \
+  } while (0)
+  switch (p.act) {
+    case MRK_ACT_GELU_ERF: MRK_EPI_ACT(MRK_ACT_GELU_ERF); break;
+    case MRK_ACT_GELU_TANH: MRK_EPI_ACT(MRK_ACT_GELU_TANH); break;
+    case MRK_ACT_RELU: MRK_EPI_ACT(MRK_ACT_RELU); break;
+    case MRK_ACT_SILU: MRK_EPI_ACT(MRK_ACT_SILU); break;
+    default: MRK_EPI_ACT(MRK_ACT_NONE); break;
+  }
+#undef MRK_EPI_ACT
+#undef MRK_EPI
 }
 
 }  // namespace mrk

@@ -5,7 +5,7 @@
 //               shared-memory stages (no multicast).
 //   warp 1      allocates TMEM, then one lane issues tcgen05.mma (128 x BN x 16 per instruction)
 //               into one of two TMEM accumulator buffers and commits stage / accumulator barriers.
-//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread), apply
+//   warps 2..9  epilogue (two warps per TMEM lane quadrant, half the columns each): tcgen05.ld the finished accumulator (one row per thread), apply
 //               bias / activation / residual / activation-derivative, store bf16 or fp32.
 // The two accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1.
 //
@@ -25,7 +25,7 @@ namespace mrk {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 320;       // TMA warp, UMMA warp, 8 epilogue warps
 
 template <int BN>
 struct SmemLayout {
@@ -69,7 +69,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[s]), 4 * 32);
+      mbar_init(smem_u32(&tmem_empty_bar[s]), 8 * 32);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -179,7 +179,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const long long row = (long long)m_blk * kBlockM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-      epilogue_tile(p, row, row_ok, t_row, n_blk * BN, BN, split_k, first_split);
+      // two warps share a TMEM lane quadrant: warps 2..5 take the left half of the columns, 6..9 the right
+      const int half = (warp - 2) >> 2;
+      epilogue_tile(p, row, row_ok, t_row + half * (BN / 2), n_blk * BN + half * (BN / 2), BN / 2, split_k,
+                    first_split);
       tc_fence_before();
       mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }

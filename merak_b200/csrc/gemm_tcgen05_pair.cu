@@ -9,7 +9,7 @@
 //
 //   warp 0   TMA producer (both CTAs; completion bytes are credited to the even CTA's barrier)
 //   warp 1   TMEM allocation (both CTAs); UMMA issue + commits (even CTA only)
-//   warps 2..5  epilogue of this CTA's 128 rows
+//   warps 2..9  epilogue of this CTA's 128 rows (two warps per TMEM lane quadrant, half the columns each)
 #include "gemm_common.cuh"
 #include "host_common.h"
 
@@ -18,7 +18,7 @@ namespace mrk {
 constexpr int kPairBlockM = 256;      // rows per cluster tile (128 per CTA)
 constexpr int kPairBlockN = 256;
 constexpr int kPairBlockK = 64;
-constexpr int kPairThreads = 192;
+constexpr int kPairThreads = 320;     // TMA warp, UMMA warp, 8 epilogue warps
 constexpr int kPairStages = 6;
 constexpr int kPairABytes = 128 * kPairBlockK * 2;            // this CTA's rows of A
 constexpr int kPairBBytes = (kPairBlockN / 2) * kPairBlockK * 2;  // this CTA's half of B
@@ -55,7 +55,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * 4 * 32);   // epilogue threads of both CTAs
+      mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * 8 * 32);   // epilogue threads of both CTAs
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -175,7 +175,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       const long long row = (long long)m_blk * kPairBlockM + (long long)cta * 128 + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kPairBlockN;
-      epilogue_tile(p, row, row_ok, t_row, n_blk * kPairBlockN, kPairBlockN, split_k, first_split);
+      // two warps share a TMEM lane quadrant: warps 2..5 take the left half of the columns, 6..9 the right
+      const int half = (warp - 2) >> 2;
+      epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), n_blk * kPairBlockN + half * (kPairBlockN / 2),
+                    kPairBlockN / 2, split_k, first_split);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
     }
