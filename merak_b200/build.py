@@ -42,7 +42,8 @@ def _nvcc() -> str:
 
 
 def _newest_header_mtime() -> float:
-    hdrs = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h"))
+    hdrs = (glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) +
+            glob.glob(os.path.join(CSRC, "*.inc")))
     return max([os.path.getmtime(h) for h in hdrs] + [0.0])
 
 

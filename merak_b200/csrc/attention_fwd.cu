@@ -1,14 +1,19 @@
 // Flash attention forward on tcgen05: O = softmax(scale * Q K^T + mask) V, plus the row
-// log-sum-exp needed by the backward pass.  One CTA owns one 128-row query block of one
-// (batch, head); key/value blocks of 128 stream through a TMA-fed shared-memory ring.
+// log-sum-exp needed by the backward pass.
 //
-//   warp 0       TMA producer (Q once, then K/V blocks)
-//   warp 1       UMMA issuer:  S_j = Q K_j^T  (TMEM, double buffered)   and   O_j = P_j V_j (TMEM)
-//   warps 2..5   softmax: thread r owns query row r (TMEM lane r): row max / exp2 / row sum need
-//                no shuffles; P_j is written to shared memory as the 128B-swizzled A operand of
-//                the second product; the running output is rescaled and accumulated in registers.
-// S_{j+1} is issued before P_j V_j, so the tensor core works on the next score block while the
-// softmax warps process the current one.
+// One CTA owns NT query tiles of 128 rows of one (batch, head) (NT = 2 for head dim 64, 1 for 128);
+// key/value blocks of 128 stream through a TMA-fed shared-memory ring shared by the tiles.
+//
+//   warp 0          TMA producer (Q tiles once, then K/V blocks)
+//   warp 1          UMMA issuer: per tile t and key block j:  S_t = Q_t K_j^T  and  O_t = P_t V_j
+//   warps 2..5      softmax warpgroup of tile 0      (thread r owns query row r = TMEM lane r:
+//   warps 6..9      softmax warpgroup of tile 1       row max / exp2 / row sum need no shuffles)
+//
+// The two warpgroups ping-pong: while one runs the softmax of its score block on the CUDA cores,
+// the tensor core computes the other tile's scores and P V product.  P goes to shared memory as
+// the 128B-swizzled A operand of the second product; each block's P V result is read back from
+// TMEM and folded into a register accumulator with the (deferred) rescale factor, one FMA per
+// element.
 //
 // Replaces the eager matmul -> softmax -> dropout -> matmul attention the reference's models use
 // (examples/models/gpt2/config.py:28 forces eager attention) and the SDPA/FlashAttention-2 calls
@@ -19,9 +24,7 @@
 
 namespace mrk {
 
-constexpr int kQ = 128;   // query rows per CTA
 constexpr int kKV = 128;  // keys per block
-constexpr int kAttnThreads = 192;
 
 struct AttnFwdParams {
   __nv_bfloat16* out;           // [B, Lq, H, D] with strides below
@@ -34,27 +37,40 @@ struct AttnFwdParams {
   unsigned* status;
 };
 
-template <int D>
+template <int D, int NT>
 struct AttnFwdSmem {
   static constexpr int kTile = 128 * D * 2;                  // one Q / K / V tile
   static constexpr int kStages = (D == 64) ? 3 : 2;
   static constexpr int kPBytes = 128 * 128 * 2;
   static constexpr int kQOff = 0;
-  static constexpr int kKVOff = kTile;
+  static constexpr int kKVOff = NT * kTile;
   static constexpr int kPOff = kKVOff + kStages * 2 * kTile;
-  static constexpr int kBarOff = kPOff + kPBytes;
-  static constexpr int kBiasOff = kBarOff + 256;             // 2 x 128 floats: key bias of the current / next block
-  static constexpr int kTotal = kBiasOff + 1024 + 1024;
+  static constexpr int kBarOff = kPOff + NT * kPBytes;
+  static constexpr int kBiasOff = kBarOff + 256;             // NT x 2 x 128 floats: staged key bias
+  static constexpr int kTotal = kBiasOff + NT * 1024 + 1024;
+  static constexpr int kThreads = 64 + NT * 128;
 };
 
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+// Barrier over the 128 threads of one softmax warpgroup that also ORs a predicate (v != 0).
+__device__ __forceinline__ bool named_bar_any_nonzero(uint32_t bar_id, float v) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.f32 q, %1, 0f00000000;\n\t"
+      "bar.red.or.pred p, %2, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "f"(v), "r"(bar_id) : "memory");
+  return r != 0;
+}
+
+template <int D, int NT>
+__global__ void __launch_bounds__(AttnFwdSmem<D, NT>::kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const AttnFwdParams p) {
-  using L = AttnFwdSmem<D>;
+  using L = AttnFwdSmem<D, NT>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kOCol = 256;  // S buffers at columns 0 and 128, O at 256
+  constexpr uint32_t kOCol = 256;  // S_t at column t*128, O_t at 256 + t*D
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -63,24 +79,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint64_t* q_full = bars;                 // 1
   uint64_t* kv_full = bars + 1;            // kStages
   uint64_t* kv_empty = kv_full + kStages;  // kStages
-  uint64_t* s_full = kv_empty + kStages;   // 2
-  uint64_t* s_empty = s_full + 2;          // 2
-  uint64_t* p_full = s_empty + 2;          // 1
-  uint64_t* o_full = p_full + 1;           // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* s_full = kv_empty + kStages;   // per tile
+  uint64_t* p_full = s_full + 2;           // per tile (128 arrivals): P_t written, S_t and O_t consumed
+  uint64_t* o_full = p_full + 2;           // per tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / (p.H / p.Hkv);
-  const int q0 = q_blk * kQ;
+  const int q0 = q_blk * (128 * NT);
+  const int causal_shift = p.Lk - p.Lq;    // key j visible to query i iff j <= i + shift
 
-  int n_blocks = (p.Lk + kKV - 1) / kKV;
-  if (p.causal) {
-    // keys visible to the last row of this block: row + (Lk - Lq)
-    const int last_key = min(p.Lk - 1, q0 + kQ - 1 + (p.Lk - p.Lq));
-    n_blocks = last_key < 0 ? 0 : min(n_blocks, last_key / kKV + 1);
+  // key blocks needed by tile t (causal: up to the diagonal of its last row)
+  int n_tile[2] = {0, 0};
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    int n = (p.Lk + kKV - 1) / kKV;
+    if (q0 + t * 128 >= p.Lq) n = 0;
+    else if (p.causal) {
+      const int last_key = min(p.Lk - 1, q0 + t * 128 + 127 + causal_shift);
+      n = last_key < 0 ? 0 : min(n, last_key / kKV + 1);
+    }
+    n_tile[t] = n;
   }
+  const int n_blocks = max(n_tile[0], n_tile[1]);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -89,12 +112,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(smem_u32(&kv_full[s]), 1);
       mbar_init(smem_u32(&kv_empty[s]), 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&s_full[s]), 1);
-      mbar_init(smem_u32(&s_empty[s]), 128);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&s_full[t]), 1);
+      mbar_init(smem_u32(&p_full[t]), 128);
+      mbar_init(smem_u32(&o_full[t]), 1);
     }
-    mbar_init(smem_u32(p_full), 128);
-    mbar_init(smem_u32(o_full), 1);
     fence_mbar_init();
     tma_prefetch_desc(&tq);
     tma_prefetch_desc(&tk);
@@ -113,10 +135,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0 && n_blocks > 0) {
-      mbar_arrive_expect_tx(smem_u32(q_full), L::kTile);
+      mbar_arrive_expect_tx(smem_u32(q_full), NT * L::kTile);
 #pragma unroll
-      for (int a = 0; a < D / 64; ++a)
-        tma_load_4d(q_smem + a * 16384, &tq, smem_u32(q_full), a * 64, q0, h, b);
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_4d(q_smem + t * L::kTile + a * 16384, &tq, smem_u32(q_full), a * 64, q0 + t * 128, h, b);
       int stage = 0;
       uint32_t phase = 0;
       for (int j = 0; j < n_blocks; ++j) {
@@ -138,194 +162,55 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
       const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);    // P (K-major) x V (MN-major)
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status);
-      int stage = 0;
+      int stage = 0, pv_stage = 0;
       uint32_t phase = 0;
-      int pv_stage = 0;
       for (int j = 0; j <= n_blocks && ok; ++j) {
+        uint32_t ks = 0;
         if (j < n_blocks) {
           ok = mbar_wait(smem_u32(&kv_full[stage]), phase, abort_flag, p.status);
           if (!ok) break;
-          ok = mbar_wait(smem_u32(&s_empty[j & 1]), ((j >> 1) & 1) ^ 1u, abort_flag, p.status);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t ks = smem_u32(smem + L::kKVOff + stage * 2 * L::kTile);
-          const uint32_t s_tmem = tmem_base + (j & 1) * 128;
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint64_t da = desc_kmajor(q_smem + (k / 4) * 16384, k % 4);
-            const uint64_t db = desc_kmajor(ks + (k / 4) * 16384, k % 4);
-            umma_bf16_ss(s_tmem, da, db, idesc_s, k != 0 ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&s_full[j & 1]));
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          ks = smem_u32(smem + L::kKVOff + stage * 2 * L::kTile);
         }
-        if (j >= 1) {
-          const int jj = j - 1;
-          ok = mbar_wait(smem_u32(p_full), jj & 1, abort_flag, p.status);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t vs = smem_u32(smem + L::kKVOff + pv_stage * 2 * L::kTile) + L::kTile;
-#pragma unroll
-          for (int k = 0; k < kKV / 16; ++k) {
-            const uint64_t da = desc_kmajor(p_smem + (k / 4) * 16384, k % 4);
-            const uint64_t db = desc_mnmajor(vs, k, 128);
-            umma_bf16_ss(tmem_base + kOCol, da, db, idesc_o, k != 0 ? 1u : 0u);
+        const uint32_t vs = smem_u32(smem + L::kKVOff + pv_stage * 2 * L::kTile) + L::kTile;
+        for (int t = 0; t < NT && ok; ++t) {
+          const bool do_s = j < n_tile[t];
+          const bool do_pv = j >= 1 && (j - 1) < n_tile[t];
+          if (do_pv) {   // softmax of block j-1 finished: S_t and O_t are free, P_t is ready
+            ok = mbar_wait(smem_u32(&p_full[t]), (j - 1) & 1, abort_flag, p.status);
+            if (!ok) break;
           }
-          umma_commit(smem_u32(&kv_empty[pv_stage]));
-          umma_commit(smem_u32(o_full));
+          tc_fence_after();
+          if (do_s) {
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+              const uint64_t da = desc_kmajor(q_smem + t * L::kTile + (k / 4) * 16384, k % 4);
+              const uint64_t db = desc_kmajor(ks + (k / 4) * 16384, k % 4);
+              umma_bf16_ss(tmem_base + t * 128, da, db, idesc_s, k != 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&s_full[t]));
+          }
+          if (do_pv) {
+#pragma unroll
+            for (int k = 0; k < kKV / 16; ++k) {
+              const uint64_t da = desc_kmajor(p_smem + t * L::kPBytes + (k / 4) * 16384, k % 4);
+              const uint64_t db = desc_mnmajor(vs, k, 128);
+              umma_bf16_ss(tmem_base + kOCol + t * D, da, db, idesc_o, k != 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&o_full[t]));
+          }
+        }
+        if (!ok) break;
+        if (j >= 1) {
+          umma_commit(smem_u32(&kv_empty[pv_stage]));    // block j-1 fully consumed by every tile
           if (++pv_stage == kStages) pv_stage = 0;
+        }
+        if (j < n_blocks) {
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else {
-    // ------------------------------- softmax / output -------------------------------
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;          // row inside the block == TMEM lane
-    const int row = q0 + r;                  // query index
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const int causal_shift = p.Lk - p.Lq;    // key j visible to query i iff j <= i + shift
-    float acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    bool ok = true;
-    const float* kb = p.key_bias ? p.key_bias + (long long)b * p.Lk : nullptr;
-    float* kbs_base = reinterpret_cast<float*>(smem + L::kBiasOff);
-
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      ok = mbar_wait(smem_u32(&s_full[j & 1]), (j >> 1) & 1, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t s_tmem = tmem_base + lane_off + (j & 1) * 128;
-      const int k0 = j * kKV;
-      // Key bias of this block goes to shared memory once (thread r stages key k0+r); blocks whose
-      // bias is all zero (no padding) take the unbiased path.
-      bool has_bias = false;
-      float* kbs = kbs_base + (j & 1) * 128;   // double buffered: a fast thread may already stage block j+1
-      if (kb != nullptr) {
-        const float bv = (k0 + r < p.Lk) ? __ldg(kb + k0 + r) * 1.4426950408889634f : 0.f;
-        uint32_t any_nz;
-        kbs[r] = bv;
-        asm volatile(
-            "{\n\t.reg .pred p, q;\n\t"
-            "setp.ne.f32 q, %1, 0f00000000;\n\t"
-            "bar.red.or.pred p, 1, 128, q;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(any_nz) : "f"(bv) : "memory");
-        has_bias = any_nz != 0;
-      }
-      const bool need_mask = (k0 + kKV > p.Lk) || (p.causal && (k0 + kKV - 1 > q0 + causal_shift)) || has_bias;
-      // pass 1: row maximum
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld32(s_tmem + c * 32, s);
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = k0 + c * 32 + i;
-            float v = __uint_as_float(s[i]) * p.scale_log2;
-            if (has_bias) v += kbs[c * 32 + i];
-            if (col >= p.Lk || (p.causal && col > row + causal_shift)) v = -INFINITY;
-            m_blk = fmaxf(m_blk, v);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, __uint_as_float(s[i]) * p.scale_log2);
-        }
-      }
-      const float m_new = fmaxf(m_run, m_blk);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);   // m_run = -inf -> 0
-      // fold in the previous block's product, then rescale
-      if (j > 0) {
-        ok = mbar_wait(smem_u32(o_full), (j - 1) & 1, abort_flag, p.status);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tmem_base + lane_off + kOCol + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(o[i])) * alpha;
-        }
-      }
-      // pass 2: probabilities -> shared memory (A operand of P V), row sum
-      float l_blk = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld32(s_tmem + c * 32, s);
-        tmem_wait_ld();
-        float pr[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(s[i]) * p.scale_log2;
-          if (need_mask) {
-            const int col = k0 + c * 32 + i;
-            if (has_bias) v += kbs[c * 32 + i];
-            if (col >= p.Lk || (p.causal && col > row + causal_shift)) v = -INFINITY;
-          }
-          pr[i] = exp2f(v - m_use);
-        }
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          packed[i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
-          const float2 back = unpack_bf16x2(packed[i]);  // sum what the tensor core will see
-          l_blk += back.x + back.y;
-        }
-        // columns c*32 .. c*32+31 live in k-atom (c/2), 16-byte chunks (c%2)*4 .. +3 of row r
-        uint8_t* tile = smem + L::kPOff + (c >> 1) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = sw128_offset((uint32_t)r, (uint32_t)((c & 1) * 4 + q));
-          *reinterpret_cast<uint4*>(tile + off) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
-      }
-      l_run = l_run * alpha + l_blk;
-      m_run = m_new;
-      tc_fence_before();
-      mbar_arrive(smem_u32(&s_empty[j & 1]));
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(p_full));
-    }
-    if (n_blocks > 0 && ok) {
-      ok = mbar_wait(smem_u32(o_full), (n_blocks - 1) & 1, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tmem_base + lane_off + kOCol + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(o[i]);
-        }
-      }
-    }
-    if (row < p.Lq) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (long long)b * p.o_sb + (long long)row * p.o_ss + (long long)h * p.o_sh;
-#pragma unroll
-      for (int q = 0; q < D / 8; ++q) {
-        uint4 w = make_uint4(pack_bf16x2(acc[8 * q] * inv, acc[8 * q + 1] * inv),
-                             pack_bf16x2(acc[8 * q + 2] * inv, acc[8 * q + 3] * inv),
-                             pack_bf16x2(acc[8 * q + 4] * inv, acc[8 * q + 5] * inv),
-                             pack_bf16x2(acc[8 * q + 6] * inv, acc[8 * q + 7] * inv));
-        reinterpret_cast<uint4*>(dst)[q] = w;
-      }
-      if (p.lse)
-        p.lse[((long long)b * p.H + h) * p.Lq + row] =
-            l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-    }
+#include "attention_fwd_softmax.inc"
   }
 
   tc_fence_before();
@@ -337,19 +222,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   }
 }
 
-template <int D>
+template <int D, int NT>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const AttnFwdParams& p, cudaStream_t stream) {
-  using L = AttnFwdSmem<D>;
+  using L = AttnFwdSmem<D, NT>;
   static bool configured[64] = {false};
   int dev = 0;
   MRK_CUDA_OK(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    MRK_CUDA_OK(cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    MRK_CUDA_OK(cudaFuncSetAttribute(attn_fwd_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured[dev & 63] = true;
   }
-  dim3 grid((p.Lq + kQ - 1) / kQ, p.H, p.B);
-  attn_fwd_kernel<D><<<grid, kAttnThreads, L::kTotal, stream>>>(tq, tk, tv, p);
+  dim3 grid((p.Lq + 128 * NT - 1) / (128 * NT), p.H, p.B);
+  attn_fwd_kernel<D, NT><<<grid, L::kThreads, L::kTotal, stream>>>(tq, tk, tv, p);
   MRK_CHECK_LAUNCH();
   return 0;
 }
@@ -392,5 +277,6 @@ MRK_API int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out,
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "attention: status word unavailable");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return D == 64 ? launch_fwd<64>(tq, tk, tv, p, s) : launch_fwd<128>(tq, tk, tv, p, s);
+  if (D == 64) return Lq > 128 ? launch_fwd<64, 2>(tq, tk, tv, p, s) : launch_fwd<64, 1>(tq, tk, tv, p, s);
+  return launch_fwd<128, 1>(tq, tk, tv, p, s);
 }
