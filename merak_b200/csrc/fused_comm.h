@@ -1,0 +1,28 @@
+// C interface of the symmetric-memory data plane and the fused compute+collective kernels.
+// Pointer arrays (`*_ptrs`) are host arrays of `n` device pointers, one per rank of the group,
+// entry `rank` being this process's own buffer.  0 = success.
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+int mrk_symm_alloc(unsigned long long bytes, void** out);
+int mrk_symm_free(void* p);
+int mrk_symm_ctrl_bytes();
+int mrk_ipc_handle_bytes();
+int mrk_ipc_get_handle(void* p, unsigned char* out);
+int mrk_ipc_open(const unsigned char* handle, void** out);
+int mrk_ipc_close(void* p);
+int mrk_dp_reduce_scatter(void* const* grad_ptrs, void* const* ctrl_ptrs, int n, int rank, long long lo, long long cnt,
+                          const unsigned char* flags, unsigned epoch, int sync, int budget_ms, void* stream);
+int mrk_dp_adamw_allgather(void* const* model_ptrs, void* const* ctrl_ptrs, int n, int rank, long long lo,
+                           long long cnt, const float* grad_shard, float* master, float* m, float* v,
+                           const unsigned char* flags, const float* hp, float grad_scale, float max_norm,
+                           const float* sumsq_src, float* norm_out, int* skip_out, unsigned epoch, int sync,
+                           int wait_partials, int budget_ms, void* stream);
+int mrk_dp_norm_gather(void* const* ctrl_ptrs, int n, int rank, float* out2, unsigned epoch, int sync, int budget_ms,
+                       void* stream);
+int mrk_symm_barrier(void* const* ctrl_ptrs, int n, int rank, int which, unsigned epoch, int signal, int budget_ms,
+                     void* stream);
+#ifdef __cplusplus
+}
+#endif

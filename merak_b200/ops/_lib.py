@@ -76,6 +76,19 @@ def _declare(lib):
     sig("mrk_colsum", c_int, P, P, c_ll, c_int, c_ll, P)
     sig("mrk_dropout", c_int, P, P, c_ll, c_float, P, c_ull, P)
     sig("mrk_scaled_cast", c_int, P, P, c_ll, P, c_float, c_int, c_int, c_int, P)
+    c_uint = ctypes.c_uint
+    sig("mrk_symm_alloc", c_int, c_ull, P)
+    sig("mrk_symm_free", c_int, P)
+    sig("mrk_symm_ctrl_bytes", c_int)
+    sig("mrk_ipc_handle_bytes", c_int)
+    sig("mrk_ipc_get_handle", c_int, P, P)
+    sig("mrk_ipc_open", c_int, P, P)
+    sig("mrk_ipc_close", c_int, P)
+    sig("mrk_dp_reduce_scatter", c_int, P, P, c_int, c_int, c_ll, c_ll, P, c_uint, c_int, c_int, P)
+    sig("mrk_dp_adamw_allgather", c_int, P, P, c_int, c_int, c_ll, c_ll, P, P, P, P, P, P, c_float, c_float,
+        P, P, P, c_uint, c_int, c_int, c_int, P)
+    sig("mrk_dp_norm_gather", c_int, P, c_int, c_int, P, c_uint, c_int, c_int, P)
+    sig("mrk_symm_barrier", c_int, P, c_int, c_int, c_int, c_uint, c_int, c_int, P)
     return lib
 
 

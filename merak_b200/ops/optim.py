@@ -25,7 +25,10 @@ def _align(n: int, a: int = 64) -> int:
 class FlatBuffers:
     """Re-homes parameters into one contiguous model buffer and one fp32 gradient buffer."""
 
-    def __init__(self, params: Iterable[torch.nn.Parameter], grad_dtype=torch.float32, pad_to: int = 64):
+    def __init__(self, params: Iterable[torch.nn.Parameter], grad_dtype=torch.float32, pad_to: int = 64,
+                 allocator=None):
+        """``allocator(numel, dtype, tag)`` (tag "model" / "grad") may supply the two buffers, e.g.
+        peer-mapped memory for the fused data-parallel kernels; it must return zeroed memory."""
         self.params: List[torch.nn.Parameter] = [p for p in params]
         assert self.params, "no parameters"
         dev, dt = self.params[0].device, self.params[0].dtype
@@ -36,8 +39,12 @@ class FlatBuffers:
             self.offsets.append(off)
             off += _align(p.numel(), 64)
         self.numel = _align(off, pad_to)
-        self.model = torch.zeros(self.numel, dtype=dt, device=dev)
-        self.grad = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+        if allocator is not None:
+            self.model = allocator(self.numel, dt, "model")
+            self.grad = allocator(self.numel, grad_dtype, "grad")
+        else:
+            self.model = torch.zeros(self.numel, dtype=dt, device=dev)
+            self.grad = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
         for p, o in zip(self.params, self.offsets):
             view = self.model[o:o + p.numel()].view(p.shape)
             view.copy_(p.data)

@@ -163,7 +163,17 @@ class PipelineEngine:
             for p in params:
                 p._no_weight_decay = id(p) in no_decay or p.dim() <= 1
             pad = 64 * self.dp_size
-            self.flat = FlatBuffers(params, grad_dtype=torch.float32, pad_to=pad)
+            # Fused data-parallel step over peer-mapped flat buffers (bf16 training on one node);
+            # it shards the optimizer state exactly as ZeRO-1 does, so it also sets ``self.zero``.
+            self.fused_dp = None
+            if self.dp_size > 1 and self.device.type == "cuda" and params[0].dtype == torch.bfloat16:
+                from ..parallel.dp_fused import FusedDataParallel
+                self.fused_dp = FusedDataParallel.create(mpu.get_data_parallel_group(), self.device, a)
+            self.flat = FlatBuffers(params, grad_dtype=torch.float32, pad_to=pad,
+                                    allocator=self.fused_dp.allocator if self.fused_dp is not None else None)
+            if self.fused_dp is not None:
+                self.zero = True
+                self.fused_dp.bind(self.flat, exclude_from_norm=self._norm_excluded_params())
             shard = None
             if self.zero:
                 per = self.flat.numel // self.dp_size
@@ -177,6 +187,19 @@ class PipelineEngine:
         self.lr_scheduler = lr_scheduler
         if self.lr_scheduler is None and lr_scheduler_factory is not None:
             self.lr_scheduler = lr_scheduler_factory(self.optimizer)
+
+    def _norm_excluded_params(self) -> List[nn.Parameter]:
+        """Parameters whose gradient this rank must not count in the global gradient norm: replicas of
+        non-tensor-parallel parameters on tensor-parallel ranks other than 0, and tied weights on every
+        stage but their first owner."""
+        out = []
+        tp_dup = mpu.get_model_parallel_world_size() > 1 and mpu.get_model_parallel_rank() != 0
+        if tp_dup:
+            out += [p for p in self._unique_params() if not getattr(p, "model_parallel", False)]
+        for spec in getattr(self.module, "tied_local", {}).values():
+            if self.stage_id != spec["stages"][0]:
+                out.append(spec["param"])
+        return out
 
     # ------------------------------------------------------------------------------------------
     # buffers
@@ -640,8 +663,8 @@ class PipelineEngine:
             return
         group = mpu.get_data_parallel_group()
         if self.flat is not None:
-            from ..parallel import dp_fused
-            if dp_fused.try_fused_reduce(self, group):
+            if getattr(self, "fused_dp", None) is not None:
+                self.fused_dp.reduce_scatter()
                 self._grads_reduced = True
                 return
             g = self.flat.grad
@@ -710,12 +733,19 @@ class PipelineEngine:
         if self.wall_clock_breakdown:
             self.timers("step").start()
         a = self.args
-        grad_scale = 1.0 / self.dp_size if (self.dp_size > 1 and not getattr(self, "_fused_dp_applied_scale", False)) else 1.0
+        grad_scale = 1.0 / self.dp_size if self.dp_size > 1 else 1.0
         if self.loss_scaler is not None:
             grad_scale /= self.loss_scaler.cur_scale
         if self.flat is not None:
-            if getattr(self, "_fused_step_done", False):
-                self._fused_step_done = False       # the fused DP kernel already updated the parameters
+            if getattr(self, "fused_dp", None) is not None:
+                sumsq = None
+                if mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1:
+                    sumsq = self.fused_dp.gathered_sumsq()
+                    if mpu.get_model_parallel_world_size() > 1:
+                        dist.all_reduce(sumsq, group=mpu.get_model_parallel_group())
+                    if self.num_stages > 1:
+                        dist.all_reduce(sumsq, group=mpu.get_pipe_parallel_group())
+                self.fused_dp.adamw_allgather(self.optimizer, grad_scale, sumsq)
             else:
                 distributed_norm = (mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1 or self.zero)
                 sumsq = self._global_grad_sumsq() if distributed_norm else None

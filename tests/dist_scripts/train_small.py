@@ -39,6 +39,8 @@ def main():
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--save_dir", default=None)
     ap.add_argument("--resume", default=None)
+    ap.add_argument("--comm", default="nccl")
+    ap.add_argument("--clip", type=float, default=1.0)
     ap.add_argument("--out", required=True)
     o = ap.parse_args()
 
@@ -62,7 +64,7 @@ def main():
         activation_checkpoint_ratio=[o.ratio] if o.ratio else None, zero_stage=1 if o.zero else None,
         parallel_vocab=bool(o.parallel_vocab), sequence_parallel=o.sp > 1, tp_overlapping_level=o.tp_overlap, megatron_sequence_parallel=bool(o.megatron_sp),
         split_method=o.split, bf16=(o.dtype == "bf16"), seed=1234, save=bool(o.save_dir), save_steps=o.steps,
-        resume_from_checkpoint=o.resume, comm_mode="nccl")
+        resume_from_checkpoint=o.resume, comm_mode=o.comm, max_grad_norm=o.clip)
     # every data-parallel layout must see the same global batch per step: dataset order is by index
     ds = SyntheticTokenDataset(V, L, 16, task=task, seed=7)      # two global batches, revisited
     trainer = FixedOrderTrainer(model, args, train_dataset=ds)

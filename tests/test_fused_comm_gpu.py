@@ -1,0 +1,162 @@
+"""Fused data-parallel kernels (gradient reduce-scatter + AdamW + parameter all-gather over
+peer-mapped memory).  On one GPU the ranks are emulated: all ranks' buffers live on the same device
+and the kernels run rank after rank with the cross-rank barriers switched off; the two-process
+test needs two GPUs."""
+import ctypes
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SCRIPT = os.path.join(HERE, "dist_scripts", "train_small.py")
+
+
+def _table(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def _adam_ref(p, m, v, g, lr, b1, b2, eps, wd, t):
+    m = b1 * m + (1 - b1) * g
+    v = b2 * v + (1 - b2) * g * g
+    p = p * (1 - lr * wd) - lr * (m / (1 - b1 ** t)) / ((v / (1 - b2 ** t)).sqrt() + eps)
+    return p, m, v
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4])
+def test_dp_kernels_emulated_ranks(n):
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    torch.manual_seed(n)
+    numel = 64 * n * 37
+    per = numel // n
+    grads = [torch.randn(numel, device=dev) * 0.1 for _ in range(n)]
+    grads_in = [g.clone() for g in grads]
+    models = [torch.zeros(numel, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+    ctrl_bytes = lib.mrk_symm_ctrl_bytes()
+    ctrls = [torch.zeros(ctrl_bytes, dtype=torch.uint8, device=dev) for _ in range(n)]
+    flags = torch.zeros(numel // 64 + 1, dtype=torch.uint8, device=dev)
+    flags[: numel // 128] = 1                     # first half decays
+    flags[numel // 64 - 3: numel // 64] |= 2      # last three granules are not counted in the norm
+    master_full = torch.randn(numel, device=dev)
+    masters = [master_full[r * per:(r + 1) * per].clone() for r in range(n)]
+    ms = [torch.zeros(per, device=dev) for _ in range(n)]
+    vs = [torch.zeros(per, device=dev) for _ in range(n)]
+    lr, b1, b2, eps, wd, t = 1e-2, 0.9, 0.999, 1e-8, 0.1, 1
+    hp = torch.tensor([lr, b1, b2, eps, wd, 1 - b1 ** t, 1 - b2 ** t], device=dev)
+    norm_out = torch.zeros(1, device=dev)
+    skip_out = torch.zeros(1, dtype=torch.int32, device=dev)
+    gt, mt, ct = _table([g.data_ptr() for g in grads]), _table([m.data_ptr() for m in models]), \
+        _table([c.data_ptr() for c in ctrls])
+    st = _lib.stream_ptr()
+    for r in range(n):
+        _lib.check(lib.mrk_dp_reduce_scatter(gt, ct, n, r, r * per, per, flags.data_ptr(), 1, 0, 100, st), "rs")
+    grad_scale, max_norm = 1.0 / n, 0.5
+    for r in range(n):
+        _lib.check(lib.mrk_dp_adamw_allgather(mt, ct, n, r, r * per, per, grads[r].data_ptr() + 4 * r * per,
+                                              masters[r].data_ptr(), ms[r].data_ptr(), vs[r].data_ptr(),
+                                              flags.data_ptr(), hp.data_ptr(), grad_scale, max_norm, None,
+                                              norm_out.data_ptr(), skip_out.data_ptr(), 1, 0, 1, 100, st), "ag")
+    torch.cuda.synchronize()
+    assert _lib.status() == 0
+    total = torch.stack(grads_in).sum(0)
+    counted = total.clone()
+    counted[(numel // 64 - 3) * 64:] = 0
+    norm = counted.double().pow(2).sum().sqrt().item() * grad_scale
+    assert abs(norm_out.item() - norm) < 1e-4 * norm
+    assert skip_out.item() == 0
+    coef = grad_scale * (max_norm / (norm + 1e-6) if norm > max_norm else 1.0)
+    wd_vec = torch.zeros(numel, device=dev)
+    wd_vec[: (numel // 128) * 64] = wd
+    p_ref, m_ref, v_ref = _adam_ref(master_full, torch.zeros_like(total), torch.zeros_like(total), total * coef,
+                                    lr, b1, b2, eps, wd_vec, t)
+    for r in range(n):
+        sl = slice(r * per, (r + 1) * per)
+        torch.testing.assert_close(grads[r][sl], total[sl], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(masters[r], p_ref[sl], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(ms[r], m_ref[sl], rtol=1e-5, atol=1e-7)
+        torch.testing.assert_close(vs[r], v_ref[sl], rtol=1e-5, atol=1e-9)
+    for k in range(n):
+        torch.testing.assert_close(models[k].float(), p_ref.bfloat16().float(), rtol=0, atol=0)
+
+
+def test_nonfinite_gradient_skips_update():
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    numel = 64 * 8
+    grad = torch.ones(numel, device=dev)
+    grad[5] = float("inf")
+    model = torch.zeros(numel, dtype=torch.bfloat16, device=dev)
+    ctrl = torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev)
+    master = torch.ones(numel, device=dev)
+    m, v = torch.zeros(numel, device=dev), torch.zeros(numel, device=dev)
+    hp = torch.tensor([1e-2, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001], device=dev)
+    norm_out, skip_out = torch.zeros(1, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    gt, mt, ct = _table([grad.data_ptr()]), _table([model.data_ptr()]), _table([ctrl.data_ptr()])
+    st = _lib.stream_ptr()
+    _lib.check(lib.mrk_dp_reduce_scatter(gt, ct, 1, 0, 0, numel, None, 1, 0, 100, st), "rs")
+    _lib.check(lib.mrk_dp_adamw_allgather(mt, ct, 1, 0, 0, numel, grad.data_ptr(), master.data_ptr(), m.data_ptr(),
+                                          v.data_ptr(), None, hp.data_ptr(), 1.0, 1.0, None, norm_out.data_ptr(),
+                                          skip_out.data_ptr(), 1, 0, 1, 100, st), "ag")
+    torch.cuda.synchronize()
+    assert skip_out.item() == 1
+    assert torch.equal(master, torch.ones_like(master)) and torch.equal(m, torch.zeros_like(m))
+
+
+def test_barrier_wait_runs_out_and_reports():
+    """A flag that nothing sets: the bounded wait gives up, the status word says so, and the
+    context stays usable."""
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(2)]
+    ct = _table([c.data_ptr() for c in ctrls])
+    torch.cuda.synchronize()
+    _lib.status(clear=True)
+    # rank 0 signals and waits for rank 1, which never runs
+    _lib.check(lib.mrk_symm_barrier(ct, 2, 0, 3, 1, 1, 20, _lib.stream_ptr()), "barrier")
+    torch.cuda.synchronize()
+    assert _lib.status(clear=True) & 2, "the flag wait should have timed out"
+    # rank 1 arrives later: both flags are now set and the wait of rank 1 completes at once
+    _lib.check(lib.mrk_symm_barrier(ct, 2, 1, 3, 1, 1, 20, _lib.stream_ptr()), "barrier")
+    torch.cuda.synchronize()
+    assert _lib.status(clear=True) == 0
+    x = torch.ones(1024, device=dev)
+    assert float((x * 2).sum()) == 2048.0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(tmp, name, world, extra):
+    import json
+    out = os.path.join(str(tmp), name + ".json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), SCRIPT, "--out", out,
+           "--device", "cuda", "--dtype", "bf16"] + extra
+    env = dict(os.environ, MERAK_QUIET="1", NCCL_NVLS_ENABLE="0")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, "%s failed:\n%s\n%s" % (name, res.stdout[-3000:], res.stderr[-3000:])
+    with open(out) as f:
+        return json.load(f)["losses"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("model", ["gpt2", "bert"])
+def test_fused_dp_matches_nccl_two_gpus(tmp_path, model):
+    base = ["--model", model, "--dp", "2", "--steps", "6", "--gas", "2"]
+    ref = _run(tmp_path, "nccl", 2, base + ["--comm", "nccl"])
+    fused = _run(tmp_path, "fused", 2, base + ["--comm", "fused"])
+    assert fused[-1] < fused[0]
+    for a, b in zip(fused, ref):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (fused, ref)
