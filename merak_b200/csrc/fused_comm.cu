@@ -372,3 +372,65 @@ MRK_API int mrk_symm_barrier(void* const* ctrl_ptrs, int n, int rank, int which,
   MRK_CHECK_LAUNCH();
   return 0;
 }
+
+// ---- tensor parallelism: second half of GEMM -> reduce-scatter / all-reduce ------------------------
+namespace mrk {
+
+// After the GEMM kernels of all ranks have added their partial rows into the owners' fp32
+// accumulators: wait for everybody, convert this rank's rows (reduce-scatter) or all rows, pulled
+// from their owners (all-reduce), to bf16, and clear the accumulator of the previous call (nobody
+// reads or adds to it any more once this call's barrier has been passed).
+__global__ void __launch_bounds__(kDpThreads)
+tp_reduce_finish_kernel(PeerPtrs accs, PeerPtrs ctrls, int n, int rank, int all_rows, __nv_bfloat16* __restrict__ out,
+                        long long rows_out, int N, int seg_rows, float* __restrict__ zero_buf, long long zero_elems,
+                        uint32_t epoch, long long budget, unsigned* status) {
+  SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(ctrls.p[rank]);
+  if (blockIdx.x == 0) symm_signal(ctrls, n, rank, 5, epoch);
+  const bool ok = symm_wait(mine, n, 5, epoch, budget, status);
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+  if (ok) {
+    const int vec_per_row = N >> 3;
+    const long long nvec = rows_out * vec_per_row;
+    for (long long i = tid; i < nvec; i += nthr) {
+      const long long r = i / vec_per_row;
+      const int cv = (int)(i - r * vec_per_row);
+      const float* src;
+      if (all_rows) {
+        const long long s = r / seg_rows;
+        const int owner = (int)(s % n);
+        const long long local = (s / n) * seg_rows + (r - s * seg_rows);
+        src = reinterpret_cast<const float*>(accs.p[owner]) + local * N + cv * 8;
+      } else {
+        src = reinterpret_cast<const float*>(accs.p[rank]) + r * N + cv * 8;
+      }
+      const float4 a = ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src));
+      const float4 b = ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src) + 1);
+      reinterpret_cast<uint4*>(out + r * N)[cv] =
+          make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+    }
+  }
+  if (zero_buf != nullptr) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long i = tid; i < (zero_elems >> 2); i += nthr) reinterpret_cast<float4*>(zero_buf)[i] = z;
+  }
+}
+
+}  // namespace mrk
+
+MRK_API int mrk_tp_reduce_finish(void* const* acc_ptrs, void* const* ctrl_ptrs, int n, int rank, int all_rows,
+                                 void* out, long long rows_out, int N, int seg_rows, float* zero_buf,
+                                 long long zero_elems, unsigned epoch, int budget_ms, void* stream) {
+  MRK_REQUIRE(n >= 2 && n <= kSymmMaxRanks && rank >= 0 && rank < n, "tp_reduce_finish: bad group");
+  MRK_REQUIRE(N % 8 == 0 && rows_out > 0 && seg_rows > 0 && (zero_elems % 4) == 0, "tp_reduce_finish: bad shape");
+  PeerPtrs a, c;
+  fill_peers(&a, acc_ptrs, n);
+  fill_peers(&c, ctrl_ptrs, n);
+  unsigned* status = status_word_device();
+  MRK_REQUIRE(status != nullptr, "tp_reduce_finish: status word unavailable");
+  const unsigned grid = dp_grid(rows_out * (N / 8));
+  tp_reduce_finish_kernel<<<grid, kDpThreads, 0, (cudaStream_t)stream>>>(
+      a, c, n, rank, all_rows, reinterpret_cast<__nv_bfloat16*>(out), rows_out, N, seg_rows, zero_buf, zero_elems,
+      epoch, budget_cycles(budget_ms), status);
+  MRK_CHECK_LAUNCH();
+  return 0;
+}

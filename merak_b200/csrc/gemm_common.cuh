@@ -3,8 +3,35 @@
 #pragma once
 #include "gemm_tcgen05.h"
 #include "sm100_ptx.cuh"
+#include "symm.cuh"
 
 namespace mrk {
+
+// Collective fused into the GEMM (tensor parallelism over peer-mapped memory).
+//   mode 1  GEMM -> reduce-scatter: every epilogue row is added (fp32 red.add over NVLink) into the
+//           accumulator of the rank that owns the row, so partial sums travel while later tiles
+//           are still being computed.
+//   mode 2  all-gather -> GEMM: a few CTAs of the grid copy the peers' shards of A into the local
+//           gathered matrix segment by segment and publish a flag per segment; the TMA producers
+//           of the compute CTAs wait for the segments their tile covers, starting with this
+//           rank's own rows.  Each remote element crosses NVLink once.
+// Rows of the full [M, *] matrix are grouped in segments of `seg_rows`; segment s belongs to rank
+// s % n and is that rank's local segment s / n (batch-first sequence sharding).
+constexpr int kGemmMaxPeers = 8;
+struct GemmComm {
+  int mode, n, rank;
+  int seg_rows;
+  int perm;                    // start the row-block order at this rank's own segments
+  int gemm_ctas;               // mode 2: CTAs [0, gemm_ctas) compute, the others gather
+  void* peer[kGemmMaxPeers];   // mode 1: fp32 accumulators; mode 2: bf16 shards of A
+  long long ld_peer;           // row pitch of those (elements)
+  void* gathered;              // mode 2: local gathered A, row pitch ld_peer
+  uint32_t* seg_flags;         // mode 2: local, one counter per segment
+  void* ctrl[kGemmMaxPeers];   // control blocks (entry barrier of mode 2)
+  uint32_t epoch;              // barrier epoch of this call
+  uint32_t flag_target;        // mode 2: value a segment counter reaches once the segment is complete
+  long long budget;            // wait budget in SM cycles
+};
 
 struct GemmParams {
   int M, N, K;
@@ -22,7 +49,90 @@ struct GemmParams {
   unsigned* status;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
+  GemmComm comm;
 };
+
+// Row-block order under a fused collective: position i of the schedule -> row block.  Blocks are
+// visited by distance of their owner from this rank (own segments first), so every rank works on a
+// different peer's rows at any time.
+__device__ __forceinline__ int comm_perm_m(const GemmParams& p, int i, int block_m) {
+  const GemmComm& c = p.comm;
+  if (c.mode == 0 || !c.perm) return i;
+  const int blocks_per_seg = c.seg_rows / block_m;
+  const int per_owner = p.num_m_blocks / c.n;
+  const int d = i / per_owner, j = i - d * per_owner;
+  const int b = j / blocks_per_seg, w = j - b * blocks_per_seg;
+  int owner = c.rank + d;
+  if (owner >= c.n) owner -= c.n;
+  return (b * c.n + owner) * blocks_per_seg + w;
+}
+
+// mode 1: where row `row` of the full output lives (owner's accumulator, local row).
+__device__ __forceinline__ float* comm_dst_row(const GemmComm& c, long long row) {
+  const long long s = row / c.seg_rows;
+  const int owner = (int)(s % c.n);
+  const long long local = (s / c.n) * c.seg_rows + (row - s * c.seg_rows);
+  return reinterpret_cast<float*>(c.peer[owner]) + local * c.ld_peer;
+}
+
+// mode 2, TMA producer thread: waits until the segments covering rows [m0, m0 + rows) have arrived.
+__device__ __forceinline__ bool comm_wait_rows(const GemmParams& p, int m0, int rows, volatile int* abort_flag) {
+  const GemmComm& c = p.comm;
+  const int last_row = min(m0 + rows, p.M) - 1;
+  const int s0 = m0 / c.seg_rows, s1 = last_row / c.seg_rows;
+  for (int s = s0; s <= s1; ++s) {
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys_u32(c.seg_flags + s) - c.flag_target) < 0) {
+      if (*abort_flag || clock64() - t0 > c.budget) {
+        *abort_flag = 1;
+        raise_status(p.status, kStatusFlagTimeout);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");   // the copies were generic-proxy stores; TMA reads next
+  return true;
+}
+
+// mode 2, gather CTAs: copy every rank's shard into the gathered matrix, own segments first.
+__device__ __forceinline__ void comm_gather_role(const GemmParams& p) {
+  const GemmComm& c = p.comm;
+  const int g = blockIdx.x - c.gemm_ctas, G = gridDim.x - c.gemm_ctas;
+  SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(c.ctrl[c.rank]);
+  PeerPtrs ctrls;
+#pragma unroll
+  for (int k = 0; k < kGemmMaxPeers; ++k) ctrls.p[k] = c.ctrl[k];
+  // every rank has staged its shard (and is done with the previous use of its buffers)
+  if (g == 0) symm_signal(ctrls, c.n, c.rank, 4, c.epoch);
+  const bool ok = symm_wait(mine, c.n, 4, c.epoch, c.budget, p.status);
+  if (!ok) return;     // consumers time out on the segment flags and drain
+  const int num_seg = p.M / c.seg_rows;
+  const int batches = num_seg / c.n;
+  const long long seg_vecs = (long long)c.seg_rows * c.ld_peer / 8;   // uint4 = 8 bf16
+  for (int d = 0; d < c.n; ++d) {
+    int owner = c.rank + d;
+    if (owner >= c.n) owner -= c.n;
+    for (int b = 0; b < batches; ++b) {
+      const int s = b * c.n + owner;
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(c.peer[owner]) +
+                                                        (long long)b * c.seg_rows * c.ld_peer);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c.gathered) +
+                                            (long long)s * c.seg_rows * c.ld_peer);
+      const long long stride = (long long)G * blockDim.x;
+      long long i = (long long)g * blockDim.x + threadIdx.x;
+      for (; i + 3 * stride < seg_vecs; i += 4 * stride) {
+        const uint4 a0 = ld_relaxed_sys_u4(src + i), a1 = ld_relaxed_sys_u4(src + i + stride);
+        const uint4 a2 = ld_relaxed_sys_u4(src + i + 2 * stride), a3 = ld_relaxed_sys_u4(src + i + 3 * stride);
+        dst[i] = a0; dst[i + stride] = a1; dst[i + 2 * stride] = a2; dst[i + 3 * stride] = a3;
+      }
+      for (; i < seg_vecs; i += stride) dst[i] = ld_relaxed_sys_u4(src + i);
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) atomicAdd(c.seg_flags + s, 1u);
+    }
+  }
+}
 
 // erf-GELU pieces from one exponential: with e = exp(-x^2/2), the normal pdf is e/sqrt(2 pi) and
 // erf(|x|/sqrt 2) = 1 - poly(t) * e, t = 1/(1 + p |x|/sqrt 2) (Abramowitz-Stegun 7.1.26, |error| < 1.5e-7).
@@ -142,9 +252,10 @@ for (int c = 0; c < ncols / 32; ++c) {
     }
   }
   if (row_ok && split_k) {
-    // partial sum of one K range: reduce into the fp32 output
-    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
-    if (full && vec_ok) {
+    // partial sum of one K range (or, under a fused reduce-scatter, of one rank): reduce into the
+    // fp32 output, which in the second case lives on the rank that owns the row
+    float* dst = (p.comm.mode == 1 ? comm_dst_row(p.comm, row) : reinterpret_cast<float*>(p.C) + row * p.ldc) + col0;
+    if (full && (vec_ok || p.comm.mode == 1)) {
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),

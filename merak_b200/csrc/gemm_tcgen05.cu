@@ -17,6 +17,8 @@
 // Covers the GEMM call sites of the reference's Column/RowParallelLinear and lm_head
 // (Merak/core/mpu/layers.py:252,354) plus the bias/GELU/residual elementwise passes that
 // follow them there.
+#include <string.h>
+
 #include "gemm_common.cuh"
 #include "host_common.h"
 
@@ -61,6 +63,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
   const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
 
+  // fused all-gather: the CTAs behind the compute CTAs only move the peers' shards of A
+  if (p.comm.mode == 2 && (int)blockIdx.x >= p.comm.gemm_ctas) {
+    comm_gather_role(p);
+    return;
+  }
+  const int cta_stride = p.comm.mode == 2 ? p.comm.gemm_ctas : (int)gridDim.x;
+
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -92,12 +101,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += cta_stride) {
         int m_blk, n_blk;
         tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        m_blk = comm_perm_m(p, m_blk, kBlockM);
         const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
         const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        if (p.comm.mode == 2) {
+          ok = comm_wait_rows(p, m0, kBlockM, abort_flag);
+          if (!ok) break;
+        }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
           if (!ok) break;
@@ -132,7 +146,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++iter) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += cta_stride, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, p.status);
@@ -165,10 +179,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int row_in_tile = quad * 32 + lane;
     int iter = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++iter) {
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += cta_stride, ++iter) {
       int m_blk, n_blk;
       tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
-      const bool split_k = p.num_splits > 1;
+      m_blk = comm_perm_m(p, m_blk, kBlockM);
+      const bool split_k = p.num_splits > 1 || p.comm.mode == 1;
       const bool first_split = (unit % p.num_splits) == 0;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
@@ -226,7 +241,17 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
   p.kb_per_split = (p.num_k_blocks + p.num_splits - 1) / p.num_splits;
   p.num_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   const int units = tiles * p.num_splits;
-  const int grid = units < sm_count() ? units : sm_count();
+  int grid = units < sm_count() ? units : sm_count();
+  if (p.comm.mode == 2) {
+    // compute CTAs + gather CTAs, all resident at once (one CTA per SM): the former wait for the latter
+    const int gather = p.comm.gemm_ctas;     // the caller passes the number of gather CTAs here
+    MRK_REQUIRE(gather >= 1 && gather < sm_count(), "gemm: bad number of gather CTAs");
+    const int room = sm_count() - gather;
+    p.comm.gemm_ctas = units < room ? units : room;
+    grid = p.comm.gemm_ctas + gather;
+  }
+  if (p.comm.mode != 0 && p.comm.perm)
+    p.comm.perm = (p.comm.seg_rows % kBlockM == 0 && p.num_m_blocks % p.comm.n == 0 && p.M % kBlockM == 0) ? 1 : 0;
   gemm_bf16_kernel<BN><<<grid, kNumThreads, L::kTotal, stream>>>(ta, tb, p);
   MRK_CHECK_LAUNCH();
   return 0;
@@ -238,18 +263,19 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p
 
 using namespace mrk;
 
-MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                          long long ldb, long long ldc, const void* bias, const void* aux_in,
-                          long long ld_aux_in, void* aux_out, long long ld_aux_out, int act, int aux_mode,
-                          int flags, float alpha, int block_n, void* stream) {
+static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                      long long ldb, long long ldc, const void* bias, const void* aux_in,
+                      long long ld_aux_in, void* aux_out, long long ld_aux_out, int act, int aux_mode,
+                      int flags, float alpha, int block_n, const GemmComm* comm, void* stream) {
   MRK_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %dx%dx%d", M, N, K);
-  MRK_REQUIRE(A && B && C, "gemm: null operand");
+  MRK_REQUIRE(A && B && (C || (comm && comm->mode == 1)), "gemm: null operand");
   MRK_REQUIRE(aux_mode == MRK_AUX_NONE || aux_in != nullptr, "gemm: aux_mode set without aux_in");
   const bool a_mn = flags & MRK_GEMM_A_MN, b_mn = flags & MRK_GEMM_B_MN;
   int bn = block_n;
   // block_n: 0 = choose; 64/128/256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel
   // (256 x 256 tile per 2-CTA cluster).  The pair kernel is the default for anything wide enough.
-  if (bn == 0 && M > 128 && N > 128) bn = 512;
+  if (bn == 0 && M > 128 && N > 128 && comm == nullptr) bn = 512;
+  if (comm != nullptr && bn == 512) bn = 256;     // the fused collectives live in the single-CTA kernel
   if (bn == 0) {
     // Heuristic: widest tile that still fills the SMs reasonably; narrow tiles for small N.
     const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
@@ -269,6 +295,8 @@ MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   else       rc = make_tmap_2d(&tb, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, kBlockK, 3);
   if (rc) return rc;
   GemmParams p;
+  memset(&p.comm, 0, sizeof(p.comm));
+  if (comm != nullptr) p.comm = *comm;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
   p.bias = bias;
@@ -282,4 +310,62 @@ MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   if (bn == 256) return launch<256>(ta, tb, p, s);
   if (bn == 128) return launch<128>(ta, tb, p, s);
   return launch<64>(ta, tb, p, s);
+}
+
+MRK_API int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, const void* bias, const void* aux_in,
+                          long long ld_aux_in, void* aux_out, long long ld_aux_out, int act, int aux_mode,
+                          int flags, float alpha, int block_n, void* stream) {
+  return gemm_entry(A, B, C, M, N, K, lda, ldb, ldc, bias, aux_in, ld_aux_in, aux_out, ld_aux_out, act, aux_mode,
+                    flags, alpha, block_n, nullptr, stream);
+}
+
+static int fill_comm(GemmComm* c, int mode, int n, int rank, int seg_rows, void* const* peers, long long ld_peer,
+                     void* const* ctrls, unsigned epoch, int budget_ms, int M) {
+  MRK_REQUIRE(n >= 2 && n <= kGemmMaxPeers && rank >= 0 && rank < n, "gemm: tensor-parallel group of %d ranks", n);
+  MRK_REQUIRE(seg_rows > 0 && M % seg_rows == 0 && (M / seg_rows) % n == 0,
+              "gemm: %d rows do not split into segments of %d over %d ranks", M, seg_rows, n);
+  memset(c, 0, sizeof(*c));
+  c->mode = mode; c->n = n; c->rank = rank; c->seg_rows = seg_rows; c->perm = 1;
+  for (int k = 0; k < n; ++k) {
+    c->peer[k] = peers[k];
+    c->ctrl[k] = ctrls ? ctrls[k] : nullptr;
+  }
+  c->ld_peer = ld_peer;
+  c->epoch = epoch;
+  c->budget = (long long)(budget_ms > 0 ? budget_ms : 2000) * 2000000ll;
+  return 0;
+}
+
+// GEMM -> reduce-scatter.  partial = A[M,K] * W[N,K]^T (+ bias on the rank that passes one); row r of
+// it is added into the fp32 accumulator ([M/n, N], pitch N) of the rank that owns r.
+MRK_API int mrk_gemm_bf16_rs(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                             const void* bias, int flags, float alpha, void* const* peer_acc, int n, int rank,
+                             int seg_rows, void* stream) {
+  MRK_REQUIRE((N % 32) == 0, "gemm_rs: N must be a multiple of 32");
+  GemmComm c;
+  int rc = fill_comm(&c, 1, n, rank, seg_rows, peer_acc, N, nullptr, 0, 0, M);
+  if (rc) return rc;
+  return gemm_entry(A, B, nullptr, M, N, K, lda, ldb, N, bias, nullptr, 0, nullptr, 0, MRK_ACT_NONE, MRK_AUX_NONE,
+                    (flags & ~MRK_GEMM_ACCUMULATE) | MRK_GEMM_OUT_F32, alpha, 0, &c, stream);
+}
+
+// all-gather -> GEMM.  `gathered` ([M, K] bf16, pitch K, local) is filled from every rank's shard
+// ([M/n, K], pitch K, peer-mapped) while C = act(gathered * W^T + bias) is computed.
+MRK_API int mrk_gemm_bf16_ag(void* gathered, void* const* peer_shards, const void* B, void* C, int M, int N, int K,
+                             long long ldb, long long ldc, const void* bias, void* aux_out, long long ld_aux_out,
+                             int act, int flags, float alpha, void* const* ctrls, unsigned* seg_flags,
+                             unsigned flag_target, int gather_ctas, int n, int rank, int seg_rows, unsigned epoch,
+                             int budget_ms, void* stream) {
+  MRK_REQUIRE((K % 8) == 0 && ((uintptr_t)gathered & 15) == 0, "gemm_ag: K must be a multiple of 8");
+  MRK_REQUIRE(!(flags & MRK_GEMM_A_MN), "gemm_ag: A must be [M, K]");
+  GemmComm c;
+  int rc = fill_comm(&c, 2, n, rank, seg_rows, peer_shards, K, ctrls, epoch, budget_ms, M);
+  if (rc) return rc;
+  c.gathered = gathered;
+  c.seg_flags = seg_flags;
+  c.flag_target = flag_target;
+  c.gemm_ctas = gather_ctas;
+  return gemm_entry(gathered, B, C, M, N, K, K, ldb, ldc, bias, nullptr, 0, aux_out, ld_aux_out, act, MRK_AUX_NONE,
+                    flags, alpha, 0, &c, stream);
 }

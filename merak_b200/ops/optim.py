@@ -79,6 +79,21 @@ class FusedAdamW:
         self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.param_groups = [{"lr": lr, "betas": betas, "eps": eps, "weight_decay": weight_decay}]
+        # single-launch update (bf16 model, fp32 gradients): per-granule weight-decay flags + the
+        # shard-update kernel of the fused data-parallel path run as a group of one rank
+        self._one_launch = None
+        if (dev.type == "cuda" and flat.model.dtype == torch.bfloat16 and flat.grad.dtype == torch.float32
+                and n % 8 == 0 and self.start % 64 == 0):
+            import ctypes
+            import numpy as np
+            fl = np.zeros(flat.numel // 64 + 1, dtype=np.uint8)
+            for s, e, decay in self.segments:
+                if decay:
+                    fl[s // 64:(e + 63) // 64] = 1
+            ctrl = torch.zeros(int(_lib.kernels().mrk_symm_ctrl_bytes()), dtype=torch.uint8, device=dev)
+            self._one_launch = {"flags": torch.from_numpy(fl).to(dev), "ctrl": ctrl,
+                                "models": (ctypes.c_void_p * 1)(flat.model.data_ptr()),
+                                "ctrls": (ctypes.c_void_p * 1)(ctrl.data_ptr())}
 
     def _segments(self, decay_mask):
         flat = self.flat
@@ -127,7 +142,15 @@ class FusedAdamW:
         if sumsq is None:
             sumsq = self.grad_sumsq()
         g = self.flat.grad
-        if g.is_cuda:
+        if g.is_cuda and self._one_launch is not None:
+            ol = self._one_launch
+            hp = self._hp_tensor(self.weight_decay)
+            _lib.check(_lib.kernels().mrk_dp_adamw_allgather(
+                ol["models"], ol["ctrls"], 1, 0, self.start, self.end - self.start, g.data_ptr() + 4 * self.start,
+                self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), ol["flags"].data_ptr(),
+                hp.data_ptr(), float(grad_scale), float(self.max_grad_norm), sumsq.data_ptr(), self._norm.data_ptr(),
+                self._skip.data_ptr(), 0, 0, 0, 0, _lib.stream_ptr()), "mrk_dp_adamw_allgather")
+        elif g.is_cuda:
             lib = _lib.kernels()
             st = _lib.stream_ptr()
             _lib.check(lib.mrk_clip_coef(sumsq.data_ptr(), float(grad_scale), float(self.max_grad_norm),

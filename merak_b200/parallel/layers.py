@@ -22,8 +22,20 @@ import torch.nn.functional as F
 
 from ..ops.elementwise import embedding_sum
 from ..ops.linear import linear as k_linear
+from . import fused_tp
 from . import mappings as M
 from . import mpu
+
+
+def _fused_comm(x, weight, sequence_parallel, seq_dim, input_sharded):
+    """The fused-collective data plane of the tensor-parallel group, or None when this call has to
+    use torch.distributed collectives (CPU, other dtypes or layouts, peer mapping unavailable)."""
+    if not fused_tp.ENABLED or not x.is_cuda:
+        return None
+    n = mpu.get_model_parallel_world_size()
+    if n == 1 or not fused_tp.usable(x, weight, n, sequence_parallel, seq_dim, input_sharded):
+        return None
+    return fused_tp.get_comm(mpu.get_model_parallel_group(), x.device)
 
 
 def divide(a: int, b: int) -> int:
@@ -106,6 +118,11 @@ class ColumnParallelLinear(nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, x):
+        comm = None if self.gather_output else _fused_comm(x, self.weight, self.sequence_parallel, self.seq_dim, True)
+        if comm is not None:
+            b = None if self.skip_bias_add else self.bias
+            y = fused_tp.column_linear_fused(x, self.weight, b, comm, self.sequence_parallel)
+            return (y, self.bias) if self.skip_bias_add else y
         if self.sequence_parallel:
             x = M.gather_from_sequence_parallel_region(x, self.seq_dim, True)
         else:
@@ -148,12 +165,19 @@ class RowParallelLinear(nn.Module):
         self.weight.partition_dim = 1
         if bias:
             self.bias = nn.Parameter(torch.zeros(output_size, dtype=params_dtype, device=dev))
+            if self.sequence_parallel:
+                self.bias.sequence_parallel = True     # sees this rank's tokens only: summed over the group
         else:
             self.register_parameter("bias", None)
 
     def forward(self, x):
         if not self.input_is_parallel:
             x = M.scatter_to_model_parallel_region(x)
+        comm = _fused_comm(x, self.weight, self.sequence_parallel, self.seq_dim, False)
+        if comm is not None:
+            b = None if self.skip_bias_add else self.bias
+            y = fused_tp.row_linear_fused(x, self.weight, b, comm, self.sequence_parallel)
+            return (y, self.bias) if self.skip_bias_add else y
         y = k_linear(x, self.weight, None)
         if self.sequence_parallel:
             y = M.reduce_scatter_to_sequence_parallel_region(y, self.seq_dim)

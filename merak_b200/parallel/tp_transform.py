@@ -130,6 +130,9 @@ class RowPara(nn.Module):
             if linear.bias is not None:
                 self.row_linear.bias = nn.Parameter(linear.bias.data.clone())
         self.row_linear.weight.model_parallel, self.row_linear.weight.partition_dim = True, 1
+        if self.row_linear.bias is not None and self.row_linear.sequence_parallel:
+            # added to this rank's sequence shard only: its gradient is summed over the group
+            self.row_linear.bias.sequence_parallel = True
 
     def forward(self, x, residual=None):
         y = self.row_linear(x)
@@ -194,20 +197,45 @@ def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, me
     return replaced
 
 
+def _scatter_output_hook(seq_dim: int):
+    def hook(module, inputs, output):
+        return M.scatter_to_sequence_parallel_region(output, seq_dim)
+    return hook
+
+
 def _enter_sequence_parallel(model: nn.Module, seq_dim: int):
+    """Starts the sequence-parallel region after the input embeddings.  A single token embedding
+    (Llama) is wrapped; where several embeddings are summed first (GPT-2: ``wte + wpe`` then ``drop``;
+    BERT: the ``embeddings`` block with its own LayerNorm) the output of that last module is
+    scattered by a forward hook, which keeps every parameter name.  Norms computed before the
+    scatter see the whole sequence on every rank and are therefore not marked sequence-parallel."""
     emb_owner, emb_name = _find_input_embedding(model)
+    full_sequence_params = set()
     if emb_owner is not None:
-        setattr(emb_owner, emb_name, _SeqScatter(getattr(emb_owner, emb_name), seq_dim))
+        if hasattr(emb_owner, "wpe") and isinstance(getattr(emb_owner, "drop", None), nn.Module):
+            emb_owner.drop.register_forward_hook(_scatter_output_hook(seq_dim))
+        elif type(emb_owner).__name__.endswith("Embeddings"):
+            emb_owner.register_forward_hook(_scatter_output_hook(seq_dim))
+            full_sequence_params = {id(p) for p in emb_owner.parameters()}
+        else:
+            setattr(emb_owner, emb_name, _SeqScatter(getattr(emb_owner, emb_name), seq_dim))
     for m in model.modules():
         if isinstance(m, nn.LayerNorm) or type(m).__name__.endswith("RMSNorm"):
             for p in m.parameters():
-                p.sequence_parallel = True
+                if id(p) not in full_sequence_params:
+                    p.sequence_parallel = True
     head = _find_output_projection(model)
     if head is not None:
         owner, name = head
         lin = getattr(owner, name)
         if isinstance(lin, nn.Linear):
             setattr(owner, name, _GatherThenLinear(lin, seq_dim))
+            # other replicated layers of the same head (BERT's transform) still run on this rank's
+            # tokens only: their gradients are summed over the group like the norms'
+            proj = {id(p) for p in lin.parameters()}
+            for p in owner.parameters():
+                if id(p) not in proj and not getattr(p, "model_parallel", False):
+                    p.sequence_parallel = True
 
 
 class _GatherThenLinear(nn.Module):

@@ -62,6 +62,8 @@ class PipelineModule(nn.Module):
         if args.params_dtype is not None and args.params_dtype != torch.float32 and model is not None:
             model.to(args.params_dtype)
         tp = mpu.get_model_parallel_world_size()
+        from ..parallel import fused_tp
+        fused_tp.ENABLED = getattr(args, "comm_mode", "fused") == "fused"
         if tp > 1 and model is not None:
             apply_tensor_parallel(model, megatron_sp=getattr(args, "megatron_sequence_parallel", False),
                                   seq_dim=args.sequence_dim, vocab_parallel=args.parallel_vocab)

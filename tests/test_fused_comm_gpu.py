@@ -160,3 +160,98 @@ def test_fused_dp_matches_nccl_two_gpus(tmp_path, model):
     assert fused[-1] < fused[0]
     for a, b in zip(fused, ref):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (fused, ref)
+
+
+# ---- tensor-parallel fused GEMMs, ranks emulated on one GPU --------------------------------------
+def _preset_flags(ctrls, which, epoch):
+    """Marks barrier `which` as already reached by every source (the emulated ranks run one after
+    the other, so nobody could signal in time)."""
+    for c in ctrls:
+        c.view(torch.int32)[which * 16: which * 16 + 16] = epoch
+
+
+@pytest.mark.parametrize("n,B,seg,Kl,N,b_mn", [(2, 2, 128, 256, 512, False), (4, 1, 256, 128, 256, True),
+                                               (2, 3, 64, 96, 160, False)])
+def test_gemm_reduce_scatter_emulated(n, B, seg, Kl, N, b_mn):
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    L = seg * n
+    M = B * L
+    xs = [torch.randn(M, Kl, device=dev, dtype=torch.bfloat16) * 0.5 for _ in range(n)]
+    ws = [torch.randn(N, Kl, device=dev, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
+    wk = [w.t().contiguous() if b_mn else w for w in ws]
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    accs = [torch.zeros(M // n * N, device=dev) for _ in range(n)]
+    ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(n)]
+    at, ct = _table([a.data_ptr() for a in accs]), _table([c.data_ptr() for c in ctrls])
+    st = _lib.stream_ptr()
+    for r in range(n):
+        _lib.check(lib.mrk_gemm_bf16_rs(xs[r].data_ptr(), wk[r].data_ptr(), M, N, Kl, Kl, wk[r].stride(0),
+                                        bias.data_ptr() if r == 0 else None, 16 if b_mn else 0, 1.0, at, n, r, seg,
+                                        st), "rs")
+    _preset_flags(ctrls, 5, 1)
+    ref = sum(x.float() @ w.float().t() for x, w in zip(xs, ws)) + bias.float()
+    ref3 = ref.view(B, n, seg, N)
+    outs_rs, outs_ar = [], []
+    for r in range(n):
+        o = torch.empty(M // n, N, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.mrk_tp_reduce_finish(at, ct, n, r, 0, o.data_ptr(), M // n, N, seg, None, 0, 1, 50, st), "fin")
+        outs_rs.append(o)
+        o2 = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.mrk_tp_reduce_finish(at, ct, n, r, 1, o2.data_ptr(), M, N, seg, None, 0, 1, 50, st), "fin")
+        outs_ar.append(o2)
+    torch.cuda.synchronize()
+    assert _lib.status() == 0
+    for r in range(n):
+        torch.testing.assert_close(outs_rs[r].float().view(B, seg, N), ref3[:, r], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(outs_ar[r].float(), ref, rtol=2e-2, atol=2e-2)
+    # clearing an accumulator
+    z = torch.ones(1024, device=dev)
+    o = torch.empty(M // n, N, dtype=torch.bfloat16, device=dev)
+    _lib.check(lib.mrk_tp_reduce_finish(at, ct, n, 0, 0, o.data_ptr(), M // n, N, seg, z.data_ptr(), 1024, 1, 50, st), "fin")
+    torch.cuda.synchronize()
+    assert float(z.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("n,B,seg,K,N", [(2, 2, 128, 256, 512), (4, 1, 256, 128, 384), (2, 1, 64, 64, 96)])
+def test_allgather_gemm_emulated(n, B, seg, K, N):
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    torch.manual_seed(1)
+    L = seg * n
+    M = B * L
+    x = torch.randn(B, L, K, device=dev, dtype=torch.bfloat16)
+    shards = [x[:, r * seg:(r + 1) * seg].contiguous().view(-1, K) for r in range(n)]
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(n)]
+    _preset_flags(ctrls, 4, 1)
+    stt, ct = _table([s.data_ptr() for s in shards]), _table([c.data_ptr() for c in ctrls])
+    ref = x.view(M, K).float() @ w.float().t() + bias.float()
+    G = 4
+    for r in range(n):
+        flags = torch.zeros(M // seg, dtype=torch.int32, device=dev)
+        gathered = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.mrk_gemm_bf16_ag(gathered.data_ptr(), stt, w.data_ptr(), y.data_ptr(), M, N, K, K, N,
+                                        bias.data_ptr(), None, 0, 0, 0, 1.0, ct, flags.data_ptr(), G, G, n, r, seg,
+                                        1, 200, _lib.stream_ptr()), "ag")
+        torch.cuda.synchronize()
+        assert _lib.status() == 0
+        assert torch.equal(gathered, x.view(M, K))
+        assert int(flags.min()) == G and int(flags.max()) == G
+        torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("sp", [0, 1])
+def test_fused_tp_matches_nccl_two_gpus(tmp_path, sp):
+    base = ["--model", "gpt2", "--tp", "2", "--steps", "6", "--gas", "2", "--megatron_sp", str(sp)]
+    ref = _run(tmp_path, "nccl", 2, base + ["--comm", "nccl"])
+    fused = _run(tmp_path, "fused", 2, base + ["--comm", "fused"])
+    assert fused[-1] < fused[0]
+    for a, b in zip(fused, ref):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (fused, ref)

@@ -76,6 +76,14 @@ def test_tp2_vocab_parallel_and_sequence_parallel(tmp_path, baseline):
     assert_close(got, baseline["llama"])
 
 
+@pytest.mark.parametrize("model", ["gpt2", "bert"])
+def test_tp2_megatron_sequence_parallel_with_biases(tmp_path, baseline, model):
+    """Summed input embeddings (GPT-2), an embedding block with its own norm and a head transform
+    (BERT), and row-parallel biases all sit at the edges of the sequence-parallel region."""
+    got = run_layout(tmp_path, "tp2_sp_" + model, 2, ["--tp", "2", "--model", model, "--megatron_sp", "1"])
+    assert_close(got, baseline[model])
+
+
 def test_pp2_tp2_recompute_4ranks(tmp_path, baseline):
     got = run_layout(tmp_path, "pp2tp2", 4, ["--pp", "2", "--tp", "2", "--recompute", "1"])
     assert_close(got, baseline["gpt2"])
