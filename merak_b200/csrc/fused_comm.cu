@@ -373,64 +373,127 @@ MRK_API int mrk_symm_barrier(void* const* ctrl_ptrs, int n, int rank, int which,
   return 0;
 }
 
-// ---- tensor parallelism: second half of GEMM -> reduce-scatter / all-reduce ------------------------
+// ---- tensor parallelism: GEMM -> reduce-scatter / all-reduce, pull side ---------------------------
 namespace mrk {
 
-// After the GEMM kernels of all ranks have added their partial rows into the owners' fp32
-// accumulators: wait for everybody, convert this rank's rows (reduce-scatter) or all rows, pulled
-// from their owners (all-reduce), to bf16, and clear the accumulator of the previous call (nobody
-// reads or adds to it any more once this call's barrier has been passed).
+// Every rank's GEMM has written its partial product [M, N] (bf16) into its peer-mapped buffer.  This
+// rank owns the rows of its sequence segments: it pulls those rows of every rank's partial
+// (coalesced 16-byte peer loads), sums them in fp32 and stores bf16.  Local row r is global row
+// ((r / seg_rows) * n + rank) * seg_rows + r % seg_rows.
+template <int N_RANKS>
 __global__ void __launch_bounds__(kDpThreads)
-tp_reduce_finish_kernel(PeerPtrs accs, PeerPtrs ctrls, int n, int rank, int all_rows, __nv_bfloat16* __restrict__ out,
-                        long long rows_out, int N, int seg_rows, float* __restrict__ zero_buf, long long zero_elems,
-                        uint32_t epoch, long long budget, unsigned* status) {
+tp_reduce_pull_kernel(PeerPtrs parts, PeerPtrs ctrls, int n_rt, int rank, __nv_bfloat16* __restrict__ out,
+                      long long rows_local, int N, int seg_rows, const __nv_bfloat16* __restrict__ bias,
+                      uint32_t epoch, int sync, long long budget, unsigned* status) {
+  const int n = N_RANKS > 0 ? N_RANKS : n_rt;
   SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(ctrls.p[rank]);
-  if (blockIdx.x == 0) symm_signal(ctrls, n, rank, 5, epoch);
-  const bool ok = symm_wait(mine, n, 5, epoch, budget, status);
-  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
-  if (ok) {
-    const int vec_per_row = N >> 3;
-    const long long nvec = rows_out * vec_per_row;
-    for (long long i = tid; i < nvec; i += nthr) {
-      const long long r = i / vec_per_row;
-      const int cv = (int)(i - r * vec_per_row);
-      const float* src;
-      if (all_rows) {
-        const long long s = r / seg_rows;
-        const int owner = (int)(s % n);
-        const long long local = (s / n) * seg_rows + (r - s * seg_rows);
-        src = reinterpret_cast<const float*>(accs.p[owner]) + local * N + cv * 8;
-      } else {
-        src = reinterpret_cast<const float*>(accs.p[rank]) + r * N + cv * 8;
-      }
-      const float4 a = ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src));
-      const float4 b = ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src) + 1);
-      reinterpret_cast<uint4*>(out + r * N)[cv] =
-          make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
-    }
+  bool ok = true;
+  if (sync) {
+    if (blockIdx.x == 0) symm_signal(ctrls, n, rank, 5, epoch);
+    ok = symm_wait(mine, n, 5, epoch, budget, status);
   }
-  if (zero_buf != nullptr) {
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (long long i = tid; i < (zero_elems >> 2); i += nthr) reinterpret_cast<float4*>(zero_buf)[i] = z;
+  if (!ok) return;
+  const int vec_per_row = N >> 3;
+  const long long nvec = rows_local * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int cv = (int)(i - r * vec_per_row);
+    const long long b = r / seg_rows;
+    const long long grow = (b * n + rank) * seg_rows + (r - b * seg_rows);
+    uint4 part[N_RANKS > 0 ? N_RANKS : kSymmMaxRanks];
+#pragma unroll
+    for (int k = 0; k < (N_RANKS > 0 ? N_RANKS : kSymmMaxRanks); ++k)
+      if (k < n) part[k] = ld_relaxed_sys_u4(reinterpret_cast<const uint4*>(
+                     reinterpret_cast<const __nv_bfloat16*>(parts.p[k]) + grow * N) + cv);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (bias != nullptr) {
+      const uint4 bb = __ldg(reinterpret_cast<const uint4*>(bias) + cv);
+      const uint32_t w[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] = f.x; acc[2 * e + 1] = f.y; }
+    }
+#pragma unroll
+    for (int k = 0; k < (N_RANKS > 0 ? N_RANKS : kSymmMaxRanks); ++k) {
+      if (k < n) {
+        const uint32_t w[4] = {part[k].x, part[k].y, part[k].z, part[k].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+      }
+    }
+    reinterpret_cast<uint4*>(out + r * N)[cv] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                           pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+// All-reduce = the pull above into a peer-mapped "reduced" buffer, then every rank pulls the other
+// ranks' reduced rows: out[row] for all M rows.
+__global__ void __launch_bounds__(kDpThreads)
+tp_gather_rows_kernel(PeerPtrs reds, PeerPtrs ctrls, int n, int rank, __nv_bfloat16* __restrict__ out, long long M,
+                      int N, int seg_rows, uint32_t epoch, int sync, long long budget, unsigned* status) {
+  SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(ctrls.p[rank]);
+  bool ok = true;
+  if (sync) {
+    if (blockIdx.x == 0) symm_signal(ctrls, n, rank, 6, epoch);
+    ok = symm_wait(mine, n, 6, epoch, budget, status);
+  }
+  if (!ok) return;
+  const int vec_per_row = N >> 3;
+  const long long nvec = M * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int cv = (int)(i - r * vec_per_row);
+    const long long s = r / seg_rows;
+    const int owner = (int)(s % n);
+    const long long local = (s / n) * seg_rows + (r - s * seg_rows);
+    reinterpret_cast<uint4*>(out + r * N)[cv] = ld_relaxed_sys_u4(
+        reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(reds.p[owner]) + local * N) + cv);
   }
 }
 
 }  // namespace mrk
 
-MRK_API int mrk_tp_reduce_finish(void* const* acc_ptrs, void* const* ctrl_ptrs, int n, int rank, int all_rows,
-                                 void* out, long long rows_out, int N, int seg_rows, float* zero_buf,
-                                 long long zero_elems, unsigned epoch, int budget_ms, void* stream) {
-  MRK_REQUIRE(n >= 2 && n <= kSymmMaxRanks && rank >= 0 && rank < n, "tp_reduce_finish: bad group");
-  MRK_REQUIRE(N % 8 == 0 && rows_out > 0 && seg_rows > 0 && (zero_elems % 4) == 0, "tp_reduce_finish: bad shape");
+MRK_API int mrk_tp_reduce_pull(void* const* part_ptrs, void* const* ctrl_ptrs, int n, int rank, void* out,
+                               long long rows_local, int N, int seg_rows, const void* bias, unsigned epoch, int sync,
+                               int budget_ms, void* stream) {
+  MRK_REQUIRE(n >= 2 && n <= kSymmMaxRanks && rank >= 0 && rank < n, "tp_reduce_pull: bad group");
+  MRK_REQUIRE(N % 8 == 0 && rows_local > 0 && seg_rows > 0 && rows_local % seg_rows == 0, "tp_reduce_pull: bad shape");
   PeerPtrs a, c;
-  fill_peers(&a, acc_ptrs, n);
+  fill_peers(&a, part_ptrs, n);
   fill_peers(&c, ctrl_ptrs, n);
   unsigned* status = status_word_device();
-  MRK_REQUIRE(status != nullptr, "tp_reduce_finish: status word unavailable");
-  const unsigned grid = dp_grid(rows_out * (N / 8));
-  tp_reduce_finish_kernel<<<grid, kDpThreads, 0, (cudaStream_t)stream>>>(
-      a, c, n, rank, all_rows, reinterpret_cast<__nv_bfloat16*>(out), rows_out, N, seg_rows, zero_buf, zero_elems,
-      epoch, budget_cycles(budget_ms), status);
+  MRK_REQUIRE(status != nullptr, "tp_reduce_pull: status word unavailable");
+  const unsigned grid = dp_grid(rows_local * (N / 8));
+  const long long b = budget_cycles(budget_ms);
+  cudaStream_t s = (cudaStream_t)stream;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  const __nv_bfloat16* bi = reinterpret_cast<const __nv_bfloat16*>(bias);
+#define MRK_PULL(NN) tp_reduce_pull_kernel<NN><<<grid, kDpThreads, 0, s>>>(a, c, n, rank, o, rows_local, N, seg_rows, bi, epoch, sync, b, status)
+  switch (n) {
+    case 2: MRK_PULL(2); break;
+    case 4: MRK_PULL(4); break;
+    case 8: MRK_PULL(8); break;
+    default: MRK_PULL(0); break;
+  }
+#undef MRK_PULL
+  MRK_CHECK_LAUNCH();
+  return 0;
+}
+
+MRK_API int mrk_tp_gather_rows(void* const* red_ptrs, void* const* ctrl_ptrs, int n, int rank, void* out, long long M,
+                               int N, int seg_rows, unsigned epoch, int sync, int budget_ms, void* stream) {
+  MRK_REQUIRE(n >= 2 && n <= kSymmMaxRanks && rank >= 0 && rank < n, "tp_gather_rows: bad group");
+  MRK_REQUIRE(N % 8 == 0 && M > 0 && seg_rows > 0, "tp_gather_rows: bad shape");
+  PeerPtrs a, c;
+  fill_peers(&a, red_ptrs, n);
+  fill_peers(&c, ctrl_ptrs, n);
+  unsigned* status = status_word_device();
+  MRK_REQUIRE(status != nullptr, "tp_gather_rows: status word unavailable");
+  tp_gather_rows_kernel<<<dp_grid(M * (N / 8)), kDpThreads, 0, (cudaStream_t)stream>>>(
+      a, c, n, rank, reinterpret_cast<__nv_bfloat16*>(out), M, N, seg_rows, epoch, sync, budget_cycles(budget_ms), status);
   MRK_CHECK_LAUNCH();
   return 0;
 }

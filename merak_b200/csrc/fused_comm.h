@@ -23,9 +23,10 @@ int mrk_dp_norm_gather(void* const* ctrl_ptrs, int n, int rank, float* out2, uns
                        void* stream);
 int mrk_symm_barrier(void* const* ctrl_ptrs, int n, int rank, int which, unsigned epoch, int signal, int budget_ms,
                      void* stream);
-int mrk_tp_reduce_finish(void* const* acc_ptrs, void* const* ctrl_ptrs, int n, int rank, int all_rows, void* out,
-                         long long rows_out, int N, int seg_rows, float* zero_buf, long long zero_elems,
-                         unsigned epoch, int budget_ms, void* stream);
+int mrk_tp_reduce_pull(void* const* part_ptrs, void* const* ctrl_ptrs, int n, int rank, void* out, long long rows_local,
+                       int N, int seg_rows, const void* bias, unsigned epoch, int sync, int budget_ms, void* stream);
+int mrk_tp_gather_rows(void* const* red_ptrs, void* const* ctrl_ptrs, int n, int rank, void* out, long long M, int N,
+                       int seg_rows, unsigned epoch, int sync, int budget_ms, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -8,13 +8,13 @@
 namespace mrk {
 
 // Collective fused into the GEMM (tensor parallelism over peer-mapped memory).
-//   mode 1  GEMM -> reduce-scatter: every epilogue row is added (fp32 red.add over NVLink) into the
-//           accumulator of the rank that owns the row, so partial sums travel while later tiles
-//           are still being computed.
-//   mode 2  all-gather -> GEMM: a few CTAs of the grid copy the peers' shards of A into the local
-//           gathered matrix segment by segment and publish a flag per segment; the TMA producers
-//           of the compute CTAs wait for the segments their tile covers, starting with this
-//           rank's own rows.  Each remote element crosses NVLink once.
+//   mode 2  all-gather -> GEMM: a few CTAs of the grid stream the peers' shards of A into the local
+//           gathered matrix (bulk async copies peer -> shared -> local, many in flight) segment by
+//           segment and publish a counter per segment; the TMA producers of the compute CTAs wait
+//           for the segments their tile covers, starting with this rank's own rows.  Each remote
+//           element crosses NVLink once.
+//   (mode 1 is reserved: GEMM -> reduce-scatter runs as a plain GEMM into a peer-mapped partial
+//   buffer followed by the pull-and-sum kernel in fused_comm.cu.)
 // Rows of the full [M, *] matrix are grouped in segments of `seg_rows`; segment s belongs to rank
 // s % n and is that rank's local segment s / n (batch-first sequence sharding).
 constexpr int kGemmMaxPeers = 8;
@@ -23,7 +23,7 @@ struct GemmComm {
   int seg_rows;
   int perm;                    // start the row-block order at this rank's own segments
   int gemm_ctas;               // mode 2: CTAs [0, gemm_ctas) compute, the others gather
-  void* peer[kGemmMaxPeers];   // mode 1: fp32 accumulators; mode 2: bf16 shards of A
+  void* peer[kGemmMaxPeers];   // bf16 shards of A, one per rank
   long long ld_peer;           // row pitch of those (elements)
   void* gathered;              // mode 2: local gathered A, row pitch ld_peer
   uint32_t* seg_flags;         // mode 2: local, one counter per segment
@@ -67,14 +67,6 @@ __device__ __forceinline__ int comm_perm_m(const GemmParams& p, int i, int block
   return (b * c.n + owner) * blocks_per_seg + w;
 }
 
-// mode 1: where row `row` of the full output lives (owner's accumulator, local row).
-__device__ __forceinline__ float* comm_dst_row(const GemmComm& c, long long row) {
-  const long long s = row / c.seg_rows;
-  const int owner = (int)(s % c.n);
-  const long long local = (s / c.n) * c.seg_rows + (row - s * c.seg_rows);
-  return reinterpret_cast<float*>(c.peer[owner]) + local * c.ld_peer;
-}
-
 // mode 2, TMA producer thread: waits until the segments covering rows [m0, m0 + rows) have arrived.
 __device__ __forceinline__ bool comm_wait_rows(const GemmParams& p, int m0, int rows, volatile int* abort_flag) {
   const GemmComm& c = p.comm;
@@ -95,8 +87,23 @@ __device__ __forceinline__ bool comm_wait_rows(const GemmParams& p, int m0, int 
   return true;
 }
 
-// mode 2, gather CTAs: copy every rank's shard into the gathered matrix, own segments first.
-__device__ __forceinline__ void comm_gather_role(const GemmParams& p) {
+// mode 2, gather CTAs: stream every rank's shard into the gathered matrix, own segments first.
+// One thread per CTA drives a ring of shared-memory slots with bulk async copies (peer or local
+// global -> shared, then shared -> local global), so that about 190 KB per CTA are in flight over
+// NVLink; plain loads from a few CTAs cannot cover the link latency.
+constexpr int kGatherChunk = 16384;
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ void comm_gather_role(const GemmParams& p, uint8_t* smem, int smem_bytes) {
   const GemmComm& c = p.comm;
   const int g = blockIdx.x - c.gemm_ctas, G = gridDim.x - c.gemm_ctas;
   SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(c.ctrl[c.rank]);
@@ -106,32 +113,64 @@ __device__ __forceinline__ void comm_gather_role(const GemmParams& p) {
   // every rank has staged its shard (and is done with the previous use of its buffers)
   if (g == 0) symm_signal(ctrls, c.n, c.rank, 4, c.epoch);
   const bool ok = symm_wait(mine, c.n, 4, c.epoch, c.budget, p.status);
-  if (!ok) return;     // consumers time out on the segment flags and drain
+  if (!ok || threadIdx.x != 0) return;     // on a timeout the consumers run out on the segment counters
+
+  int slots = (smem_bytes - 512) / kGatherChunk;
+  if (slots > 12) slots = 12;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + slots * kGatherChunk);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 16);
+  *abort_flag = 0;
+  for (int s = 0; s < slots; ++s) mbar_init(smem_u32(&bars[s]), 1);
+  fence_mbar_init();
+
   const int num_seg = p.M / c.seg_rows;
   const int batches = num_seg / c.n;
-  const long long seg_vecs = (long long)c.seg_rows * c.ld_peer / 8;   // uint4 = 8 bf16
-  for (int d = 0; d < c.n; ++d) {
+  const long long seg_bytes = (long long)c.seg_rows * c.ld_peer * 2;
+  const int chunks_per_seg = (int)((seg_bytes + kGatherChunk - 1) / kGatherChunk);
+  const int mine_per_seg = chunks_per_seg > g ? (chunks_per_seg - g + G - 1) / G : 0;   // chunks g, g+G, ...
+  const long long total = (long long)mine_per_seg * num_seg;
+  // chunk i of this CTA: segment order position i / mine_per_seg, chunk g + (i % mine_per_seg) * G
+  auto locate = [&](long long i, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& seg) {
+    const int pos = (int)(i / mine_per_seg), ci = g + (int)(i % mine_per_seg) * G;
+    const int d = pos / batches, b = pos - d * batches;
     int owner = c.rank + d;
     if (owner >= c.n) owner -= c.n;
-    for (int b = 0; b < batches; ++b) {
-      const int s = b * c.n + owner;
-      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(c.peer[owner]) +
-                                                        (long long)b * c.seg_rows * c.ld_peer);
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c.gathered) +
-                                            (long long)s * c.seg_rows * c.ld_peer);
-      const long long stride = (long long)G * blockDim.x;
-      long long i = (long long)g * blockDim.x + threadIdx.x;
-      for (; i + 3 * stride < seg_vecs; i += 4 * stride) {
-        const uint4 a0 = ld_relaxed_sys_u4(src + i), a1 = ld_relaxed_sys_u4(src + i + stride);
-        const uint4 a2 = ld_relaxed_sys_u4(src + i + 2 * stride), a3 = ld_relaxed_sys_u4(src + i + 3 * stride);
-        dst[i] = a0; dst[i + stride] = a1; dst[i + 2 * stride] = a2; dst[i + 3 * stride] = a3;
-      }
-      for (; i < seg_vecs; i += stride) dst[i] = ld_relaxed_sys_u4(src + i);
+    seg = b * c.n + owner;
+    const long long off = (long long)ci * kGatherChunk;
+    bytes = (uint32_t)min((long long)kGatherChunk, seg_bytes - off);
+    src = reinterpret_cast<const uint8_t*>(c.peer[owner]) + (long long)b * seg_bytes + off;
+    dst = reinterpret_cast<uint8_t*>(c.gathered) + (long long)seg * seg_bytes + off;
+  };
+  long long head = 0, tail = 0;
+  bool good = true;
+  while (tail < total && good) {
+    while (head < total && head - tail < slots) {
+      const int slot = (int)(head % slots);
+      if (head >= slots)      // the store that last read this slot has to be done with shared memory
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      const uint8_t* src; uint8_t* dst; uint32_t bytes; int seg;
+      locate(head, src, dst, bytes, seg);
+      mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);
+      bulk_g2s(smem_u32(smem + slot * kGatherChunk), src, bytes, smem_u32(&bars[slot]));
+      ++head;
+    }
+    const int slot = (int)(tail % slots);
+    good = mbar_wait(smem_u32(&bars[slot]), (uint32_t)((tail / slots) & 1), abort_flag, p.status);
+    if (!good) break;
+    const uint8_t* src; uint8_t* dst; uint32_t bytes; int seg;
+    locate(tail, src, dst, bytes, seg);
+    bulk_s2g(dst, smem_u32(smem + slot * kGatherChunk), bytes);
+    ++tail;
+    if (tail % mine_per_seg == 0) {      // this CTA's part of the segment is on its way: complete and publish
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
       __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) atomicAdd(c.seg_flags + s, 1u);
+      atomicAdd(c.seg_flags + seg, 1u);
     }
   }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (mine_per_seg == 0 && good)         // more gather CTAs than chunks: still count for every segment
+    for (int s = 0; s < num_seg; ++s) atomicAdd(c.seg_flags + s, 1u);
 }
 
 // erf-GELU pieces from one exponential: with e = exp(-x^2/2), the normal pdf is e/sqrt(2 pi) and
@@ -252,10 +291,9 @@ for (int c = 0; c < ncols / 32; ++c) {
     }
   }
   if (row_ok && split_k) {
-    // partial sum of one K range (or, under a fused reduce-scatter, of one rank): reduce into the
-    // fp32 output, which in the second case lives on the rank that owns the row
-    float* dst = (p.comm.mode == 1 ? comm_dst_row(p.comm, row) : reinterpret_cast<float*>(p.C) + row * p.ldc) + col0;
-    if (full && (vec_ok || p.comm.mode == 1)) {
+    // partial sum of one K range: reduce into the fp32 output
+    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+    if (full && vec_ok) {
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),

@@ -65,7 +65,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   // fused all-gather: the CTAs behind the compute CTAs only move the peers' shards of A
   if (p.comm.mode == 2 && (int)blockIdx.x >= p.comm.gemm_ctas) {
-    comm_gather_role(p);
+    comm_gather_role(p, smem, L::kTotal - 1024);
     return;
   }
   const int cta_stride = p.comm.mode == 2 ? p.comm.gemm_ctas : (int)gridDim.x;
@@ -183,7 +183,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int m_blk, n_blk;
       tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
       m_blk = comm_perm_m(p, m_blk, kBlockM);
-      const bool split_k = p.num_splits > 1 || p.comm.mode == 1;
+      const bool split_k = p.num_splits > 1;
       const bool first_split = (unit % p.num_splits) == 0;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
@@ -268,7 +268,7 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
                       long long ld_aux_in, void* aux_out, long long ld_aux_out, int act, int aux_mode,
                       int flags, float alpha, int block_n, const GemmComm* comm, void* stream) {
   MRK_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %dx%dx%d", M, N, K);
-  MRK_REQUIRE(A && B && (C || (comm && comm->mode == 1)), "gemm: null operand");
+  MRK_REQUIRE(A && B && C, "gemm: null operand");
   MRK_REQUIRE(aux_mode == MRK_AUX_NONE || aux_in != nullptr, "gemm: aux_mode set without aux_in");
   const bool a_mn = flags & MRK_GEMM_A_MN, b_mn = flags & MRK_GEMM_B_MN;
   int bn = block_n;
@@ -335,19 +335,6 @@ static int fill_comm(GemmComm* c, int mode, int n, int rank, int seg_rows, void*
   c->epoch = epoch;
   c->budget = (long long)(budget_ms > 0 ? budget_ms : 2000) * 2000000ll;
   return 0;
-}
-
-// GEMM -> reduce-scatter.  partial = A[M,K] * W[N,K]^T (+ bias on the rank that passes one); row r of
-// it is added into the fp32 accumulator ([M/n, N], pitch N) of the rank that owns r.
-MRK_API int mrk_gemm_bf16_rs(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                             const void* bias, int flags, float alpha, void* const* peer_acc, int n, int rank,
-                             int seg_rows, void* stream) {
-  MRK_REQUIRE((N % 32) == 0, "gemm_rs: N must be a multiple of 32");
-  GemmComm c;
-  int rc = fill_comm(&c, 1, n, rank, seg_rows, peer_acc, N, nullptr, 0, 0, M);
-  if (rc) return rc;
-  return gemm_entry(A, B, nullptr, M, N, K, lda, ldb, N, bias, nullptr, 0, nullptr, 0, MRK_ACT_NONE, MRK_AUX_NONE,
-                    (flags & ~MRK_GEMM_ACCUMULATE) | MRK_GEMM_OUT_F32, alpha, 0, &c, stream);
 }
 
 // all-gather -> GEMM.  `gathered` ([M, K] bf16, pitch K, local) is filled from every rank's shard

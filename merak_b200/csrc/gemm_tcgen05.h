@@ -28,11 +28,7 @@ int mrk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
                   long long ldb, long long ldc, const void* bias, const void* aux_in,
                   long long ld_aux_in, void* aux_out, long long ld_aux_out, int act, int aux_mode,
                   int flags, float alpha, int block_n, void* stream);
-// Tensor-parallel GEMMs with the collective fused in (peer-mapped memory, see gemm_common.cuh):
-// GEMM -> reduce-scatter into the owners' fp32 accumulators, and all-gather -> GEMM.
-int mrk_gemm_bf16_rs(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                     const void* bias, int flags, float alpha, void* const* peer_acc, int n, int rank, int seg_rows,
-                     void* stream);
+// All-gather -> GEMM for tensor parallelism over peer-mapped memory (see gemm_common.cuh).
 int mrk_gemm_bf16_ag(void* gathered, void* const* peer_shards, const void* B, void* C, int M, int N, int K,
                      long long ldb, long long ldc, const void* bias, void* aux_out, long long ld_aux_out, int act,
                      int flags, float alpha, void* const* ctrls, unsigned* seg_flags, unsigned flag_target,

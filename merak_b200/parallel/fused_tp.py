@@ -27,7 +27,7 @@ from ..ops import gemm as G
 from ..ops.linear import _as2d, _bias_grad, _weight_grad
 from .symm import SymmGroup
 
-GATHER_CTAS = 8
+GATHER_CTAS = 16     # upper bound on the CTAs of a fused all-gather GEMM that only move data
 ENABLED = True      # cleared by the engine when ``comm_mode`` is not "fused"
 _FLAG_B_MN = 16
 
@@ -40,13 +40,14 @@ class TPComm:
         self.symm = symm
         self.n, self.rank = symm.n, symm.rank
         self.device = symm.device
-        self.acc = [None, None, None]       # fp32 accumulators (rotating: push / convert / clear)
-        self.acc_elems = 0
+        self.part = [None, None]            # bf16 partial products of this rank (rotating), pulled by the owners
+        self.part_elems = 0
+        self.red = [None, None]             # bf16 reduced rows of this rank (rotating), pulled for an all-reduce
+        self.red_elems = 0
         self.stage = [None, None]           # bf16 staging of this rank's all-gather input (rotating)
         self.stage_elems = 0
         self.rs_calls = 0
         self.ag_calls = 0
-        self._prev_acc_used = 0
         self.seg_flags = torch.zeros(1 << 14, dtype=torch.int32, device=self.device)
         self._flag_segs = 0
         self._flag_calls = 0
@@ -56,12 +57,15 @@ class TPComm:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.symm.group)
 
-    def _ensure_acc(self, elems: int):
-        if elems > self.acc_elems:
+    def _ensure_part(self, elems: int, red_elems: int):
+        if elems > self.part_elems:
             self._quiesce()
-            self.acc_elems = max(elems, int(self.acc_elems * 1.5))
-            self.acc = [self.symm.alloc(self.acc_elems * 4, torch.float32) for _ in range(3)]
-            self._prev_acc_used = 0
+            self.part_elems = max(elems, int(self.part_elems * 1.5))
+            self.part = [self.symm.alloc(self.part_elems * 2, torch.bfloat16) for _ in range(2)]
+        if red_elems > self.red_elems:
+            self._quiesce()
+            self.red_elems = max(red_elems, int(self.red_elems * 1.5))
+            self.red = [self.symm.alloc(self.red_elems * 2, torch.bfloat16) for _ in range(2)]
 
     def _ensure_stage(self, elems: int):
         if elems > self.stage_elems:
@@ -73,30 +77,48 @@ class TPComm:
     def gemm_reduce(self, x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], seg_rows: int,
                     all_rows: bool, b_mn: bool = False) -> torch.Tensor:
         """x2 [M, Kl] (this rank's slice of the contraction), w [N, Kl] (or [Kl, N] with ``b_mn``).
-        Returns rows of ``sum over ranks of x2 w^T``: all M rows when ``all_rows`` else this rank's."""
+        Returns rows of ``sum over ranks of x2 w^T (+ bias)``: all M rows when ``all_rows`` else this
+        rank's.  The GEMM writes its partial product into a peer-mapped buffer; the owners of the rows
+        pull and sum them (fp32) in the kernel that follows.  Buffers rotate over two calls: a rank
+        re-uses one only after it has passed the barrier of the call in between, which every rank
+        reaches after it has finished reading."""
         lib = _lib.kernels()
         M, K = x2.shape
         N = w.shape[1] if b_mn else w.shape[0]
         rows_local = M // self.n
-        self._ensure_acc(rows_local * N)
+        self._ensure_part(M * N, rows_local * N if all_rows else 0)
         k = self.rs_calls
         self.rs_calls += 1
-        acc, prev = self.acc[k % 3], self.acc[(k + 2) % 3]
+        part = self.part[k % 2]
+        G.gemm(x2, w, b_mn=b_mn, out=part.tensor[:M * N].view(M, N))
         st = _lib.stream_ptr()
-        b = bias if (bias is not None and self.rank == 0) else None
-        _lib.check(lib.mrk_gemm_bf16_rs(x2.data_ptr(), w.data_ptr(), M, N, K, x2.stride(0), w.stride(0),
-                                        b.data_ptr() if b is not None else None, _FLAG_B_MN if b_mn else 0, 1.0,
-                                        acc.table, self.n, self.rank, seg_rows, st), "mrk_gemm_bf16_rs")
-        rows_out = M if all_rows else rows_local
-        out = torch.empty(rows_out, N, dtype=torch.bfloat16, device=x2.device)
-        _lib.check(lib.mrk_tp_reduce_finish(acc.table, self.symm.ctrl.table, self.n, self.rank, 1 if all_rows else 0,
-                                            out.data_ptr(), rows_out, N, seg_rows,
-                                            prev.local_ptr if self._prev_acc_used else None, self._prev_acc_used,
-                                            k + 1, self.budget_ms, st), "mrk_tp_reduce_finish")
-        self._prev_acc_used = rows_local * N
+        if all_rows:
+            red = self.red[k % 2]
+            dst_ptr = red.local_ptr
+        else:
+            out = torch.empty(rows_local, N, dtype=torch.bfloat16, device=x2.device)
+            dst_ptr = out.data_ptr()
+        _lib.check(lib.mrk_tp_reduce_pull(part.table, self.symm.ctrl.table, self.n, self.rank, dst_ptr, rows_local, N,
+                                          seg_rows, bias.data_ptr() if bias is not None else None, k + 1, 1,
+                                          self.budget_ms, st), "mrk_tp_reduce_pull")
+        if not all_rows:
+            return out
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+        _lib.check(lib.mrk_tp_gather_rows(red.table, self.symm.ctrl.table, self.n, self.rank, out.data_ptr(), M, N,
+                                          seg_rows, k + 1, 1, self.budget_ms, st), "mrk_tp_gather_rows")
         return out
 
     # -- all-gather -> GEMM ---------------------------------------------------------------------------
+    def _gather_ctas(self, M: int, N: int, K: int) -> int:
+        """CTAs taken from the GEMM grid to stream the peers' shards: enough for the remote bytes to
+        arrive while the tiles that do not need them are computed (about 45 GB/s per CTA with ~190 KB
+        in flight), no more."""
+        gemm_s = 2.0 * M * N * K / 1.3e15
+        window = gemm_s * (self.n - 1) / self.n
+        remote = 2.0 * M * K * (self.n - 1) / self.n
+        need = int(remote / max(window, 1e-6) / 45e9) + 1
+        return max(2, min(GATHER_CTAS, need))
+
     def gather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], seg_rows: int,
                     b_mn: bool = False, act: int = G.ACT_NONE, want_preact: bool = False):
         """x_local [M/n, K] (this rank's sequence shard).  Returns (y [M, N], gathered [M, K], preact)."""
@@ -114,7 +136,8 @@ class TPComm:
             assert num_seg <= self.seg_flags.numel()
             self.seg_flags.zero_()
             self._flag_segs, self._flag_calls = num_seg, 0
-        self._flag_calls += 1
+        gather_ctas = self._gather_ctas(M, N, K)
+        self._flag_calls += gather_ctas          # every gather CTA bumps every segment counter once
         gathered = torch.empty(M, K, dtype=torch.bfloat16, device=x_local.device)
         y = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device)
         pre = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device) if want_preact else None
@@ -122,7 +145,7 @@ class TPComm:
             gathered.data_ptr(), stage.table, w.data_ptr(), y.data_ptr(), M, N, K, w.stride(0), N,
             bias.data_ptr() if bias is not None else None, pre.data_ptr() if pre is not None else None, N, act,
             _FLAG_B_MN if b_mn else 0, 1.0, self.symm.ctrl.table, self.seg_flags.data_ptr(),
-            GATHER_CTAS * self._flag_calls, GATHER_CTAS, self.n, self.rank, seg_rows, k + 1, self.budget_ms,
+            self._flag_calls, gather_ctas, self.n, self.rank, seg_rows, k + 1, self.budget_ms,
             _lib.stream_ptr()), "mrk_gemm_bf16_ag")
         return y, gathered, pre
 

@@ -170,49 +170,36 @@ def _preset_flags(ctrls, which, epoch):
         c.view(torch.int32)[which * 16: which * 16 + 16] = epoch
 
 
-@pytest.mark.parametrize("n,B,seg,Kl,N,b_mn", [(2, 2, 128, 256, 512, False), (4, 1, 256, 128, 256, True),
-                                               (2, 3, 64, 96, 160, False)])
-def test_gemm_reduce_scatter_emulated(n, B, seg, Kl, N, b_mn):
+@pytest.mark.parametrize("n,B,seg,N", [(2, 2, 128, 512), (4, 1, 256, 256), (3, 3, 64, 160)])
+def test_reduce_pull_and_gather_rows_emulated(n, B, seg, N):
     from merak_b200.ops import _lib
     lib = _lib.kernels()
     dev = torch.device("cuda")
     torch.manual_seed(0)
     L = seg * n
     M = B * L
-    xs = [torch.randn(M, Kl, device=dev, dtype=torch.bfloat16) * 0.5 for _ in range(n)]
-    ws = [torch.randn(N, Kl, device=dev, dtype=torch.bfloat16) * 0.1 for _ in range(n)]
-    wk = [w.t().contiguous() if b_mn else w for w in ws]
+    parts = [torch.randn(M, N, device=dev, dtype=torch.bfloat16) for _ in range(n)]
     bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
-    accs = [torch.zeros(M // n * N, device=dev) for _ in range(n)]
     ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(n)]
-    at, ct = _table([a.data_ptr() for a in accs]), _table([c.data_ptr() for c in ctrls])
+    pt, ct = _table([a.data_ptr() for a in parts]), _table([c.data_ptr() for c in ctrls])
     st = _lib.stream_ptr()
-    for r in range(n):
-        _lib.check(lib.mrk_gemm_bf16_rs(xs[r].data_ptr(), wk[r].data_ptr(), M, N, Kl, Kl, wk[r].stride(0),
-                                        bias.data_ptr() if r == 0 else None, 16 if b_mn else 0, 1.0, at, n, r, seg,
-                                        st), "rs")
-    _preset_flags(ctrls, 5, 1)
-    ref = sum(x.float() @ w.float().t() for x, w in zip(xs, ws)) + bias.float()
+    ref = sum(p_.float() for p_ in parts) + bias.float()
     ref3 = ref.view(B, n, seg, N)
-    outs_rs, outs_ar = [], []
+    reds = [torch.empty(M // n, N, dtype=torch.bfloat16, device=dev) for _ in range(n)]
     for r in range(n):
-        o = torch.empty(M // n, N, dtype=torch.bfloat16, device=dev)
-        _lib.check(lib.mrk_tp_reduce_finish(at, ct, n, r, 0, o.data_ptr(), M // n, N, seg, None, 0, 1, 50, st), "fin")
-        outs_rs.append(o)
-        o2 = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-        _lib.check(lib.mrk_tp_reduce_finish(at, ct, n, r, 1, o2.data_ptr(), M, N, seg, None, 0, 1, 50, st), "fin")
-        outs_ar.append(o2)
+        _lib.check(lib.mrk_tp_reduce_pull(pt, ct, n, r, reds[r].data_ptr(), M // n, N, seg, bias.data_ptr(), 1, 0, 50,
+                                          st), "pull")
+    rt = _table([a.data_ptr() for a in reds])
+    outs = []
+    for r in range(n):
+        o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.mrk_tp_gather_rows(rt, ct, n, r, o.data_ptr(), M, N, seg, 1, 0, 50, st), "gather")
+        outs.append(o)
     torch.cuda.synchronize()
     assert _lib.status() == 0
     for r in range(n):
-        torch.testing.assert_close(outs_rs[r].float().view(B, seg, N), ref3[:, r], rtol=2e-2, atol=2e-2)
-        torch.testing.assert_close(outs_ar[r].float(), ref, rtol=2e-2, atol=2e-2)
-    # clearing an accumulator
-    z = torch.ones(1024, device=dev)
-    o = torch.empty(M // n, N, dtype=torch.bfloat16, device=dev)
-    _lib.check(lib.mrk_tp_reduce_finish(at, ct, n, 0, 0, o.data_ptr(), M // n, N, seg, z.data_ptr(), 1024, 1, 50, st), "fin")
-    torch.cuda.synchronize()
-    assert float(z.abs().sum()) == 0.0
+        torch.testing.assert_close(reds[r].float().view(B, seg, N), ref3[:, r].bfloat16().float(), rtol=0, atol=0)
+        torch.testing.assert_close(outs[r].float(), ref.bfloat16().float(), rtol=0, atol=0)
 
 
 @pytest.mark.parametrize("n,B,seg,K,N", [(2, 2, 128, 256, 512), (4, 1, 256, 128, 384), (2, 1, 64, 64, 96)])
