@@ -144,10 +144,13 @@ __device__ __forceinline__ void comm_gather_role(const GemmParams& p, uint8_t* s
   long long head = 0, tail = 0;
   bool good = true;
   while (tail < total && good) {
-    while (head < total && head - tail < slots) {
+    // At most slots - 4 loads are in flight, so the slot a new load lands in was last read by a store
+    // issued at least four stores ago: waiting until no more than three stores are still reading
+    // shared memory frees it without draining the store queue.
+    while (head < total && head - tail < slots - 4) {
       const int slot = (int)(head % slots);
-      if (head >= slots)      // the store that last read this slot has to be done with shared memory
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      if (head >= slots)
+        asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
       const uint8_t* src; uint8_t* dst; uint32_t bytes; int seg;
       locate(head, src, dst, bytes, seg);
       mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);
