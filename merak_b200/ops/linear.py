@@ -31,9 +31,9 @@ def _as2d(x, K):
     return x2
 
 
-def _weight_grad(dy2, x2, weight):
-    """dW[N,K] = dy2^T x2, accumulated into ``weight.main_grad`` when present."""
-    mg = getattr(weight, "main_grad", None)
+def _weight_grad(dy2, x2, weight, mg=None):
+    """dW[N,K] = dy2^T x2, accumulated into ``weight.main_grad`` (or ``mg``) when present."""
+    mg = mg if mg is not None else getattr(weight, "main_grad", None)
     if mg is not None:
         G.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg.view(weight.shape), accumulate=True)
         return None
@@ -62,6 +62,7 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x2, weight, bias)
         ctx.in_shape = x.shape
         ctx.has_res = residual is not None
+        ctx.main_grad = getattr(weight, "main_grad", None)     # slices of stacked weights carry their own view
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
@@ -73,7 +74,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx2, _ = G.gemm(dy2, weight, b_mn=True)
             dx = dx2.view(ctx.in_shape)
-        dw = _weight_grad(dy2, x2, weight) if weight.requires_grad else None
+        dw = _weight_grad(dy2, x2, weight, ctx.main_grad) if weight.requires_grad else None
         db = _bias_grad(dy2, bias)
         return dx, dw, db, (dy if ctx.has_res else None)
 

@@ -162,6 +162,18 @@ class PipelineEngine:
                     no_decay.update(id(p) for p in m.parameters(recurse=False))
             for p in params:
                 p._no_weight_decay = id(p) in no_decay or p.dim() <= 1
+            # Expert-parallel parameters differ between the ranks of the expert-parallel group: they get
+            # their own flat buffers and optimizer, reduced only over the replicas of the same experts.
+            self.flat_expert, self.optimizer_expert = None, None
+            expert_params = [p for p in params if getattr(p, "expert_parallel", False)]
+            if expert_params and mpu.get_expert_parallel_world_size() > 1:
+                if mpu.get_expert_parallel_world_size() != self.dp_size:
+                    raise NotImplementedError("expert parallel degree must equal the data parallel degree (or 1)")
+                params = [p for p in params if not getattr(p, "expert_parallel", False)]
+                self.flat_expert = FlatBuffers(expert_params, grad_dtype=torch.float32, pad_to=64)
+                self.optimizer_expert = FusedAdamW(self.flat_expert, lr=a.learning_rate,
+                                                   betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                                   weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm)
             pad = 64 * self.dp_size
             # Fused data-parallel step over peer-mapped flat buffers (bf16 training on one node);
             # it shards the optimizer state exactly as ZeRO-1 does, so it also sets ``self.zero``.
@@ -184,6 +196,8 @@ class PipelineEngine:
         else:
             self.optimizer = optimizer if optimizer is not None else optimizer_factory(params)
             self.zero = False
+        if getattr(self, "optimizer_expert", None) is not None:
+            self.optimizer_expert.param_groups = self.optimizer.param_groups     # one learning-rate schedule
         self.lr_scheduler = lr_scheduler
         if self.lr_scheduler is None and lr_scheduler_factory is not None:
             self.lr_scheduler = lr_scheduler_factory(self.optimizer)
@@ -285,7 +299,8 @@ class PipelineEngine:
     # ------------------------------------------------------------------------------------------
     def _graph_capable(self) -> bool:
         return (bool(getattr(self.args, "cuda_graph", False)) and self.device.type == "cuda" and self.num_stages == 1
-                and self.flat is not None and self.loss_scaler is None and not getattr(self, "_graph_failed", False))
+                and self.flat is not None and self.loss_scaler is None and not getattr(self, "_graph_failed", False)
+                and getattr(self, "flat_expert", None) is None and not hasattr(self.module, "_has_moe"))
 
     def _graph_step_body(self):
         out = self.module((), self._g_ext)
@@ -417,6 +432,7 @@ class PipelineEngine:
         carried = tuple(carried or ())
         self.module.current_buffer = buf
         out = self.module(carried, self.buf_externals[buf])
+        self._collect_aux_loss(buf)
         if self.is_last:
             if not getattr(self, "_compute_loss", True) or (not self._training_pass and self.args.return_logits):
                 self._eval_outputs.append(out.detach() if isinstance(out, torch.Tensor) else out)
@@ -434,6 +450,22 @@ class PipelineEngine:
             self.buf_outputs[buf] = out if isinstance(out, tuple) else (out,)
         if self.wall_clock_breakdown:
             self.timers("forward").stop()
+
+    def _collect_aux_loss(self, buf: int):
+        """Auxiliary losses that layers of this stage left in ``module.aux_loss`` during the forward
+        pass (router load balancing) are kept per pipeline buffer and join that buffer's backward."""
+        mods = getattr(self, "_aux_modules", None)
+        if mods is None:
+            mods = self._aux_modules = [m for m in self.module.modules() if hasattr(m, "aux_loss_alpha")]
+            self.buf_aux = {}
+        total = None
+        for m in mods:
+            a = getattr(m, "aux_loss", None)
+            if a is not None:
+                total = a if total is None else total + a
+                m.aux_loss = None
+        if total is not None and self._training_pass:
+            self.buf_aux[buf] = total
 
     def _exec_precheckpoint_forward_pass(self, buf: int):
         """Forward under ``pre_checkpoint``: every recompute segment registers a record that
@@ -468,12 +500,19 @@ class PipelineEngine:
             scale = 1.0 / self.micro_batches
             if self.loss_scaler is not None:
                 scale *= self.loss_scaler.cur_scale
+            aux = self.buf_aux.pop(buf, None)
+            if aux is not None:
+                loss = loss + aux.to(loss.dtype)
             (loss * scale).backward()
             self.buf_loss[buf] = None
         else:
             outs = self.buf_outputs[buf]
             grads = self.buf_out_grads[buf]
             pairs = [(o, g) for o, g in zip(outs, grads or []) if isinstance(o, torch.Tensor) and o.requires_grad]
+            aux = self.buf_aux.pop(buf, None)
+            if aux is not None and aux.requires_grad:
+                scale = (1.0 / self.micro_batches) * (self.loss_scaler.cur_scale if self.loss_scaler is not None else 1.0)
+                pairs.append((aux, torch.full_like(aux, scale)))
             if pairs:
                 torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
             self.buf_outputs[buf] = None
@@ -492,7 +531,8 @@ class PipelineEngine:
         """Gradients autograd produced as ``p.grad`` (PyTorch-path ops) move into the flat buffer."""
         if self.flat is None:
             return
-        for p in self.flat.params:
+        extra = self.flat_expert.params if getattr(self, "flat_expert", None) is not None else []
+        for p in list(self.flat.params) + list(extra):
             if p.grad is not None:
                 p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                 p.grad = None
@@ -737,22 +777,37 @@ class PipelineEngine:
         if self.loss_scaler is not None:
             grad_scale /= self.loss_scaler.cur_scale
         if self.flat is not None:
+            expert_ss = None
+            if getattr(self, "optimizer_expert", None) is not None:
+                # squared norm of the expert gradients of the whole expert-parallel group
+                expert_ss = self.optimizer_expert.grad_sumsq().clone()
+                dist.all_reduce(expert_ss, group=mpu.get_expert_parallel_group())
+                if self.num_stages > 1:
+                    dist.all_reduce(expert_ss, group=mpu.get_pipe_parallel_group())
             if getattr(self, "fused_dp", None) is not None:
                 sumsq = None
-                if mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1:
+                if mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1 or expert_ss is not None:
                     sumsq = self.fused_dp.gathered_sumsq()
                     if mpu.get_model_parallel_world_size() > 1:
                         dist.all_reduce(sumsq, group=mpu.get_model_parallel_group())
                     if self.num_stages > 1:
                         dist.all_reduce(sumsq, group=mpu.get_pipe_parallel_group())
+                    if expert_ss is not None:
+                        sumsq = sumsq + expert_ss
                 self.fused_dp.adamw_allgather(self.optimizer, grad_scale, sumsq)
             else:
-                distributed_norm = (mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1 or self.zero)
+                distributed_norm = (mpu.get_model_parallel_world_size() > 1 or self.num_stages > 1 or self.zero
+                                    or expert_ss is not None)
                 sumsq = self._global_grad_sumsq() if distributed_norm else None
+                if expert_ss is not None:
+                    sumsq = sumsq + expert_ss
                 self.optimizer.step(grad_scale=grad_scale, sumsq=sumsq)
                 if self.zero:
                     dist.all_gather_into_tensor(self.flat.model, self.flat.model[self.optimizer.start:self.optimizer.end]
                                                 .clone(), group=mpu.get_data_parallel_group())
+            if getattr(self, "optimizer_expert", None) is not None:
+                self.optimizer_expert.step(grad_scale=grad_scale, sumsq=sumsq)
+                self.flat_expert.zero_grad()
             if self.loss_scaler is not None:
                 self.loss_scaler.update_scale(bool(self.optimizer.skipped().item()))
             self.flat.zero_grad()

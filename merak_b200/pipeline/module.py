@@ -305,7 +305,10 @@ class PipelineModule(nn.Module):
         if n == 1:
             return
         src = mpu.get_data_parallel_ranks()[0]
+        ep = mpu.get_expert_parallel_world_size()
         for p in self.parameters():
+            if ep > 1 and getattr(p, "expert_parallel", False):
+                continue        # every rank of the expert-parallel group holds different experts
             dist.broadcast(p.data, src, group=group)
 
     # -- tied weights ------------------------------------------------------------------------------

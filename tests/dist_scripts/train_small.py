@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--dp", type=int, default=1)
     ap.add_argument("--sp", type=int, default=1)
+    ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--tp_overlap", type=int, default=0)
     ap.add_argument("--model", default="gpt2")
     ap.add_argument("--steps", type=int, default=8)
@@ -44,7 +45,7 @@ def main():
     ap.add_argument("--out", required=True)
     o = ap.parse_args()
 
-    Merak.init(o.pp, o.tp, o.dp, sp=o.sp, backend="gloo" if o.device == "cpu" else "nccl")
+    Merak.init(o.pp, o.tp, o.dp, sp=o.sp, ep=o.ep, backend="gloo" if o.device == "cpu" else "nccl")
     torch.manual_seed(1234)
     V, L = 512, 32
     if o.model == "gpt2":
@@ -53,6 +54,10 @@ def main():
     elif o.model == "bert":
         model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=0.0))
         task = "mlm"
+    elif o.model == "moe":
+        from merak_b200.models.moe import DeepseekV2ForCausalLM, deepseek_v2_config
+        model = DeepseekV2ForCausalLM(deepseek_v2_config("deepseek-tiny", vocab_size=V, aux_loss_alpha=0.01))
+        task = "causal"
     else:
         model = LlamaForCausalLM(llama_config("llama-tiny", vocab_size=V))
         task = "causal"

@@ -84,6 +84,20 @@ def test_tp2_megatron_sequence_parallel_with_biases(tmp_path, baseline, model):
     assert_close(got, baseline[model])
 
 
+def test_moe_expert_parallel_and_pipeline(tmp_path):
+    """Mixture-of-experts model: experts split over two expert-parallel ranks (tokens exchanged by
+    all-to-all, expert gradients kept out of the data-parallel reduction) and a two-stage pipeline
+    (router auxiliary losses join the backward pass of their own stage) both reproduce the
+    single-process loss curve."""
+    single = run_layout(tmp_path, "moe_single", 1, ["--model", "moe", "--steps", "5"])
+    assert single[-1] < single[0]
+    ep2 = run_layout(tmp_path, "moe_dp2_ep2", 2, ["--model", "moe", "--steps", "5", "--dp", "2", "--ep", "2",
+                                                  "--gas", "2"])
+    assert_close(ep2, single)
+    pp2 = run_layout(tmp_path, "moe_pp2", 2, ["--model", "moe", "--steps", "5", "--pp", "2"])
+    assert_close(pp2, single)
+
+
 def test_pp2_tp2_recompute_4ranks(tmp_path, baseline):
     got = run_layout(tmp_path, "pp2tp2", 4, ["--pp", "2", "--tp", "2", "--recompute", "1"])
     assert_close(got, baseline["gpt2"])
