@@ -96,6 +96,13 @@ class CheckpointSaver:
             torch.save({"optimizer_state_dict": _cpu(optimizer.state_dict()),
                         "param_shapes": U.get_zero_param_shapes(model, engine.flat)}, zname,
                        _use_new_zipfile_serialization=False)
+        if engine is not None and getattr(engine, "flat_expert", None) is not None:
+            # expert-parallel parameters differ per rank of the expert-parallel group: one file each
+            ename = _expert_file(name)
+            esd = {"model": {k: v.detach().cpu() for k, v in model.state_dict().items() if _is_expert_key(model, k)}}
+            if not a.no_save_optim:
+                esd["optimizer"] = _cpu(engine.optimizer_expert.state_dict())
+            torch.save(esd, ename, _use_new_zipfile_serialization=False)
         _barrier()
         if _is_rank0():
             if best_model:
@@ -107,6 +114,17 @@ class CheckpointSaver:
             log_dist("saved checkpoint at iteration %s to %s" % (iteration, os.path.dirname(name)), ranks=[0])
         _barrier()
         return name
+
+
+def _expert_file(name: str) -> str:
+    """File of this rank's experts next to the model file ``name``."""
+    return os.path.join(os.path.dirname(name), "expert_parallel_rank_{:02d}_states.pt".format(
+        mpu.get_expert_parallel_rank()))
+
+
+def _is_expert_key(model, key: str) -> bool:
+    p = dict(model.named_parameters()).get(key)
+    return p is not None and getattr(p, "expert_parallel", False)
 
 
 def _cpu(obj):
@@ -162,6 +180,18 @@ class CheckpointLoader:
             if t is not None:
                 spec["param"].data.copy_(t)
         finetune = a.finetune or release
+        esd = None
+        if engine is not None and getattr(engine, "flat_expert", None) is not None and os.path.isfile(_expert_file(name)):
+            esd = torch.load(_expert_file(name), map_location="cpu", weights_only=False)
+            own = dict(model.state_dict())
+            for k, v in esd["model"].items():
+                if k in own:
+                    own[k].copy_(v)
+            if not finetune and not a.no_load_optim and "optimizer" in esd:
+                engine.optimizer_expert.load_state_dict(_to_device(esd["optimizer"], _device_of(model)))
+            else:
+                eo = engine.optimizer_expert
+                eo.master.copy_(eo.flat.model[eo.start:eo.end].float())
         if not finetune and not a.no_load_optim:
             zero = bool(engine is not None and getattr(engine, "zero", False))
             if zero:

@@ -27,6 +27,9 @@ int mrk_tp_reduce_pull(void* const* part_ptrs, void* const* ctrl_ptrs, int n, in
                        int N, int seg_rows, const void* bias, unsigned epoch, int sync, int budget_ms, void* stream);
 int mrk_tp_gather_rows(void* const* red_ptrs, void* const* ctrl_ptrs, int n, int rank, void* out, long long M, int N,
                        int seg_rows, unsigned epoch, int sync, int budget_ms, void* stream);
+int mrk_moe_alltoall_push(void* const* recv_ptrs, void* const* ctrl_ptrs, int n, int rank, const void* send,
+                          const long long* send_begin, const long long* dst_row, int H, int elem_bytes, unsigned epoch,
+                          int sync, int budget_ms, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,95 @@ def exchange_rows(x: torch.Tensor, in_splits: List[int], out_splits: List[int], 
     return _AllToAllRows.apply(x, in_splits, out_splits, group)
 
 
+# ---- peer-store exchange ---------------------------------------------------------------------------
+FUSED_ENABLED = True      # cleared when ``comm_mode`` is not "fused"
+
+
+class EPComm:
+    """Peer-mapped receive buffers of one expert-parallel group for the push all-to-all kernel
+    (``csrc/moe_dispatch.cu``).  Two buffers rotate: a rank can only start call k after every rank
+    has finished call k-1, i.e. after everybody has consumed what call k-2 delivered."""
+
+    def __init__(self, symm):
+        self.symm, self.n, self.rank = symm, symm.n, symm.rank
+        self.bufs = [None, None]
+        self.cap_bytes = 0
+        self.calls = 0
+        self.budget_ms = 20000
+
+    def _ensure(self, worst_bytes: int):
+        """``worst_bytes``: size of the largest possible delivery (every row of every rank arriving
+        here); the same on all ranks, so growing needs no negotiation."""
+        if worst_bytes > self.cap_bytes:
+            torch.cuda.synchronize(self.symm.device)
+            dist.barrier(group=self.symm.group)
+            self.cap_bytes = max(worst_bytes, 1 << 20)
+            self.bufs = [self.symm.alloc(self.cap_bytes, torch.uint8) for _ in range(2)]
+
+    def push(self, x: torch.Tensor, send_begin: List[int], dst_row: List[int], rows_out: int,
+             worst_rows: int) -> torch.Tensor:
+        import ctypes
+        from ..ops import _lib
+        H = x.shape[1]
+        self._ensure(worst_rows * H * x.element_size())
+        buf = self.bufs[self.calls % 2]
+        self.calls += 1
+        n = self.n
+        sb = (ctypes.c_longlong * (n + 1))(*send_begin)
+        dr = (ctypes.c_longlong * n)(*dst_row)
+        x = x.contiguous()
+        _lib.check(_lib.kernels().mrk_moe_alltoall_push(buf.table, self.symm.ctrl.table, n, self.rank, x.data_ptr(), sb,
+                                                        dr, H, x.element_size(), self.calls, 1, self.budget_ms,
+                                                        _lib.stream_ptr()), "mrk_moe_alltoall_push")
+        nbytes = rows_out * H * x.element_size()
+        return buf.tensor[:nbytes].view(x.dtype).view(rows_out, H).clone()
+
+
+_EP_COMMS = {}
+
+
+def get_ep_comm(group, device) -> Optional[EPComm]:
+    """Collective on first use: the EPComm of ``group`` or None (CPU, peer mapping unavailable)."""
+    key = id(group)
+    if key not in _EP_COMMS:
+        sg = None
+        if FUSED_ENABLED and device.type == "cuda":
+            from .symm import SymmGroup
+            sg = SymmGroup.create(group, device)
+        _EP_COMMS[key] = EPComm(sg) if sg is not None else None
+    return _EP_COMMS[key]
+
+
+class _PushRows(torch.autograd.Function):
+    """All-to-all of rows by peer stores.  ``C[s][d]`` = rows rank s sends to rank d (host matrix);
+    ``forward_dir`` True sends this rank's blocks C[rank][:], False returns blocks C[:][rank]."""
+
+    @staticmethod
+    def forward(ctx, x, C, comm: EPComm, forward_dir: bool):
+        ctx.C, ctx.comm, ctx.forward_dir = C, comm, forward_dir
+        return _push(x, C, comm, forward_dir)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return _push(dy, ctx.C, ctx.comm, not ctx.forward_dir), None, None, None
+
+
+def _push(x, C, comm: EPComm, forward_dir: bool):
+    n, me = comm.n, comm.rank
+    if forward_dir:
+        sizes = [C[me][d] for d in range(n)]                                   # my block for each destination
+        dst_row = [sum(C[s][d] for s in range(me)) for d in range(n)]            # after lower-ranked sources
+        rows_out = sum(C[s][me] for s in range(n))
+    else:
+        sizes = [C[s][me] for s in range(n)]                                   # give each source its rows back
+        dst_row = [sum(C[s][d] for d in range(me)) for s in range(n)]            # its block for me, in its order
+        rows_out = sum(C[me][d] for d in range(n))
+    begin = [0]
+    for v in sizes:
+        begin.append(begin[-1] + v)
+    return comm.push(x, begin, dst_row, rows_out, worst_rows=sum(sum(r) for r in C))
+
+
 class TopKRouter(nn.Module):
     """Softmax-then-top-k gate (DeepSeek-V2: ``norm_topk_prob`` off, ``routed_scaling_factor``)."""
 
@@ -169,12 +258,17 @@ class MoELayer(nn.Module):
 
         group = mpu.get_expert_parallel_group() if n > 1 else None
         if n > 1:
-            recv_counts = torch.empty_like(counts)
-            dist.all_to_all_single(recv_counts, counts, group=group)          # [n, E_local] from every source
-            rc = recv_counts.view(n, self.num_local)
-            in_splits = counts.view(n, self.num_local).sum(1).tolist()
-            out_splits = rc.sum(1).tolist()
-            recv = exchange_rows(send, in_splits, out_splits, group)
+            all_counts = torch.empty(n * E, dtype=counts.dtype, device=counts.device)
+            dist.all_gather_into_tensor(all_counts, counts, group=group)       # every rank's per-expert counts
+            all_counts = all_counts.view(n, n, self.num_local)                 # [source, destination, local expert]
+            rc = all_counts[:, self.ep_rank, :]                                 # rows arriving here, per source
+            C = all_counts.sum(2).tolist()                                      # rows source -> destination
+            in_splits, out_splits = C[self.ep_rank], [C[s_][self.ep_rank] for s_ in range(n)]
+            comm = get_ep_comm(group, x.device) if x.is_cuda else None
+            if comm is not None:
+                recv = _PushRows.apply(send, C, comm, True)
+            else:
+                recv = exchange_rows(send, in_splits, out_splits, group)
             # received rows are [source][local expert]; regroup expert-major
             src_expert = torch.arange(self.num_local, device=x.device).repeat(n)
             row_expert = torch.repeat_interleave(src_expert, rc.reshape(-1))
@@ -189,7 +283,10 @@ class MoELayer(nn.Module):
         if n > 1:
             inv = torch.empty_like(regroup)
             inv[regroup] = torch.arange(regroup.numel(), device=x.device)
-            back = exchange_rows(y.index_select(0, inv), out_splits, in_splits, group)
+            if comm is not None:
+                back = _PushRows.apply(y.index_select(0, inv), C, comm, False)
+            else:
+                back = exchange_rows(y.index_select(0, inv), out_splits, in_splits, group)
         else:
             back = y
         pair_w = w.reshape(-1).index_select(0, order).to(back.dtype).unsqueeze(1)

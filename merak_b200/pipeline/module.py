@@ -64,6 +64,8 @@ class PipelineModule(nn.Module):
         tp = mpu.get_model_parallel_world_size()
         from ..parallel import fused_tp
         fused_tp.ENABLED = getattr(args, "comm_mode", "fused") == "fused"
+        from ..parallel import expert as _expert
+        _expert.FUSED_ENABLED = fused_tp.ENABLED
         if tp > 1 and model is not None:
             apply_tensor_parallel(model, megatron_sp=getattr(args, "megatron_sequence_parallel", False),
                                   seq_dim=args.sequence_dim, vocab_parallel=args.parallel_vocab)
