@@ -13,6 +13,7 @@ from __future__ import annotations
 import datetime
 import json
 import os
+import re
 import random
 import shutil
 from typing import Optional
@@ -235,6 +236,13 @@ class CheckpointLoader:
         tp, rank = mpu.get_model_parallel_world_size(), mpu.get_model_parallel_rank()
         target = model.state_dict()
         loaded = 0
+        # Hugging Face GPT-2 stores its projections as Conv1D ([in, out]); this framework's are [out, in]
+        conv1d = False
+        cfg_file = os.path.join(path, "config.json")
+        if os.path.isfile(cfg_file):
+            with open(cfg_file) as f:
+                conv1d = json.load(f).get("model_type") == "gpt2"
+        fused_parts = {"c_attn": 3, "qkv": 3, "qkv_proj": 3, "gate_up_proj": 2}
         for key, dst in target.items():
             parts = key.split(".")
             body = ".".join(parts[1:]) if parts[0].isdigit() else key
@@ -243,8 +251,14 @@ class CheckpointLoader:
             if src_name is None:
                 continue
             t = getter(src_name)
+            if conv1d and t.dim() == 2 and re.search(r"\.(c_attn|c_proj|c_fc)\.weight$", plain):
+                t = t.t().contiguous()
             if t.shape != dst.shape and tp > 1:
-                if "col_linear" in key or (t.dim() >= 1 and t.shape[0] == dst.shape[0] * tp):
+                nfused = next((v for k, v in fused_parts.items() if ("." + k + ".") in ("." + plain)), 1)
+                if "col_linear" in key and nfused > 1 and t.shape[0] % (nfused * tp) == 0:
+                    # fused [q; k; v] / [gate; up] rows: every part is split on its own
+                    t = torch.cat([part.chunk(tp, 0)[rank] for part in t.chunk(nfused, 0)], 0)
+                elif "col_linear" in key or (t.dim() >= 1 and t.shape[0] == dst.shape[0] * tp):
                     t = t.chunk(tp, 0)[rank]
                 elif "row_linear" in key and t.dim() == 2:
                     t = t.chunk(tp, 1)[rank]

@@ -1,0 +1,26 @@
+"""The example scripts run end to end on CPU with tiny sizes (framework models, the generic
+torch.fx path for a plain nn.Module, and the torch.export capture path)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+COMMON = ["--per_device_train_batch_size", "2", "--gradient_accumulation_steps", "2", "--max_steps", "2",
+          "--logging_steps", "1", "--no_cuda", "true", "--report_to", "none"]
+
+
+@pytest.mark.parametrize("script,extra", [
+    ("models/gpt2/run_gpt.py", ["--model_size", "gpt2-tiny", "--seq_length", "32", "--dataset_size", "32"]),
+    ("image-classification/run_vit.py", ["--image_size", "32", "--hidden_size", "64", "--layers", "2", "--heads", "2",
+                                         "--num_labels", "10", "--dataset_size", "32"]),
+    ("unet/run_unet.py", ["--image_size", "32", "--width", "8", "--dataset_size", "32"]),
+    ("lora/run_lora.py", ["--model_size", "llama-tiny", "--seq_length", "32", "--dataset_size", "32"]),
+])
+def test_example_runs(tmp_path, script, extra):
+    cmd = [sys.executable, os.path.join(ROOT, "examples", script), "--output_dir", str(tmp_path)] + extra + COMMON
+    env = dict(os.environ, MERAK_QUIET="1", OMP_NUM_THREADS="2", MASTER_PORT="29%03d" % (os.getpid() % 1000))
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert "steps: 2 loss:" in (res.stdout + res.stderr)
