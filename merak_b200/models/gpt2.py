@@ -69,6 +69,7 @@ class GPT2Attention(nn.Module):
         self.c_attn = Linear(self.embed_dim, 3 * self.embed_dim)
         self.c_attn.fused_parts = 3          # rows are [q; k; v]: shard each part separately under TP
         self.c_proj = Linear(self.embed_dim, self.embed_dim)
+        self.c_attn.tp_unit = self.c_proj.tp_unit = self.head_dim     # heads are never split between ranks
         self.resid_pdrop = config.resid_pdrop
 
     def forward(self, x, residual=None):

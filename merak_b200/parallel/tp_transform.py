@@ -71,16 +71,27 @@ def set_tp_layer_lists(col_para_list: Optional[Sequence[str]] = None, row_para_l
     MANUAL["set"] = True
 
 
-def _slice_fused(weight: torch.Tensor, dim: int, rank: int, tp: int, parts=None, sizes=None) -> torch.Tensor:
+def _unit_range(total: int, tp: int, rank: int, unit: int = 1):
+    """``[start, start + size)`` of rank ``rank`` when ``total`` elements made of indivisible groups of
+    ``unit`` (attention heads) are split over ``tp`` ranks; the first ``groups % tp`` ranks get one
+    group more (GPT-2 1.5B: 25 heads over 2 ranks -> 13 + 12)."""
+    groups = total // max(1, unit)
+    base, rem = divmod(groups, tp)
+    n = base + (1 if rank < rem else 0)
+    start = base * rank + min(rank, rem)
+    return start * unit, n * unit
+
+
+def _slice_fused(weight: torch.Tensor, dim: int, rank: int, tp: int, parts=None, sizes=None, unit: int = 1) -> torch.Tensor:
     """This rank's slice of a (possibly fused) weight along ``dim``."""
     if sizes is None and parts:
         sizes = [weight.shape[dim] // parts] * parts
     if not sizes:
-        return weight.chunk(tp, dim=dim)[rank].contiguous()
+        sizes = [weight.shape[dim]]
     pieces, off = [], 0
     for sz in sizes:
-        part = weight.narrow(dim, off, sz)
-        pieces.append(part.chunk(tp, dim=dim)[rank])
+        start, n = _unit_range(sz, tp, rank, unit if sz % max(1, unit) == 0 else 1)
+        pieces.append(weight.narrow(dim, off + start, n))
         off += sz
     return torch.cat(pieces, dim=dim).contiguous()
 
@@ -95,14 +106,16 @@ class ColPara(nn.Module):
         w = linear.weight
         self.in_features, self.out_features = linear.in_features, linear.out_features
         parts, sizes = getattr(linear, "fused_parts", None), getattr(linear, "fused_sizes", None)
+        unit = int(getattr(linear, "tp_unit", 1) or 1)
         self.col_linear = ColumnParallelLinear(linear.in_features, linear.out_features,
                                                bias=linear.bias is not None, gather_output=gather_output,
                                                sequence_parallel=sequence_parallel, seq_dim=seq_dim,
                                                params_dtype=w.dtype, device="meta")
-        if w.device.type != "meta":
-            self.col_linear.weight = nn.Parameter(_slice_fused(w.data, 0, rank, tp, parts, sizes))
+        if True:        # slicing works on meta tensors too (shapes only)
+            self.col_linear.weight = nn.Parameter(_slice_fused(w.data, 0, rank, tp, parts, sizes, unit))
             if linear.bias is not None:
-                self.col_linear.bias = nn.Parameter(_slice_fused(linear.bias.data, 0, rank, tp, parts, sizes))
+                self.col_linear.bias = nn.Parameter(_slice_fused(linear.bias.data, 0, rank, tp, parts, sizes, unit))
+            self.col_linear.output_size_per_partition = self.col_linear.weight.shape[0]
         for p in self.col_linear.parameters():
             p.model_parallel, p.partition_dim = True, 0
         self.fused_parts, self.fused_sizes = parts, sizes
@@ -125,8 +138,10 @@ class RowPara(nn.Module):
                                             input_is_parallel=input_is_parallel,
                                             sequence_parallel=sequence_parallel, seq_dim=seq_dim,
                                             params_dtype=w.dtype, device="meta")
-        if w.device.type != "meta":
-            self.row_linear.weight = nn.Parameter(w.data.chunk(tp, dim=1)[rank].contiguous())
+        if True:
+            unit = int(getattr(linear, "tp_unit", 1) or 1)
+            self.row_linear.weight = nn.Parameter(_slice_fused(w.data, 1, rank, tp, None, None, unit))
+            self.row_linear.input_size_per_partition = self.row_linear.weight.shape[1]
             if linear.bias is not None:
                 self.row_linear.bias = nn.Parameter(linear.bias.data.clone())
         self.row_linear.weight.model_parallel, self.row_linear.weight.partition_dim = True, 1

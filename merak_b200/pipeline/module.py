@@ -297,6 +297,17 @@ class PipelineModule(nn.Module):
             self.act_ckpt_interval = 0
 
     def configure_distributed_model(self, device):
+        if any(p.device.type == "meta" for p in self.parameters()):
+            # the model was built under ``init_empty_weights``: only this stage's (tensor-parallel
+            # slices of the) parameters are ever allocated, directly on the training device
+            from ..utils.device_to_meta import materialize_meta
+            std = float(getattr(self.config, "initializer_range", 0.02) or 0.02)
+            materialize_meta(self, device, init_std=std)
+            for spec in self.tied_local.values():          # the tied tensors are new objects now
+                for idx, name in spec["uses"]:
+                    if self.local_start <= idx < self.local_stop:
+                        spec["param"] = dict(self.all_layers[idx].named_parameters())[name]
+                        break
         self.to(device)
         self._broadcast_model()
 

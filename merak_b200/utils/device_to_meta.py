@@ -30,9 +30,13 @@ def init_empty_weights(include_buffers: bool = False):
 def materialize_meta(module: nn.Module, device, init_std: float = 0.02, dtype=None):
     """Allocates every ``meta`` parameter / buffer of ``module`` on ``device`` and initialises it:
     normal(0, std) for matrices and embeddings, ones for norm weights, zeros for biases."""
+    done = {}       # a parameter shared by several modules (tied embeddings) stays one tensor
     for m in module.modules():
         for name, p in list(m._parameters.items()):
             if p is None or p.device.type != "meta":
+                continue
+            if id(p) in done:
+                m._parameters[name] = done[id(p)]
                 continue
             t = torch.empty(p.shape, dtype=dtype or p.dtype, device=device)
             if p.dim() >= 2:
@@ -41,7 +45,11 @@ def materialize_meta(module: nn.Module, device, init_std: float = 0.02, dtype=No
                 t.fill_(1.0)
             else:
                 t.zero_()
-            m._parameters[name] = nn.Parameter(t, requires_grad=p.requires_grad)
+            new = nn.Parameter(t, requires_grad=p.requires_grad)
+            for attr, val in vars(p).items():          # model_parallel, sequence_parallel, ... tags
+                setattr(new, attr, val)
+            done[id(p)] = new
+            m._parameters[name] = new
         for name, b in list(m._buffers.items()):
             if b is not None and b.device.type == "meta":
                 m._buffers[name] = torch.zeros(b.shape, dtype=b.dtype, device=device)

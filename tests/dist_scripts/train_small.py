@@ -40,6 +40,8 @@ def main():
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--save_dir", default=None)
     ap.add_argument("--resume", default=None)
+    ap.add_argument("--n_head", type=int, default=0)
+    ap.add_argument("--meta", type=int, default=0)
     ap.add_argument("--comm", default="nccl")
     ap.add_argument("--clip", type=float, default=1.0)
     ap.add_argument("--out", required=True)
@@ -48,8 +50,13 @@ def main():
     Merak.init(o.pp, o.tp, o.dp, sp=o.sp, ep=o.ep, backend="gloo" if o.device == "cpu" else "nccl")
     torch.manual_seed(1234)
     V, L = 512, 32
+    import contextlib
+    build_ctx = Merak.init_empty_weights() if o.meta else contextlib.nullcontext()
+    build_ctx.__enter__()
     if o.model == "gpt2":
-        model = GPT2LMHeadModel(gpt2_config("gpt2-tiny", vocab_size=V, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0))
+        over = dict(n_head=o.n_head, n_embd=32 * o.n_head) if o.n_head else {}
+        model = GPT2LMHeadModel(gpt2_config("gpt2-tiny", vocab_size=V, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
+                                            **over))
         task = "causal"
     elif o.model == "bert":
         model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=0.0))
@@ -61,6 +68,7 @@ def main():
     else:
         model = LlamaForCausalLM(llama_config("llama-tiny", vocab_size=V))
         task = "causal"
+    build_ctx.__exit__(None, None, None)
     args = Merak.MerakArguments(
         output_dir=o.save_dir or "/tmp/merak_b200_test", per_device_train_batch_size=o.mbs,
         gradient_accumulation_steps=o.gas, max_steps=o.steps, logging_steps=0, learning_rate=1e-3 if o.model == "gpt2" else 3e-3,

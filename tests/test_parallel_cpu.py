@@ -84,6 +84,20 @@ def test_tp2_megatron_sequence_parallel_with_biases(tmp_path, baseline, model):
     assert_close(got, baseline[model])
 
 
+def test_tp2_uneven_attention_heads(tmp_path):
+    """Five heads over two tensor-parallel ranks (3 + 2): heads are never split between ranks."""
+    single = run_layout(tmp_path, "h5_single", 1, ["--n_head", "5", "--steps", "4"])
+    tp2 = run_layout(tmp_path, "h5_tp2", 2, ["--n_head", "5", "--steps", "4", "--tp", "2"])
+    assert_close(tp2, single)
+
+
+def test_meta_device_model_materialises_per_stage(tmp_path):
+    """A model built under ``init_empty_weights`` is traced, split and tensor-parallelised on the meta
+    device; every rank allocates and initialises only its own stage's slices, and training converges."""
+    got = run_layout(tmp_path, "meta_pp2tp2", 4, ["--meta", "1", "--pp", "2", "--tp", "2", "--steps", "6"])
+    assert got[-1] < got[0] - 0.3, got
+
+
 def test_moe_expert_parallel_and_pipeline(tmp_path):
     """Mixture-of-experts model: experts split over two expert-parallel ranks (tokens exchanged by
     all-to-all, expert gradients kept out of the data-parallel reduction) and a two-stage pipeline
