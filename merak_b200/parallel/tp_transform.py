@@ -248,9 +248,10 @@ def _enter_sequence_parallel(model: nn.Module, seq_dim: int):
             # other replicated layers of the same head (BERT's transform) still run on this rank's
             # tokens only: their gradients are summed over the group like the norms'
             proj = {id(p) for p in lin.parameters()}
-            for p in owner.parameters():
-                if id(p) not in proj and not getattr(p, "model_parallel", False):
-                    p.sequence_parallel = True
+            if owner is not model:      # a dedicated head module; the root model owns everything else too
+                for p in owner.parameters():
+                    if id(p) not in proj and not getattr(p, "model_parallel", False):
+                        p.sequence_parallel = True
 
 
 class _GatherThenLinear(nn.Module):
