@@ -246,6 +246,14 @@ class PipelineEngine:
         self.data_iter = data_iter
         self.total_loss = None
         self._grads_reduced = False
+        if getattr(self.args, "failure_detection_timeout", 0) and dist.is_initialized() and dist.get_world_size() > 1:
+            if getattr(self, "_failure_detector", None) is None:
+                from ..utils.failure import FailureDetector
+                self._failure_detector = FailureDetector(timeout_s=float(self.args.failure_detection_timeout))
+            self._failure_detector.step_barrier(self.global_steps)      # raises RankFailureError
+            if self.device.type == "cuda":
+                from ..utils.failure import check_device_status
+                check_device_status()                                   # raises DeviceWaitTimeout
         if self.wall_clock_breakdown:
             self.timers("train_batch").start()
         if self._graph_capable():
