@@ -73,6 +73,12 @@ struct NormFwdParams {
   int params_f32;
 };
 
+constexpr int kNormSlots = 32;     // accumulator rows of the weight / bias gradient partial sums
+
+__device__ __forceinline__ void red_add_f4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 template <int THREADS, int kMaxVecPerThread>
 __global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const NormFwdParams p) {
   __shared__ float red[THREADS / 32];
@@ -176,7 +182,8 @@ struct NormBwdParams {
 };
 
 template <int THREADS, int kMaxVecPerThread>
-__global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p) {
+__global__ void __launch_bounds__(THREADS, (THREADS == 128 && kMaxVecPerThread == 1) ? 8 : 1)
+norm_bwd_kernel(const NormBwdParams p) {
   __shared__ float red[THREADS / 32];
   const int nvec = p.H / 8;
   const bool drop = p.rng != nullptr && p.p_drop > 0.f && p.dx != nullptr;
@@ -189,18 +196,43 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p
 #pragma unroll
     for (int i = 0; i < 8; ++i) { dg[it][i] = 0.f; db[it][i] = 0.f; }
 
+  // The loads of the next row are issued before the reductions of the current one, so a block keeps
+  // two rows in flight instead of stalling on DRAM between its block-wide sums.
+  uint4 raw_dy[kMaxVecPerThread], raw_z[kMaxVecPerThread];
+  auto fetch = [&](long long row) {
+#pragma unroll
+    for (int it = 0; it < kMaxVecPerThread; ++it) {
+      const int vi = threadIdx.x + it * THREADS;
+      if (vi < nvec && row < p.M) {
+        raw_dy[it] = __ldg(reinterpret_cast<const uint4*>(p.dy + row * p.H + vi * 8));
+        raw_z[it] = __ldg(reinterpret_cast<const uint4*>(p.z + row * p.H + vi * 8));
+      }
+    }
+  };
+  auto unpack8 = [](const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = unpack_bf16x2(w[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  };
+  fetch(blockIdx.x);
   for (long long row = blockIdx.x; row < p.M; row += gridDim.x) {
     const float mean = p.mean ? p.mean[row] : 0.f;
     const float rstd = p.rstd[row];
     float xh[kMaxVecPerThread][8], dxh[kMaxVecPerThread][8];
     float s1 = 0.f, s2 = 0.f;
+    float dyv_all[kMaxVecPerThread][8];
+#pragma unroll
+    for (int it = 0; it < kMaxVecPerThread; ++it) {
+      const int vi = threadIdx.x + it * THREADS;
+      if (vi < nvec) { unpack8(raw_dy[it], dyv_all[it]); unpack8(raw_z[it], xh[it]); }
+    }
+    fetch(row + gridDim.x);
 #pragma unroll
     for (int it = 0; it < kMaxVecPerThread; ++it) {
       const int vi = threadIdx.x + it * THREADS;
       if (vi < nvec) {
-        float dyv[8], g[8];
-        load8(p.dy + row * p.H + vi * 8, dyv);
-        load8(p.z + row * p.H + vi * 8, xh[it]);
+        float g[8];
+        float (&dyv)[8] = dyv_all[it];
         load8p(p.gamma, vi * 8, p.params_f32, g);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -242,36 +274,40 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const NormBwdParams p
       }
     }
   }
-  // every thread owns distinct columns: store this block's partial sums, reduced by a second kernel
-  float* pg = p.partial + (long long)blockIdx.x * 2 * p.H;
+  // every thread owns distinct columns: add this block's partial sums into one of kNormSlots
+  // accumulator rows (zero before the launch); a second kernel sums the rows and clears them again
+  float* pg = p.partial + (long long)(blockIdx.x % kNormSlots) * 2 * p.H;
 #pragma unroll
   for (int it = 0; it < kMaxVecPerThread; ++it) {
     const int vi = threadIdx.x + it * THREADS;
     if (vi < nvec) {
-      reinterpret_cast<float4*>(pg + vi * 8)[0] = make_float4(dg[it][0], dg[it][1], dg[it][2], dg[it][3]);
-      reinterpret_cast<float4*>(pg + vi * 8)[1] = make_float4(dg[it][4], dg[it][5], dg[it][6], dg[it][7]);
-      reinterpret_cast<float4*>(pg + p.H + vi * 8)[0] = make_float4(db[it][0], db[it][1], db[it][2], db[it][3]);
-      reinterpret_cast<float4*>(pg + p.H + vi * 8)[1] = make_float4(db[it][4], db[it][5], db[it][6], db[it][7]);
+      red_add_f4(pg + vi * 8, dg[it][0], dg[it][1], dg[it][2], dg[it][3]);
+      red_add_f4(pg + vi * 8 + 4, dg[it][4], dg[it][5], dg[it][6], dg[it][7]);
+      red_add_f4(pg + p.H + vi * 8, db[it][0], db[it][1], db[it][2], db[it][3]);
+      red_add_f4(pg + p.H + vi * 8 + 4, db[it][4], db[it][5], db[it][6], db[it][7]);
     }
   }
 }
 
 __global__ void __launch_bounds__(256)
-norm_bwd_reduce_kernel(const float* __restrict__ partial, int blocks, int H, float* __restrict__ dgamma,
+norm_bwd_reduce_kernel(float* __restrict__ partial, int blocks, int H, float* __restrict__ dgamma,
                        float* __restrict__ dbeta) {
   // grid.y = 0: gamma, 1: beta; 8 row-lanes x 32 columns per block
   const int col = blockIdx.x * 32 + (threadIdx.x & 31);
   const int rl = threadIdx.x >> 5;
   const int which = blockIdx.y;
-  float* out = which == 0 ? dgamma : dbeta;
-  if (out == nullptr) return;
+  float* out = which == 0 ? dgamma : dbeta;     // may be null (RMSNorm has no bias): the rows are still cleared
   float acc = 0.f;
   if (col < H)
-    for (int b = rl; b < blocks; b += 8) acc += partial[((long long)b * 2 + which) * H + col];
+    for (int b = rl; b < blocks; b += 8) {
+      float* slot = partial + ((long long)b * 2 + which) * H + col;
+      acc += *slot;
+      *slot = 0.f;            // leave the accumulator rows clean for the next call
+    }
   __shared__ float sm[8][33];
   sm[rl][threadIdx.x & 31] = acc;
   __syncthreads();
-  if (rl == 0 && col < H) {
+  if (rl == 0 && col < H && out != nullptr) {
     for (int k = 1; k < 8; ++k) acc += sm[k][threadIdx.x & 31];
     out[col] = acc;
   }
@@ -310,7 +346,8 @@ MRK_API int mrk_norm_fwd(const void* x, const void* residual, const void* gamma,
 }
 
 // Number of workspace rows (each 2*H floats) mrk_norm_bwd may use.
-MRK_API int mrk_norm_bwd_workspace_rows() { return sm_count() * 8; }
+// The workspace must be zero before the first call; every call leaves it zero again.
+MRK_API int mrk_norm_bwd_workspace_rows() { return kNormSlots; }
 
 MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, const void* gamma, const float* mean,
                          const float* rstd, void* dres, void* dx, float* dgamma, float* dbeta, float* workspace,
@@ -330,7 +367,7 @@ MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, co
   else launch_norm_bwd<256, 4>(p, grid, s);
   MRK_CHECK_LAUNCH();
   dim3 rgrid((H + 31) / 32, 2);
-  norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(workspace, (int)grid, H, dgamma, dbeta);
+  norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(workspace, kNormSlots, H, dgamma, dbeta);
   MRK_CHECK_LAUNCH();
   return 0;
 }
@@ -346,9 +383,9 @@ MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, co
 // -------------------------------------------------------------------------------------------------
 namespace mrk {
 constexpr int kNoAllocMaxH = 2048;        // largest hidden size served
-constexpr int kNoAllocMaxBlocks = 296;    // partial-sum rows (two per SM on a 148-SM part)
-// 296 * 2 * 2048 floats = 4.6 MiB, resident on every GPU that loads this library, until exit.
-static __device__ __align__(256) float g_norm_noalloc_scratch[kNoAllocMaxBlocks * 2 * kNoAllocMaxH];
+// kNormSlots * 2 * 2048 floats = 512 KiB, resident on every GPU that loads this library, until exit.
+// Device arrays start out zero, and every call leaves the accumulator rows zero again.
+static __device__ __align__(256) float g_norm_noalloc_scratch[kNormSlots * 2 * kNoAllocMaxH];
 
 // Device address of the array above, per device.  The symbol's name is only a host-side handle;
 // the address a kernel can use has to be asked for, with the device in question current.
@@ -384,14 +421,15 @@ MRK_API int mrk_norm_bwd_noalloc(const void* dy, const void* z, const void* dz_e
                   rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, scratch,
                   nullptr, 0ull, 0.f, M, H, rms, params_f32};
   cudaStream_t s = (cudaStream_t)stream;
-  const unsigned grid = (unsigned)(M < kNoAllocMaxBlocks ? M : kNoAllocMaxBlocks);
-  // Every block overwrites its whole row of partial sums before the reduction reads rows
-  // [0, grid), so nothing in the shared array has to start at zero.
+  const long long cap = (long long)sm_count() * 8;
+  const unsigned grid = (unsigned)(M < cap ? M : cap);
+  // Blocks add their partial sums into the kNormSlots accumulator rows; the reduction kernel sums
+  // the rows and clears them, so the array is zero again when the next call starts.
   if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
   else launch_norm_bwd<128, 2>(p, grid, s);
   MRK_CHECK_LAUNCH();
   dim3 rgrid((H + 31) / 32, 2);
-  norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(scratch, (int)grid, H, dgamma, dbeta);
+  norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(scratch, kNormSlots, H, dgamma, dbeta);
   MRK_CHECK_LAUNCH();
   return 0;
 }

@@ -6,7 +6,7 @@
 // memory-pool callback, a process whose whole GPU memory was handed out up front, or an embedding
 // application that may launch kernels but must not call cudaMalloc.  Such callers cannot supply the
 // partial-sum workspace mrk_norm_bwd asks for, so here the workspace is a fixed array inside the
-// library (4.6 MiB per GPU, held from library load until the process exits).
+// library (512 KiB per GPU, held from library load until the process exits).
 //
 // Differences from mrk_norm_bwd:
 //   * no workspace argument and no dropout (rng) arguments; everything else means the same;
@@ -15,9 +15,8 @@
 //   * the first call on each device looks up the device address of the built-in array; make that
 //     first call with the device current and before any stream capture is started;
 //   * all calls share the one array: two calls that may overlap on the same GPU (different
-//     streams, different threads) race on it and must be ordered by the caller.  The array keeps
-//     whatever the previous call left; every call overwrites the part it reads, so stale
-//     contents are never observed.
+//     streams, different threads) race on it and must be ordered by the caller.  The array is
+//     zero when the library is loaded and every call leaves it zero again.
 //   * it calls no cudaMalloc / cudaFree and no allocating library routine.
 #pragma once
 #ifdef __cplusplus

@@ -89,7 +89,7 @@ class _FusedNorm(torch.autograd.Function):
         dgamma = torch.empty(H, dtype=torch.float32, device=dy.device)
         dbeta = torch.empty(H, dtype=torch.float32, device=dy.device) if has_bias else None
         lib = _lib.kernels()
-        ws = torch.empty((lib.mrk_norm_bwd_workspace_rows(), 2, H), dtype=torch.float32, device=dy.device)
+        ws = _workspace(dy.device, H, lib)
         rc = lib.mrk_norm_bwd(
             dy2.data_ptr(), z.data_ptr(), _lib.ptr(e2), weight.data_ptr(), _lib.ptr(mean), rstd.data_ptr(),
             dres.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), _lib.ptr(dbeta), ws.data_ptr(), _lib.ptr(rng), call_id,
@@ -108,6 +108,20 @@ def _param_grad(param, grad_f32):
         mg.add_(grad_f32.view(mg.shape))
         return None
     return grad_f32.to(param.dtype)
+
+
+_WORKSPACES = {}
+
+
+def _workspace(device, H, lib):
+    """Accumulator rows for the weight / bias gradient partial sums: zero on creation, and every
+    backward call leaves them zero again, so one buffer per (device, hidden size) serves all calls
+    issued in stream order."""
+    key = (device.index, H, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = _WORKSPACES[key] = torch.zeros((lib.mrk_norm_bwd_workspace_rows(), 2, H), dtype=torch.float32, device=device)
+    return ws
 
 
 def fused_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,

@@ -3,7 +3,7 @@
 
     python -m merak_b200.ops.profile_cases <case> [--iters N]
 
-Cases: gemm, gemm_gelu, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce.
+Cases: gemm, gemm_gelu, gemm_k1024, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce.
 Each prints the CUDA-event time per launch and the achieved TFLOP/s or GB/s.  The multi-rank
 kernels run with all ranks' buffers on this one GPU and the cross-rank barriers pre-satisfied, so
 they measure the kernels' data path, not NVLink.
@@ -46,8 +46,8 @@ def main():
     bf = torch.bfloat16
     lib = _lib.kernels()
     it = o.iters
-    if o.case in ("gemm", "gemm_gelu"):
-        M, N, K = 16384, 4096, 4096
+    if o.case in ("gemm", "gemm_gelu", "gemm_k1024"):
+        M, N, K = (16384, 4096, 4096) if o.case != "gemm_k1024" else (16384, 3072, 1024)
         a = torch.randn(M, K, device=dev, dtype=bf)
         b = torch.randn(N, K, device=dev, dtype=bf) * 0.02
         bias = torch.randn(N, device=dev, dtype=bf)

@@ -56,7 +56,7 @@ def _ptr(t):
 def test_noalloc_matches_regular_entry_point_twice(rms):
     lib = _lib()
     stream = torch.cuda.current_stream().cuda_stream
-    # two different problems back to back: the second one reuses the scratch the first one filled,
+    # two different problems back to back: the second one reuses the scratch the first one used (and cleared),
     # with a different row count and hidden size
     for M, H, seed in ((3000, 1024, 1), (333, 1600, 2)):
         dy, z, extra, gamma, mean, rstd = _case(M, H, rms, seed)
@@ -66,7 +66,7 @@ def test_noalloc_matches_regular_entry_point_twice(rms):
             dgamma = torch.full((H,), float("nan"), device="cuda")
             dbeta = None if rms else torch.full((H,), float("nan"), device="cuda")
             if which == "regular":
-                ws = torch.empty((lib.mrk_norm_bwd_workspace_rows(), 2, H), device="cuda")
+                ws = torch.zeros((lib.mrk_norm_bwd_workspace_rows(), 2, H), device="cuda")   # must start at zero
                 rc = lib.mrk_norm_bwd(dy.data_ptr(), z.data_ptr(), extra.data_ptr(), gamma.data_ptr(), _ptr(mean),
                                       rstd.data_ptr(), dres.data_ptr(), dres.data_ptr(), dgamma.data_ptr(),
                                       _ptr(dbeta), ws.data_ptr(), 0, 0, 0.0, M, H, int(rms), 0, stream)
