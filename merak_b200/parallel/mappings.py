@@ -219,8 +219,20 @@ def _all_to_all(x, scatter_dim, gather_dim, group, n):
         return x
     parts = [c.contiguous() for c in x.chunk(n, dim=scatter_dim)]
     send = torch.cat(parts, 0)
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
+    recv = None
+    if send.is_cuda:
+        # peer-mapped group: every rank stores its blocks straight into the destinations' buffers
+        # (the push all-to-all kernel of the expert-parallel path) instead of a library collective
+        from . import expert
+        comm = expert.get_ep_comm(group, send.device)
+        per = parts[0].shape[0]
+        flat = send.reshape(n * per, -1)
+        if comm is not None and (flat.shape[1] * flat.element_size()) % 16 == 0:
+            begin = [k * per for k in range(n + 1)]
+            recv = comm.push(flat, begin, [comm.rank * per] * n, n * per, worst_rows=n * per).view_as(send)
+    if recv is None:
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
     return torch.cat(list(recv.chunk(n, dim=0)), dim=gather_dim)
 
 

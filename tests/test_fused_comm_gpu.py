@@ -281,3 +281,14 @@ def test_moe_expert_parallel_fused_matches_nccl_two_gpus(tmp_path):
     assert fused[-1] < fused[0]
     for a, b in zip(fused, ref):
         assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (fused, ref)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ulysses_sequence_parallel_fused_matches_nccl_two_gpus(tmp_path):
+    """Ulysses head/sequence all-to-all through the peer-store kernel against all_to_all_single."""
+    base = ["--model", "llama", "--sp", "2", "--steps", "6", "--gas", "2"]
+    ref = _run(tmp_path, "nccl", 2, base + ["--comm", "nccl"])
+    fused = _run(tmp_path, "fused", 2, base + ["--comm", "fused"])
+    assert fused[-1] < fused[0]
+    for a, b in zip(fused, ref):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (fused, ref)
