@@ -3,7 +3,8 @@
 
     python -m merak_b200.ops.profile_cases <case> [--iters N]
 
-Cases: gemm, gemm_gelu, gemm_k1024, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce.
+Cases: gemm, gemm_gelu, gemm_k1024, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce,
+cross_entropy, rope, swiglu, embedding, colsum, moe_push.
 Each prints the CUDA-event time per launch and the achieved TFLOP/s or GB/s.  The multi-rank
 kernels run with all ranks' buffers on this one GPU and the cross-rank barriers pre-satisfied, so
 they measure the kernels' data path, not NVLink.
@@ -139,6 +140,71 @@ def main():
             ms = _time(lambda: _lib.check(lib.mrk_tp_reduce_pull(pt, ct, n, 0, out.data_ptr(), M // n, N, seg, None, 1,
                                                                  0, 50, _lib.stream_ptr()), "pull"), it)
             print("tp_reduce_pull %dx%d from %d ranks: %.3f ms  %.0f GB/s" % (M // n, N, n, ms, (n + 1) * (M // n) * N * 2 / ms / 1e6))
+    elif o.case == "cross_entropy":
+        from .cross_entropy import softmax_cross_entropy
+        M, V = 8192, 30522
+        logits = (torch.randn(M, V, device=dev, dtype=bf) * 2).requires_grad_(True)
+        labels = torch.randint(0, V, (M,), device=dev)
+        labels[::7] = -100
+
+        def run():
+            loss = softmax_cross_entropy(logits, labels)
+            torch.autograd.grad(loss, logits)
+        ms = _time(run, it)
+        # forward reads the logits once, backward reads them again and writes the gradient
+        print("cross_entropy fwd+bwd %dx%d: %.3f ms  %.0f GB/s" % (M, V, ms, 3.0 * M * V * 2 / ms / 1e6))
+    elif o.case == "rope":
+        from .elementwise import apply_rope, rope_tables
+        B, L, H, D = 8, 4096, 32, 128
+        x = torch.randn(B, L, H, D, device=dev, dtype=bf)
+        cos, sin = rope_tables(L, D, 10000.0, dev)
+        with torch.no_grad():
+            ms = _time(lambda: apply_rope(x, cos, sin), it)
+        print("rope B%d L%d H%d D%d: %.3f ms  %.0f GB/s" % (B, L, H, D, ms, 2.0 * x.numel() * 2 / ms / 1e6))
+    elif o.case == "swiglu":
+        from .elementwise import swiglu
+        M, F = 16384, 11008
+        gu = torch.randn(M, 2 * F, device=dev, dtype=bf, requires_grad=True)
+        with torch.no_grad():
+            ms = _time(lambda: swiglu(gu), it)
+        print("swiglu fwd %dx%d: %.3f ms  %.0f GB/s" % (M, F, ms, 3.0 * M * F * 2 / ms / 1e6))
+        y = swiglu(gu)
+        dy = torch.randn_like(y)
+        ms = _time(lambda: torch.autograd.grad(y, gu, dy, retain_graph=True), it)
+        print("swiglu bwd %dx%d: %.3f ms  %.0f GB/s" % (M, F, ms, 5.0 * M * F * 2 / ms / 1e6))
+    elif o.case == "embedding":
+        from .elementwise import embedding_sum
+        T, H, V = 65536, 1024, 30522
+        table = torch.randn(V, H, device=dev, dtype=bf, requires_grad=True)
+        ids = torch.randint(0, V, (64, T // 64), device=dev)
+        with torch.no_grad():
+            ms = _time(lambda: embedding_sum([ids], [table]), it)
+        print("embedding fwd %d tokens x %d: %.3f ms  %.0f GB/s" % (T, H, ms, 2.0 * T * H * 2 / ms / 1e6))
+        out = embedding_sum([ids], [table])
+        dy = torch.randn_like(out)
+        ms = _time(lambda: torch.autograd.grad(out, table, dy, retain_graph=True), it)
+        print("embedding bwd %d tokens x %d: %.3f ms" % (T, H, ms))
+    elif o.case == "colsum":
+        from .elementwise import colsum
+        M, N = 16384, 4096
+        x = torch.randn(M, N, device=dev, dtype=bf)
+        out = torch.zeros(N, device=dev)
+        ms = _time(lambda: colsum(x, out), it)
+        print("colsum %dx%d: %.3f ms  %.0f GB/s" % (M, N, ms, M * N * 2 / ms / 1e6))
+    elif o.case == "moe_push":
+        n, H = 2, 2048
+        rows = 24576                                  # 4096 tokens x top-6 per rank
+        sends = [torch.randn(rows, H, device=dev, dtype=bf) for _ in range(n)]
+        recvs = [torch.empty(rows, H, device=dev, dtype=bf) for _ in range(n)]
+        ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(n)]
+        rt, ct = _table([r.data_ptr() for r in recvs]), _table([c.data_ptr() for c in ctrls])
+        half = rows // 2
+        sb = (ctypes.c_longlong * (n + 1))(0, half, rows)
+        dr = (ctypes.c_longlong * n)(0, 0)             # rank 0's blocks go first in every destination
+        ms = _time(lambda: _lib.check(lib.mrk_moe_alltoall_push(rt, ct, n, 0, sends[0].data_ptr(), sb, dr, H, 2, 1, 0,
+                                                                50, _lib.stream_ptr()), "push"), it)
+        print("moe_alltoall_push %d rows x %d (one rank, both destinations on this GPU): %.3f ms  %.0f GB/s" % (
+            rows, H, ms, 2.0 * rows * H * 2 / ms / 1e6))
     else:
         raise SystemExit("unknown case " + o.case)
     torch.cuda.synchronize()
