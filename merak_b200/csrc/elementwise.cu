@@ -377,6 +377,48 @@ rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, 
   }
 }
 
+// 16-byte variant: a thread rotates 8 (low, high) pairs; needs D % 16 == 0 and 16-byte aligned rows.
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, const float* __restrict__ cosb,
+                const float* __restrict__ sinb, const long long* __restrict__ pos, long long B, int L, int H, int D,
+                long long sb, long long ss, long long sh, long long ysb, long long yss, long long ysh, int inverse) {
+  const int half = D / 2;
+  const int groups = half / 8;
+  const long long total = B * L * H * (long long)groups;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int pj = (int)(i % groups) * 8;
+    long long r = i / groups;
+    const int h = (int)(r % H); r /= H;
+    const int l = (int)(r % L);
+    const long long b = r / L;
+    const long long p = pos ? pos[b * L + l] : l;
+    const __nv_bfloat16* src = x + b * sb + l * ss + h * sh;
+    __nv_bfloat16* dst = y + b * ysb + l * yss + h * ysh;
+    const uint4 lo4 = *reinterpret_cast<const uint4*>(src + pj);
+    const uint4 hi4 = *reinterpret_cast<const uint4*>(src + half + pj);
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cosb + p * half + pj));
+    const float4 c1 = __ldg(reinterpret_cast<const float4*>(cosb + p * half + pj) + 1);
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sinb + p * half + pj));
+    const float4 s1 = __ldg(reinterpret_cast<const float4*>(sinb + p * half + pj) + 1);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    if (inverse) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sn[k] = -sn[k];
+    }
+    const uint32_t lw[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hw[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+    uint32_t ol[4], oh[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 lo = unpack_bf16x2(lw[k]), hi = unpack_bf16x2(hw[k]);
+      ol[k] = pack_bf16x2(lo.x * c[2 * k] - hi.x * sn[2 * k], lo.y * c[2 * k + 1] - hi.y * sn[2 * k + 1]);
+      oh[k] = pack_bf16x2(hi.x * c[2 * k] + lo.x * sn[2 * k], hi.y * c[2 * k + 1] + lo.y * sn[2 * k + 1]);
+    }
+    *reinterpret_cast<uint4*>(dst + pj) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+    *reinterpret_cast<uint4*>(dst + half + pj) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+  }
+}
+
 // -------------------------------------------------------------------------------------------------
 // SwiGLU on a fused [M, 2F] gate|up tensor:  out = silu(gate) * up ;  backward writes [M, 2F].
 // -------------------------------------------------------------------------------------------------
@@ -640,6 +682,15 @@ MRK_API int mrk_rope(const void* x, void* y, const float* cosb, const float* sin
                      int L, int H, int D, long long sb, long long ss, long long sh, long long ysb, long long yss,
                      long long ysh, int inverse, void* stream) {
   MRK_REQUIRE(D % 4 == 0, "rope: head dim must be a multiple of 4");
+  const bool vec = D % 16 == 0 && ((sb | ss | sh | ysb | yss | ysh) % 8) == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0 &&
+                   (((uintptr_t)cosb | (uintptr_t)sinb) & 15) == 0;
+  if (vec) {
+    const long long total8 = B * L * H * (long long)(D / 16);
+    rope_vec_kernel<<<grid_for(total8, 256, 8), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (__nv_bfloat16*)y, cosb, sinb, pos, B, L, H, D, sb, ss, sh, ysb, yss, ysh, inverse);
+    MRK_CHECK_LAUNCH();
+    return 0;
+  }
   const long long total = B * L * H * (long long)(D / 4);
   rope_kernel<<<grid_for(total, 256, 8), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (__nv_bfloat16*)y, cosb, sinb, pos, B, L, H, D, sb, ss, sh, ysb, yss, ysh, inverse);

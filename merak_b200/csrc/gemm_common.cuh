@@ -49,6 +49,7 @@ struct GemmParams {
   unsigned* status;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
+  int tma_store;                  // the kernel may write C through shared memory + TMA stores (bf16, no accumulate)
   GemmComm comm;
 };
 
@@ -259,9 +260,15 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // Epilogue of one accumulator tile for one thread: `row` is this thread's output row, `t_row` the
 // TMEM address of its lane at the tile's first column, `col_base` the first output column of the
 // tile and `ncols` its width.  All 32 lanes of the warp call this together.
+// `stage` (optional): shared-memory staging of this warp group's 128 x 128 output block, laid out as
+// two 128-row x 64-column boxes in the 128-byte TMA swizzle; when given, the finished bf16 values go
+// there (row `r_in_tile`) instead of to global memory and the caller issues the TMA stores.  The
+// caller only passes it for tiles where that is legal (bf16 output, no accumulate, no split-K, and
+// either a full-width block or no side tensors).
 template <int kAct, int kAux>
 __device__ __noinline__ void epilogue_tile_t(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
-                                              int col_base, int ncols, bool split_k, bool first_split) {
+                                              int col_base, int ncols, bool split_k, bool first_split,
+                                              uint8_t* stage, int r_in_tile) {
   const bool out_f32 = (p.flags & MRK_GEMM_OUT_F32) != 0;
   const bool accumulate = (p.flags & MRK_GEMM_ACCUMULATE) != 0;
   const bool bias_f32 = (p.flags & MRK_GEMM_BIAS_F32) != 0;
@@ -281,17 +288,82 @@ for (int c = 0; c < ncols / 32; ++c) {
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
   const bool full = (col0 + 32 <= p.N);
   if (p.bias != nullptr && first_split) {
+    const bool bias_vec = full && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
     if (bias_f32) {
       const float* b = reinterpret_cast<const float*>(p.bias) + col0;
+      if (bias_vec) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (full || col0 + j < p.N) v[j] += __ldg(b + j);
+        for (int q = 0; q < 8; ++q) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(b) + q);
+          v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (full || col0 + j < p.N) v[j] += __ldg(b + j);
+      }
     } else {
       const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+      if (bias_vec) {       // the same 64 bytes for every lane: four broadcast loads instead of 32 scalar ones
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (full || col0 + j < p.N) v[j] += __bfloat162float(__ldg(b + j));
+        for (int q = 0; q < 4; ++q) {
+          const uint4 t = __ldg(reinterpret_cast<const uint4*>(b) + q);
+          const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16x2(w[e]);
+            v[8 * q + 2 * e] += f.x;
+            v[8 * q + 2 * e + 1] += f.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (full || col0 + j < p.N) v[j] += __bfloat162float(__ldg(b + j));
+      }
     }
+  }
+  if (stage != nullptr) {
+    // shared-memory staged output: side tensors are only present on full-width blocks here
+    if (p.aux_out != nullptr && row_ok) {
+      uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                            pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+    }
+    if (kAct != MRK_ACT_NONE && kAux != MRK_AUX_DACT) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act<kAct>(v[j]);
+    }
+    if (kAux != MRK_AUX_NONE && row_ok) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 a = __ldg(src + q);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(w[e]);
+          if (kAux == MRK_AUX_ADD) {
+            v[8 * q + 2 * e] += f.x;
+            v[8 * q + 2 * e + 1] += f.y;
+          } else {
+            v[8 * q + 2 * e] *= apply_act_grad<kAct>(f.x);
+            v[8 * q + 2 * e + 1] *= apply_act_grad<kAct>(f.y);
+          }
+        }
+      }
+    }
+    uint8_t* box = stage + (c >> 1) * 16384;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t off = sw128_offset((uint32_t)r_in_tile, (uint32_t)((c & 1) * 4 + q));
+      *reinterpret_cast<uint4*>(box + off) =
+          make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                     pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+    }
+    continue;
   }
   if (row_ok && split_k) {
     // partial sum of one K range: reduce into the fp32 output
@@ -398,8 +470,10 @@ for (int c = 0; c < ncols / 32; ++c) {
 // Picks the epilogue specialised for (activation, aux mode) once per tile, so the per-element code
 // has no run-time dispatch.
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
-                                              int col_base, int ncols, bool split_k, bool first_split) {
-#define MRK_EPI(ACT, AUX) epilogue_tile_t<ACT, AUX>(p, row, row_ok, t_row, col_base, ncols, split_k, first_split)
+                                              int col_base, int ncols, bool split_k, bool first_split,
+                                              uint8_t* stage = nullptr, int r_in_tile = 0) {
+#define MRK_EPI(ACT, AUX) \
+  epilogue_tile_t<ACT, AUX>(p, row, row_ok, t_row, col_base, ncols, split_k, first_split, stage, r_in_tile)
 #define MRK_EPI_ACT(ACT)                                             \
   do {                                                               \
     if (p.aux_mode == MRK_AUX_ADD) MRK_EPI(ACT, MRK_AUX_ADD);        \

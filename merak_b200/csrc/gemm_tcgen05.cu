@@ -257,7 +257,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
   return 0;
 }
 
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream);
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams& p,
+                     cudaStream_t stream);
 
 }  // namespace mrk
 
@@ -296,6 +297,7 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
   if (rc) return rc;
   GemmParams p;
   memset(&p.comm, 0, sizeof(p.comm));
+  p.tma_store = 0;
   if (comm != nullptr) p.comm = *comm;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
@@ -306,7 +308,18 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 512) return launch_gemm_pair(ta, tb, p, s);
+  if (bn == 512) {
+    // bf16 outputs that a tensor map can describe leave through shared memory + TMA stores
+    CUtensorMap tc = ta;
+    p.tma_store = 0;
+    if (!(flags & (MRK_GEMM_OUT_F32 | MRK_GEMM_ACCUMULATE)) && (ldc % 8) == 0 &&
+        (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+      rc = make_tmap_2d(&tc, C, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 128, 3);
+      if (rc) return rc;
+      p.tma_store = 1;
+    }
+    return launch_gemm_pair(ta, tb, tc, p, s);
+  }
   if (bn == 256) return launch<256>(ta, tb, p, s);
   if (bn == 128) return launch<128>(ta, tb, p, s);
   return launch<64>(ta, tb, p, s);

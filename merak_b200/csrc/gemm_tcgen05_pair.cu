@@ -9,7 +9,10 @@
 //
 //   warp 0   TMA producer (both CTAs; completion bytes are credited to the even CTA's barrier)
 //   warp 1   TMEM allocation (both CTAs); UMMA issue + commits (even CTA only)
-//   warps 2..9  epilogue of this CTA's 128 rows (two warps per TMEM lane quadrant, half the columns each)
+//   warps 2..9  epilogue of this CTA's 128 rows (two warps per TMEM lane quadrant, half the columns each).
+//               bf16 outputs are staged in shared memory (128-byte swizzled boxes) and written with TMA
+//               stores: full 128-byte lines instead of 16-byte pieces scattered over 32 rows per
+//               instruction, which is what made the epilogue the bottleneck of short-K problems.
 #include "gemm_common.cuh"
 #include "host_common.h"
 
@@ -19,20 +22,22 @@ constexpr int kPairBlockM = 256;      // rows per cluster tile (128 per CTA)
 constexpr int kPairBlockN = 256;
 constexpr int kPairBlockK = 64;
 constexpr int kPairThreads = 320;     // TMA warp, UMMA warp, 8 epilogue warps
-constexpr int kPairStages = 6;
+constexpr int kPairStages = 5;
 constexpr int kPairABytes = 128 * kPairBlockK * 2;            // this CTA's rows of A
 constexpr int kPairBBytes = (kPairBlockN / 2) * kPairBlockK * 2;  // this CTA's half of B
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;    // 32 KB
-constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + 1024 + 1024;
+constexpr int kPairStagingBytes = 2 * 32768;   // epilogue staging: two 128 x 128 bf16 blocks (TMA-store source)
+constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes + 1024 + 1024;
 
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                      const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   constexpr uint32_t kTmemCols = 512;   // two 256-column accumulator buffers
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* bar_base = smem + kPairStages * kPairStageBytes;
+  uint8_t* staging = smem + kPairStages * kPairStageBytes;
+  uint8_t* bar_base = staging + kPairStagingBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);       // used in the even CTA only
   uint64_t* empty_bar = full_bar + kPairStages;                     // one per CTA
   uint64_t* tmem_full_bar = empty_bar + kPairStages;                // one per CTA
@@ -60,6 +65,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.tma_store) tma_prefetch_desc(&tma_c);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
@@ -159,6 +165,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     // ------------------------------- epilogue (both CTAs) -------------------------------
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
+    // two warps share a TMEM lane quadrant: warps 2..5 take the left half of the columns, 6..9 the right
+    const int half = (warp - 2) >> 2;
+    uint8_t* stage = staging + half * 32768;
+    const bool store_thread = (warp == 2 + half * 4) && lane == 0;     // issues this half's TMA stores
+    bool staged_before = false;
     int iter = 0;
     bool ok = true;
     for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++iter) {
@@ -172,16 +183,36 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const long long row = (long long)m_blk * kPairBlockM + (long long)cta * 128 + row_in_tile;
+      const long long row0 = (long long)m_blk * kPairBlockM + (long long)cta * 128;
+      const long long row = row0 + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kPairBlockN;
-      // two warps share a TMEM lane quadrant: warps 2..5 take the left half of the columns, 6..9 the right
-      const int half = (warp - 2) >> 2;
-      epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), n_blk * kPairBlockN + half * (kPairBlockN / 2),
-                    kPairBlockN / 2, split_k, first_split);
+      const int col_half = n_blk * kPairBlockN + half * (kPairBlockN / 2);
+      // staged output for this block? (uniform over the four warps of the half)
+      const bool staged = p.tma_store && !split_k && col_half < p.N &&
+                          (col_half + kPairBlockN / 2 <= p.N || (p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr));
+      if (staged_before) {       // the previous block's TMA stores must have read the staging buffer
+        if (store_thread) tma_store_wait_read<0>();
+        named_bar_sync(1 + half, 128);
+      }
+      epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k, first_split,
+                    staged ? stage : nullptr, row_in_tile);
       tc_fence_before();
-      mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));    // TMEM is free; stores go on below
+      if (staged) {
+        fence_proxy_async_smem();
+        named_bar_sync(1 + half, 128);
+        if (store_thread && row0 < p.M) {
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+            if (col_half + b * 64 < p.N)
+              tma_store_2d(&tma_c, smem_u32(stage + b * 16384), col_half + b * 64, (int32_t)row0);
+          tma_store_commit();
+        }
+      }
+      staged_before = staged;
     }
+    if (store_thread) tma_store_wait_read<0>();     // shared memory stays valid until the last store has read it
   }
 
   tc_fence_before();
@@ -195,7 +226,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   }
 }
 
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t stream) {
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams& p,
+                     cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   MRK_CUDA_OK(cudaGetDevice(&dev));
@@ -236,7 +268,8 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, p));
+  if (p.num_splits > 1) p.tma_store = 0;
+  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, tc, p));
   count_launch();
   return 0;
 }
