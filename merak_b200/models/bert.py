@@ -23,7 +23,7 @@ from ..ops import gemm as G
 from ..ops.attention import flash_attention, flash_attention_packed
 from ..ops.cross_entropy import softmax_cross_entropy
 from ..ops.elementwise import dropout, embedding_sum
-from ..ops.linear import linear as k_linear, mlp as k_mlp
+from ..ops.linear import linear as k_linear, linear_fork, mlp as k_mlp, mlp_fork as k_mlp_fork
 from ..ops.modules import LayerNorm, Linear, expose_fused_projection
 from ..ops.norm import fused_norm
 
@@ -75,14 +75,21 @@ class BertSelfAttention(nn.Module):
         self.qkv.fused_parts = 3
         expose_fused_projection(self, "qkv", ("query", "key", "value"))
 
-    def forward(self, x, key_bias=None):
-        qkv = self.qkv(x)
+    def forward(self, x, key_bias=None, fork: bool = False):
+        """``fork=True`` also returns ``x`` for the residual connection (its gradient is then summed in
+        the QKV data-gradient GEMM, see ``ops.linear.linear_fork``)."""
+        x_res = x
+        if fork and type(self.qkv) is Linear:
+            qkv, x_res = linear_fork(x, self.qkv.weight, self.qkv.bias)
+        else:
+            qkv = self.qkv(x)
         B, L = qkv.shape[0], qkv.shape[1]     # the projection may have gathered the sequence
         local = qkv.shape[-1] // 3
         heads = local // self.attention_head_size
         qkv = qkv.view(B, L, 3 * heads, self.attention_head_size)
         ctx = flash_attention_packed(qkv, heads, heads, key_bias=key_bias, causal=False)
-        return ctx.reshape(B, L, local)
+        ctx = ctx.reshape(B, L, local)
+        return (ctx, x_res) if fork else ctx
 
 
 class BertSelfOutput(nn.Module):
@@ -103,7 +110,8 @@ class BertAttention(nn.Module):
         self.output = BertSelfOutput(config)
 
     def forward(self, x, key_bias=None):
-        return self.output(self.self(x, key_bias), x)
+        ctx, x_res = self.self(x, key_bias, fork=True)
+        return self.output(ctx, x_res)
 
 
 class BertIntermediate(nn.Module):
@@ -132,7 +140,7 @@ class BertLayer(nn.Module):
         a = self.attention(hidden_states, key_bias)
         fc1, fc2 = self.intermediate.dense, self.output.dense
         if type(fc1) is Linear and type(fc2) is Linear:
-            ff = k_mlp(a, fc1.weight, fc1.bias, fc2.weight, fc2.bias, self.intermediate.act)
+            ff, a = k_mlp_fork(a, fc1.weight, fc1.bias, fc2.weight, fc2.bias, self.intermediate.act)
         else:
             ff = fc2(G.act_forward(self.intermediate.act, fc1(a)))
         return self.output.LayerNorm(ff, residual=a, p_drop=self.output.p)

@@ -52,9 +52,13 @@ def _bias_grad(dy2, bias):
 
 
 class _Linear(torch.autograd.Function):
+    """``fork=True`` also returns the input (as an alias): a caller that feeds ``x`` both into this
+    layer and into a residual connection takes the residual from the second output, and the sum of
+    the two gradients of ``x`` then happens in the epilogue of the data-gradient GEMM instead of in
+    a separate elementwise kernel."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, residual):
+    def forward(ctx, x, weight, bias, residual, fork=False):
         N, K = weight.shape
         x2 = _as2d(x, K)
         r2 = _as2d(residual, N) if residual is not None else None
@@ -63,20 +67,27 @@ class _Linear(torch.autograd.Function):
         ctx.in_shape = x.shape
         ctx.has_res = residual is not None
         ctx.main_grad = getattr(weight, "main_grad", None)     # slices of stacked weights carry their own view
+        ctx.fork = fork
+        if fork:
+            ctx.set_materialize_grads(False)
+            return y.view(*x.shape[:-1], N), x.view_as(x)
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dx_extra=None):
         x2, weight, bias = ctx.saved_tensors
         N, K = weight.shape
+        if dy is None:           # fork: only the pass-through output was used
+            return dx_extra, None, None, None, None
         dy2 = _as2d(dy, N)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx2, _ = G.gemm(dy2, weight, b_mn=True)
+            e2 = _as2d(dx_extra, K) if dx_extra is not None else None
+            dx2, _ = G.gemm(dy2, weight, b_mn=True, aux_in=e2, aux_mode=G.AUX_ADD if e2 is not None else G.AUX_NONE)
             dx = dx2.view(ctx.in_shape)
         dw = _weight_grad(dy2, x2, weight, ctx.main_grad) if weight.requires_grad else None
         db = _bias_grad(dy2, bias)
-        return dx, dw, db, (dy if ctx.has_res else None)
+        return dx, dw, db, (dy if ctx.has_res else None), None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -86,13 +97,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             flop_counter.add(2 * (x.numel() // x.shape[-1]) * weight.shape[0] * weight.shape[1])
         y = F.linear(x, weight, bias)
         return y + residual if residual is not None else y
-    return _Linear.apply(x, weight, bias, residual)
+    return _Linear.apply(x, weight, bias, residual, False)
+
+
+def linear_fork(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """``(x W^T + b, x)``: use the second result wherever ``x`` is needed again (residual), see
+    :class:`_Linear`."""
+    if not _lib.use_kernels(x, weight) or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return linear(x, weight, bias), x
+    return _Linear.apply(x, weight, bias, None, True)
 
 
 class _MLP(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, x, w1, b1, w2, b2, act, residual):
+    def forward(ctx, x, w1, b1, w2, b2, act, residual, fork=False):
         F1, K = w1.shape
         N = w2.shape[0]
         x2 = _as2d(x, K)
@@ -101,12 +120,18 @@ class _MLP(torch.autograd.Function):
         y, _ = G.gemm(a, w2, bias=b2, aux_in=r2, aux_mode=G.AUX_ADD if r2 is not None else G.AUX_NONE)
         ctx.save_for_backward(x2, w1, b1, w2, b2, h, a)
         ctx.act, ctx.in_shape, ctx.has_res = act, x.shape, residual is not None
+        ctx.fork = fork
+        if fork:
+            ctx.set_materialize_grads(False)
+            return y.view(*x.shape[:-1], N), x.view_as(x)
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dx_extra=None):
         x2, w1, b1, w2, b2, h, a = ctx.saved_tensors
         N = w2.shape[0]
+        if dy is None:
+            return dx_extra, None, None, None, None, None, None, None
         dy2 = _as2d(dy, N)
         # dh = (dy W2) * act'(h): derivative applied in the GEMM epilogue
         dh, _ = G.gemm(dy2, w2, b_mn=True, act=ctx.act, aux_in=h, aux_mode=G.AUX_DACT)
@@ -114,11 +139,12 @@ class _MLP(torch.autograd.Function):
         db2 = _bias_grad(dy2, b2)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx2, _ = G.gemm(dh, w1, b_mn=True)
+            e2 = _as2d(dx_extra, w1.shape[1]) if dx_extra is not None else None
+            dx2, _ = G.gemm(dh, w1, b_mn=True, aux_in=e2, aux_mode=G.AUX_ADD if e2 is not None else G.AUX_NONE)
             dx = dx2.view(ctx.in_shape)
         dw1 = _weight_grad(dh, x2, w1) if w1.requires_grad else None
         db1 = _bias_grad(dh, b1)
-        return dx, dw1, db1, dw2, db2, None, (dy if ctx.has_res else None)
+        return dx, dw1, db1, dw2, db2, None, (dy if ctx.has_res else None), None
 
 
 def mlp(x, w1, b1, w2, b2, act: int = G.ACT_GELU_ERF, residual=None):
@@ -129,4 +155,11 @@ def mlp(x, w1, b1, w2, b2, act: int = G.ACT_GELU_ERF, residual=None):
         hdn = G.act_forward(act, F.linear(x, w1, b1))
         y = F.linear(hdn, w2, b2)
         return y + residual if residual is not None else y
-    return _MLP.apply(x, w1, b1, w2, b2, act, residual)
+    return _MLP.apply(x, w1, b1, w2, b2, act, residual, False)
+
+
+def mlp_fork(x, w1, b1, w2, b2, act: int = G.ACT_GELU_ERF):
+    """``(mlp(x), x)``: the second result carries ``x`` to the residual connection, see :class:`_Linear`."""
+    if not _lib.use_kernels(x, w1, w2) or x.dtype != torch.bfloat16:
+        return mlp(x, w1, b1, w2, b2, act), x
+    return _MLP.apply(x, w1, b1, w2, b2, act, None, True)

@@ -64,6 +64,8 @@ class _FusedNorm(torch.autograd.Function):
             float(p_drop), float(eps), M, H, int(rms), int(params_f32), _lib.stream_ptr())
         _lib.check(rc, "mrk_norm_fwd")
         ctx.save_for_backward(z, weight, mean, rstd, rng)
+        # an unused output must not cost a zero-filled gradient tensor (and a pass over it in the kernel)
+        ctx.set_materialize_grads(False)
         ctx.meta = (rms, p_drop, call_id, bias is not None, residual is not None, x.shape, params_f32)
         ctx.need_z = need_z
         if need_z:
@@ -75,6 +77,10 @@ class _FusedNorm(torch.autograd.Function):
         z, weight, mean, rstd, rng = ctx.saved_tensors
         rms, p_drop, call_id, has_bias, has_res, shape, params_f32 = ctx.meta
         H = shape[-1]
+        if dy is None:          # only the pre-norm sum was used downstream
+            if dz_extra is None:
+                return None, None, None, None, None, None, None
+            dy = torch.zeros_like(dz_extra)
         dy2 = dy.reshape(-1, H)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()

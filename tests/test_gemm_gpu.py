@@ -93,3 +93,43 @@ def test_gemm_split_k_wgrad(shape):
     _lib.assert_status_ok("gemm")
     ref = base + a.float().t() @ b.float()
     _check(out, ref, K, "split-k")
+
+
+def test_linear_and_mlp_fork_sum_input_gradients_in_the_gemm():
+    """``linear_fork`` / ``mlp_fork`` hand the input through as a second output; the two gradients of
+    the input are added in the data-gradient GEMM's epilogue."""
+    from merak_b200.ops import gemm as G
+    from merak_b200.ops.linear import linear, linear_fork, mlp, mlp_fork
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    M, K, N, F = 384, 256, 320, 512
+    x = (torch.randn(3, M // 3, K, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(N, device=dev).bfloat16().requires_grad_(True)
+    gy = torch.randn(3, M // 3, N, device=dev).bfloat16()
+    gx = torch.randn(3, M // 3, K, device=dev).bfloat16()
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    y, xr = linear_fork(xa, w, b)
+    ((y.float() * gy.float()).sum() + (xr.float() * gx.float()).sum()).backward()
+    dw_fork, w.grad = w.grad.clone(), None
+    y2 = linear(xb, w, b)
+    ((y2.float() * gy.float()).sum() + (xb.float() * gx.float()).sum()).backward()
+    torch.testing.assert_close(y.float(), y2.float(), rtol=0, atol=0)
+    torch.testing.assert_close(xa.grad.float(), xb.grad.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dw_fork.float(), w.grad.float(), rtol=0, atol=0)
+    # only the pass-through output used
+    xc = x.clone().requires_grad_(True)
+    _, xr = linear_fork(xc, w, b)
+    (xr.float() * gx.float()).sum().backward()
+    torch.testing.assert_close(xc.grad.float(), gx.float(), rtol=0, atol=0)
+    # MLP
+    w1 = (torch.randn(F, K, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    b1 = torch.zeros(F, device=dev).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(K, F, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    b2 = torch.zeros(K, device=dev).bfloat16().requires_grad_(True)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    y, xr = mlp_fork(xa, w1, b1, w2, b2, G.ACT_GELU_ERF)
+    ((y.float() * gx.float()).sum() + (xr.float() * gx.float()).sum()).backward()
+    y2 = mlp(xb, w1, b1, w2, b2, G.ACT_GELU_ERF)
+    ((y2.float() * gx.float()).sum() + (xb.float() * gx.float()).sum()).backward()
+    torch.testing.assert_close(xa.grad.float(), xb.grad.float(), rtol=2e-2, atol=2e-2)
