@@ -50,6 +50,7 @@ struct GemmParams {
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
   int tma_store;                  // the kernel may write C through shared memory + TMA stores (bf16, no accumulate)
+  int tma_store_aux;              // ... and the pre-activation side output too (second tensor map)
   GemmComm comm;
 };
 
@@ -268,7 +269,7 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 template <int kAct, int kAux>
 __device__ __noinline__ void epilogue_tile_t(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
                                               int col_base, int ncols, bool split_k, bool first_split,
-                                              uint8_t* stage, int r_in_tile) {
+                                              uint8_t* stage, int r_in_tile, int pass) {
   const bool out_f32 = (p.flags & MRK_GEMM_OUT_F32) != 0;
   const bool accumulate = (p.flags & MRK_GEMM_ACCUMULATE) != 0;
   const bool bias_f32 = (p.flags & MRK_GEMM_BIAS_F32) != 0;
@@ -324,8 +325,21 @@ for (int c = 0; c < ncols / 32; ++c) {
     }
   }
   if (stage != nullptr) {
-    // shared-memory staged output: side tensors are only present on full-width blocks here
-    if (p.aux_out != nullptr && row_ok) {
+    // shared-memory staged output: side tensors are only present on full-width blocks here.
+    // pass 1 stages the pre-activation side output alone, pass 2 the main output without it; pass 0
+    // does the main output and writes a side output, if any, directly.
+    if (pass == 1) {
+      uint8_t* box = stage + (c >> 1) * 16384;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t off = sw128_offset((uint32_t)r_in_tile, (uint32_t)((c & 1) * 4 + q));
+        *reinterpret_cast<uint4*>(box + off) =
+            make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                       pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+      }
+      continue;
+    }
+    if (pass == 0 && p.aux_out != nullptr && row_ok) {
       uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
 #pragma unroll
       for (int q = 0; q < 4; ++q)
@@ -471,9 +485,9 @@ for (int c = 0; c < ncols / 32; ++c) {
 // has no run-time dispatch.
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, long long row, bool row_ok, uint32_t t_row,
                                               int col_base, int ncols, bool split_k, bool first_split,
-                                              uint8_t* stage = nullptr, int r_in_tile = 0) {
+                                              uint8_t* stage = nullptr, int r_in_tile = 0, int pass = 0) {
 #define MRK_EPI(ACT, AUX) \
-  epilogue_tile_t<ACT, AUX>(p, row, row_ok, t_row, col_base, ncols, split_k, first_split, stage, r_in_tile)
+  epilogue_tile_t<ACT, AUX>(p, row, row_ok, t_row, col_base, ncols, split_k, first_split, stage, r_in_tile, pass)
 #define MRK_EPI_ACT(ACT)                                             \
   do {                                                               \
     if (p.aux_mode == MRK_AUX_ADD) MRK_EPI(ACT, MRK_AUX_ADD);        \

@@ -257,8 +257,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
   return 0;
 }
 
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams& p,
-                     cudaStream_t stream);
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& taux,
+                     GemmParams& p, cudaStream_t stream);
 
 }  // namespace mrk
 
@@ -298,6 +298,7 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
   GemmParams p;
   memset(&p.comm, 0, sizeof(p.comm));
   p.tma_store = 0;
+  p.tma_store_aux = 0;
   if (comm != nullptr) p.comm = *comm;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
@@ -318,7 +319,13 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
       if (rc) return rc;
       p.tma_store = 1;
     }
-    return launch_gemm_pair(ta, tb, tc, p, s);
+    CUtensorMap taux = ta;
+    if (p.tma_store && aux_out != nullptr && (ld_aux_out % 8) == 0 && (reinterpret_cast<uintptr_t>(aux_out) & 15) == 0) {
+      rc = make_tmap_2d(&taux, aux_out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ld_aux_out, 64, 128, 3);
+      if (rc) return rc;
+      p.tma_store_aux = 1;
+    }
+    return launch_gemm_pair(ta, tb, tc, taux, p, s);
   }
   if (bn == 256) return launch<256>(ta, tb, p, s);
   if (bn == 128) return launch<128>(ta, tb, p, s);

@@ -31,7 +31,8 @@ constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes
 
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                      const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_aux,
+                      const GemmParams p) {
   constexpr uint32_t kTmemCols = 512;   // two 256-column accumulator buffers
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -66,6 +67,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (p.tma_store) tma_prefetch_desc(&tma_c);
+    if (p.tma_store_aux) tma_prefetch_desc(&tma_aux);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
@@ -195,8 +197,27 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (store_thread) tma_store_wait_read<0>();
         named_bar_sync(1 + half, 128);
       }
+      const bool two_pass = staged && p.tma_store_aux && p.aux_out != nullptr;
+      if (two_pass) {
+        // pre-activation side output first: stage, store, and wait until the buffer can be reused
+        epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k,
+                      first_split, stage, row_in_tile, 1);
+        fence_proxy_async_smem();
+        named_bar_sync(1 + half, 128);
+        if (store_thread) {
+          if (row0 < p.M) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+              if (col_half + b * 64 < p.N)
+                tma_store_2d(&tma_aux, smem_u32(stage + b * 16384), col_half + b * 64, (int32_t)row0);
+          }
+          tma_store_commit();
+          tma_store_wait_read<0>();
+        }
+        named_bar_sync(1 + half, 128);
+      }
       epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k, first_split,
-                    staged ? stage : nullptr, row_in_tile);
+                    staged ? stage : nullptr, row_in_tile, two_pass ? 2 : 0);
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));    // TMEM is free; stores go on below
       if (staged) {
@@ -226,8 +247,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   }
 }
 
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams& p,
-                     cudaStream_t stream) {
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& taux,
+                     GemmParams& p, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   MRK_CUDA_OK(cudaGetDevice(&dev));
@@ -269,7 +290,8 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (p.num_splits > 1) p.tma_store = 0;
-  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, tc, p));
+  if (!p.tma_store) p.tma_store_aux = 0;
+  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, tc, taux, p));
   count_launch();
   return 0;
 }
