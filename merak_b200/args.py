@@ -109,6 +109,8 @@ class MerakArguments:
     comm_mode: str = field(default="fused", metadata={
         "help": "fused: sm_100a kernels fused with their collectives over peer memory; "
                 "nccl: plain torch.distributed collectives (baseline / oracle)"})
+    deallocate_pipeline_outputs: bool = field(default=False, metadata={
+        "help": "free a stage's output activations once they have been sent to the next stage"})
     failure_detection_timeout: float = field(default=0.0, metadata={
         "help": "> 0: heartbeat every rank through the process-group store and raise RankFailureError at the "
                 "next step boundary when a peer has been silent for this many seconds"})

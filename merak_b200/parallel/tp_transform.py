@@ -154,6 +154,27 @@ class RowPara(nn.Module):
         return y if residual is None else y + residual
 
 
+class ConvPara(nn.Module):
+    """Channel-parallel replacement of a ``nn.Conv2d`` named in ``CONV_PARA_LIST``: the input channels
+    are split over the tensor-parallel ranks and the partial outputs summed; parameters live under
+    ``conv`` (Merak/core/tensor_parallel/mp_layers.py:186-226)."""
+
+    def __init__(self, conv: nn.Conv2d):
+        super().__init__()
+        from .layers import ColParallelConv2d
+        tp, rank = mpu.get_model_parallel_world_size(), mpu.get_model_parallel_rank()
+        self.conv = ColParallelConv2d(conv.in_channels, conv.out_channels, conv.kernel_size, conv.stride, conv.padding,
+                                      conv.dilation, conv.groups, bias=conv.bias is not None,
+                                      params_dtype=conv.weight.dtype, device=conv.weight.device)
+        self.conv.weight = nn.Parameter(conv.weight.data.chunk(tp, dim=1)[rank].contiguous())
+        self.conv.weight.model_parallel, self.conv.weight.partition_dim = True, 1
+        if conv.bias is not None:
+            self.conv.bias = nn.Parameter(conv.bias.data.clone())
+
+    def forward(self, x):
+        return self.conv(x)
+
+
 class _SeqScatter(nn.Module):
     """Wraps a module whose output starts the sequence-parallel region: scatters along ``dim``."""
 
@@ -190,6 +211,11 @@ def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, me
     for parent_name, parent in list(model.named_modules()):
         for child_name, child in list(parent.named_children()):
             full = (parent_name + "." if parent_name else "") + child_name
+            if isinstance(child, nn.Conv2d) and CONV_PARA_LIST and _matches(full, CONV_PARA_LIST) and \
+                    child.groups == 1 and child.in_channels % tp == 0:
+                setattr(parent, child_name, ConvPara(child))
+                replaced.append(full)
+                continue
             if not isinstance(child, nn.Linear) or any(s in full for s in skip):
                 continue
             if _matches(full, row):          # row first: "output.dense" also ends with "dense"

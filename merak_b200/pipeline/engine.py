@@ -522,7 +522,14 @@ class PipelineEngine:
                 scale = (1.0 / self.micro_batches) * (self.loss_scaler.cur_scale if self.loss_scaler is not None else 1.0)
                 pairs.append((aux, torch.full_like(aux, scale)))
             if pairs:
-                torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+                if getattr(self, "buf_out_meta", {}).pop(buf, None) is not None:
+                    # freed outputs no longer match their gradients' shapes: call the engine directly
+                    from torch.autograd import Variable
+                    Variable._execution_engine.run_backward(
+                        tensors=tuple(o for o, _ in pairs), grad_tensors=tuple(g for _, g in pairs), keep_graph=False,
+                        create_graph=False, inputs=tuple(), allow_unreachable=True, accumulate_grad=True)
+                else:
+                    torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
             self.buf_outputs[buf] = None
             self.buf_out_grads[buf] = None
         if not self.is_first:
@@ -565,6 +572,33 @@ class PipelineEngine:
         p2p.send_forward(outs)
         if self.wall_clock_breakdown:
             self.timers("pipe_send_output").stop()
+        self._free_sent_outputs(buf)
+
+    def _free_sent_outputs(self, buf: int):
+        """``deallocate_pipeline_outputs``: after the activation has been sent this stage only needs the
+        outputs' ``grad_fn``; their storage is released (Merak/core/pipeline/utils.py:113-150)."""
+        if not getattr(self.args, "deallocate_pipeline_outputs", False):
+            return
+        from .utils import deallocate_output_tensor
+        outs = self.buf_outputs[buf] or ()
+        if not hasattr(self, "buf_out_meta"):
+            self.buf_out_meta = {}
+        self.buf_out_meta[buf] = [(tuple(o.shape), o.dtype) if isinstance(o, torch.Tensor) else None for o in outs]
+        for o in outs:
+            if isinstance(o, torch.Tensor) and o.requires_grad and o._base is None and o.numel() > 1:
+                deallocate_output_tensor(o)
+
+    def _grad_buffers_like(self, buf: int):
+        """Receive buffers for the gradients of this buffer's floating-point outputs (shapes from
+        before the outputs were freed, when they were)."""
+        outs = self.buf_outputs[buf]
+        meta = getattr(self, "buf_out_meta", {}).get(buf)
+        res = []
+        for i, o in enumerate(outs):
+            if isinstance(o, torch.Tensor) and o.is_floating_point():
+                shape, dtype = meta[i] if meta is not None else (tuple(o.shape), o.dtype)
+                res.append(torch.empty(shape, dtype=dtype, device=o.device))
+        return res
 
     def _ensure_act_meta_sent(self, outs):
         if not self._meta_sent["act"]:
@@ -606,7 +640,7 @@ class PipelineEngine:
         if self.is_last:
             return None
         outs = self.buf_outputs[buf]
-        bufs = [torch.empty_like(o) for o in outs if isinstance(o, torch.Tensor) and o.is_floating_point()]
+        bufs = self._grad_buffers_like(buf)
         work = p2p.recv_backward(bufs, wait=False)
         it = iter(bufs)
         self.buf_out_grads[buf] = [next(it) if (isinstance(o, torch.Tensor) and o.is_floating_point()) else None
@@ -629,12 +663,13 @@ class PipelineEngine:
         outs = [o.detach() for o in self.buf_outputs[send_buf]]
         self._ensure_act_meta_sent(outs)
         routs = self.buf_outputs[recv_buf]
-        gb = [torch.empty_like(o) for o in routs if isinstance(o, torch.Tensor) and o.is_floating_point()]
+        gb = self._grad_buffers_like(recv_buf)
         if self.wall_clock_breakdown:
             self.timers("pipe_send_output_recv_grad").start()
         p2p.send_forward_recv_backward(outs, gb)
         if self.wall_clock_breakdown:
             self.timers("pipe_send_output_recv_grad").stop()
+        self._free_sent_outputs(send_buf)
         it = iter(gb)
         self.buf_out_grads[recv_buf] = [next(it) if (isinstance(o, torch.Tensor) and o.is_floating_point()) else None
                                         for o in routs]

@@ -42,6 +42,7 @@ def main():
     ap.add_argument("--resume", default=None)
     ap.add_argument("--n_head", type=int, default=0)
     ap.add_argument("--meta", type=int, default=0)
+    ap.add_argument("--dealloc", type=int, default=0)
     ap.add_argument("--comm", default="nccl")
     ap.add_argument("--clip", type=float, default=1.0)
     ap.add_argument("--out", required=True)
@@ -77,7 +78,8 @@ def main():
         activation_checkpoint_ratio=[o.ratio] if o.ratio else None, zero_stage=1 if o.zero else None,
         parallel_vocab=bool(o.parallel_vocab), sequence_parallel=o.sp > 1, tp_overlapping_level=o.tp_overlap, megatron_sequence_parallel=bool(o.megatron_sp),
         split_method=o.split, bf16=(o.dtype == "bf16"), seed=1234, save=bool(o.save_dir), save_steps=o.steps,
-        resume_from_checkpoint=o.resume, comm_mode=o.comm, max_grad_norm=o.clip)
+        resume_from_checkpoint=o.resume, comm_mode=o.comm, max_grad_norm=o.clip,
+        deallocate_pipeline_outputs=bool(o.dealloc))
     # every data-parallel layout must see the same global batch per step: dataset order is by index
     ds = SyntheticTokenDataset(V, L, 16, task=task, seed=7)      # two global batches, revisited
     trainer = FixedOrderTrainer(model, args, train_dataset=ds)

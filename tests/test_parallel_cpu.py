@@ -84,6 +84,12 @@ def test_tp2_megatron_sequence_parallel_with_biases(tmp_path, baseline, model):
     assert_close(got, baseline[model])
 
 
+def test_pp2_deallocate_sent_outputs(tmp_path, baseline):
+    """Outputs are freed after the send; backward runs from their grad_fn through the autograd engine."""
+    got = run_layout(tmp_path, "pp2_dealloc", 2, ["--pp", "2", "--dealloc", "1"])
+    assert_close(got, baseline["gpt2"])
+
+
 def test_tp2_uneven_attention_heads(tmp_path):
     """Five heads over two tensor-parallel ranks (3 + 2): heads are never split between ranks."""
     single = run_layout(tmp_path, "h5_single", 1, ["--n_head", "5", "--steps", "4"])
