@@ -112,10 +112,6 @@ dp_reduce_scatter_kernel(PeerPtrs grads, PeerPtrs ctrls, int n_rt, int rank, lon
   }
 }
 
-struct AdamHp {
-  float lr, b1, b2, eps, wd, bc1, bc2;
-};
-
 template <int N>
 __global__ void __launch_bounds__(kDpThreads)
 dp_adamw_allgather_kernel(PeerPtrs models, PeerPtrs ctrls, int n_rt, int rank, long long lo, long long cnt,

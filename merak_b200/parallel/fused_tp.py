@@ -166,13 +166,6 @@ def reset():
     _COMMS.clear()
 
 
-def _seg_rows(x: torch.Tensor, seq_dim: int, n: int, sharded: bool) -> int:
-    """Rows per (batch, rank) segment of the flattened [tokens, H] matrix for a [B, L, H] tensor whose
-    sequence dimension is (or will be) sharded over n ranks."""
-    assert x.dim() == 3 and seq_dim == 1, "fused tensor parallelism expects batch-first [B, L, H] activations"
-    return x.shape[1] if sharded else x.shape[1] // n
-
-
 class _RowLinearFused(torch.autograd.Function):
     """Row-parallel linear: forward GEMM -> reduce-scatter (sequence parallel) or all-reduce."""
 

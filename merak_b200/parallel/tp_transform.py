@@ -111,11 +111,11 @@ class ColPara(nn.Module):
                                                bias=linear.bias is not None, gather_output=gather_output,
                                                sequence_parallel=sequence_parallel, seq_dim=seq_dim,
                                                params_dtype=w.dtype, device="meta")
-        if True:        # slicing works on meta tensors too (shapes only)
-            self.col_linear.weight = nn.Parameter(_slice_fused(w.data, 0, rank, tp, parts, sizes, unit))
-            if linear.bias is not None:
-                self.col_linear.bias = nn.Parameter(_slice_fused(linear.bias.data, 0, rank, tp, parts, sizes, unit))
-            self.col_linear.output_size_per_partition = self.col_linear.weight.shape[0]
+        # slicing works on meta tensors too (shapes only), so models built under init_empty_weights pass
+        self.col_linear.weight = nn.Parameter(_slice_fused(w.data, 0, rank, tp, parts, sizes, unit))
+        if linear.bias is not None:
+            self.col_linear.bias = nn.Parameter(_slice_fused(linear.bias.data, 0, rank, tp, parts, sizes, unit))
+        self.col_linear.output_size_per_partition = self.col_linear.weight.shape[0]
         for p in self.col_linear.parameters():
             p.model_parallel, p.partition_dim = True, 0
         self.fused_parts, self.fused_sizes = parts, sizes
@@ -138,12 +138,11 @@ class RowPara(nn.Module):
                                             input_is_parallel=input_is_parallel,
                                             sequence_parallel=sequence_parallel, seq_dim=seq_dim,
                                             params_dtype=w.dtype, device="meta")
-        if True:
-            unit = int(getattr(linear, "tp_unit", 1) or 1)
-            self.row_linear.weight = nn.Parameter(_slice_fused(w.data, 1, rank, tp, None, None, unit))
-            self.row_linear.input_size_per_partition = self.row_linear.weight.shape[1]
-            if linear.bias is not None:
-                self.row_linear.bias = nn.Parameter(linear.bias.data.clone())
+        unit = int(getattr(linear, "tp_unit", 1) or 1)
+        self.row_linear.weight = nn.Parameter(_slice_fused(w.data, 1, rank, tp, None, None, unit))
+        self.row_linear.input_size_per_partition = self.row_linear.weight.shape[1]
+        if linear.bias is not None:
+            self.row_linear.bias = nn.Parameter(linear.bias.data.clone())
         self.row_linear.weight.model_parallel, self.row_linear.weight.partition_dim = True, 1
         if self.row_linear.bias is not None and self.row_linear.sequence_parallel:
             # added to this rank's sequence shard only: its gradient is summed over the group

@@ -254,6 +254,11 @@ class PipelineEngine:
             if self.device.type == "cuda":
                 from ..utils.failure import check_device_status
                 check_device_status()                                   # raises DeviceWaitTimeout
+        if self.device.type == "cuda" and self.global_steps % 16 == 0:
+            # a bounded device-side wait that ran out (peer flag, mbarrier) leaves a bit in the status
+            # word; the results since then are invalid, so stop instead of training on
+            from ..utils.failure import check_device_status
+            check_device_status()
         if self.wall_clock_breakdown:
             self.timers("train_batch").start()
         if self._graph_capable():
