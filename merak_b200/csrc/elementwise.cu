@@ -714,7 +714,8 @@ MRK_API int mrk_swiglu_bwd(const void* gu, const void* dout, void* dgu, long lon
 
 MRK_API int mrk_colsum(const void* x, float* out, long long M, int N, long long ld, void* stream) {
   MRK_REQUIRE(N % 2 == 0 && ld % 2 == 0, "colsum: N must be even");
-  if (N % 8 == 0 && ld % 8 == 0 && ((uintptr_t)x & 15) == 0) {
+  if (ld % 8 == 0 && ld >= (N + 7) / 8 * 8 && ((uintptr_t)x & 15) == 0) {
+    // (a ragged last group of columns is read up to the row pitch and only its valid columns are added)
     // 16-byte loads: a block covers 256 columns x its row range, 8 row lanes, 4 rows in flight per thread
     const int col_blocks = (N / 8 + 31) / 32;
     int row_blocks = (int)((long long)sm_count() * 8 / col_blocks);

@@ -194,3 +194,17 @@ def test_linear_and_mlp_autograd():
     ref = 2 * (gy.float().reshape(-1, N).t() @ x2.detach().float().reshape(-1, K))
     assert w.grad is None and rel(w.main_grad, ref) < 2e-2
     _lib.assert_status_ok("linear")
+
+
+@pytest.mark.parametrize("M,N,pitch", [(1000, 4096, 4096), (777, 30522, 30528), (513, 250, 256), (64, 30, 30)])
+def test_colsum_vector_and_ragged(M, N, pitch):
+    """Column sums (bias gradients): 16-byte path for full and ragged widths with a padded pitch, scalar
+    path otherwise; garbage in the padding columns must not leak into the result."""
+    from merak_b200.ops.elementwise import colsum
+    torch.manual_seed(0)
+    buf = torch.full((M, pitch), float("nan"), device="cuda", dtype=torch.bfloat16)
+    buf[:, :N] = torch.randn(M, N, device="cuda").bfloat16()
+    x = buf[:, :N]
+    out = colsum(x)
+    ref = x.float().sum(0)
+    torch.testing.assert_close(out, ref, rtol=2e-3, atol=2e-2)
