@@ -250,23 +250,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tmem_wait_ld();
         uint32_t pk[16], dsk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv_[2];
+        for (int i8 = 0; i8 < 32; i8 += 8) {
+          // the per-query statistics are the same for every lane: 16-byte broadcast loads, 8 columns at a time
+          const float4 l0 = *reinterpret_cast<const float4*>(st + col0 + i8);
+          const float4 l1 = *reinterpret_cast<const float4*>(st + col0 + i8 + 4);
+          const float4 d0 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8);
+          const float4 d1 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8 + 4);
+          const float lse8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+          const float dl8[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = col0 + i + e;
-            const float lse2 = st[col], dl = st[128 + col];
-            float x = fmaf(__uint_as_float(s[i + e]), p.scale_log2, kbias - lse2);
-            float pe = exp2f(x);
-            if (need_mask) {
-              const int q = q0 + col;
-              if (key >= p.Lk || (p.causal && key > q + shift)) pe = 0.f;
+          for (int j = 0; j < 8; j += 2) {
+            float pv[2], dv_[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int i = i8 + j + e;
+              const float x = fmaf(__uint_as_float(s[i]), p.scale_log2, kbias - lse8[j + e]);
+              float pe = exp2f(x);
+              if (need_mask) {
+                const int q = q0 + col0 + i;
+                if (key >= p.Lk || (p.causal && key > q + shift)) pe = 0.f;
+              }
+              pv[e] = pe;
+              dv_[e] = pe * (__uint_as_float(dp[i]) - dl8[j + e]) * p.scale;
             }
-            pv[e] = pe;
-            dv_[e] = pe * (__uint_as_float(dp[i + e]) - dl) * p.scale;
+            pk[(i8 + j) >> 1] = pack_bf16x2(pv[0], pv[1]);
+            dsk[(i8 + j) >> 1] = pack_bf16x2(dv_[0], dv_[1]);
           }
-          pk[i >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dsk[i >> 1] = pack_bf16x2(dv_[0], dv_[1]);
         }
         // columns col0..col0+31 -> atom (col0/64), 16-byte chunks ((col0%64)/8)..+3 of row r
         const uint32_t atom = (uint32_t)(col0 >> 6), ch0 = (uint32_t)((col0 & 63) >> 3);
@@ -362,35 +371,39 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const 
                                      float* __restrict__ delta, float* __restrict__ dq_acc, int B, int H, int Lq,
                                      long long o_sb, long long o_ss, long long o_sh, long long do_sb,
                                      long long do_ss, long long do_sh) {
-  // one warp per (b, q, h) row
-  const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
-  const long long total = (long long)B * Lq * H;
-  if (row >= total) return;
+  // D/8 lanes per (b, q, h) row, 16-byte loads: a warp covers 4 rows (D = 64) or 2 rows (D = 128)
+  constexpr int kLanes = D / 8;
+  constexpr int kRowsPerWarp = 32 / kLanes;
   const int lane = threadIdx.x & 31;
-  const int h = (int)(row % H);
-  const long long bq = row / H;
-  const int q = (int)(bq % Lq);
-  const int b = (int)(bq / Lq);
-  const __nv_bfloat16* po = o + b * o_sb + q * o_ss + h * o_sh;
-  const __nv_bfloat16* pd = dout + b * do_sb + q * do_ss + h * do_sh;
+  const int sub = lane / kLanes, l = lane % kLanes;
+  const long long warp_id = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const long long row = warp_id * kRowsPerWarp + sub;
+  const long long total = (long long)B * Lq * H;
+  const bool live = row < total;
   float acc = 0.f;
-  constexpr int kPer = D / 32;   // 2 or 4 elements per lane
-  if (kPer == 2) {
-    const float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(po)[lane]);
-    const float2 c = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(pd)[lane]);
-    acc = a.x * c.x + a.y * c.y;
-  } else {
-    const uint2 ua = reinterpret_cast<const uint2*>(po)[lane];
-    const uint2 uc = reinterpret_cast<const uint2*>(pd)[lane];
-    const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y), c0 = unpack_bf16x2(uc.x), c1 = unpack_bf16x2(uc.y);
-    acc = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  int h = 0, q = 0, b = 0;
+  if (live) {
+    h = (int)(row % H);
+    const long long bq = row / H;
+    q = (int)(bq % Lq);
+    b = (int)(bq / Lq);
+    const uint4 ua = __ldg(reinterpret_cast<const uint4*>(o + b * o_sb + q * o_ss + h * o_sh) + l);
+    const uint4 uc = __ldg(reinterpret_cast<const uint4*>(dout + b * do_sb + q * do_ss + h * do_sh) + l);
+    const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wc[4] = {uc.x, uc.y, uc.z, uc.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16x2(wa[k]), c = unpack_bf16x2(wc[k]);
+      acc += a.x * c.x + a.y * c.y;
+    }
   }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) delta[((long long)b * H + h) * Lq + q] = acc;
-  float* z = dq_acc + row * D;
-  if (kPer == 2) reinterpret_cast<float2*>(z)[lane] = make_float2(0.f, 0.f);
-  else           reinterpret_cast<float4*>(z)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = kLanes / 2; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (live) {
+    if (l == 0) delta[((long long)b * H + h) * Lq + q] = acc;
+    float4* z = reinterpret_cast<float4*>(dq_acc + row * D + l * 8);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 }
 
 // dq (bf16, strided [B,Lq,H,D]) = dq_acc (fp32 contiguous)
@@ -450,7 +463,8 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
   const long long rows = (long long)B * Lq * H;
   {
     const int warps_per_block = 8;
-    const long long blocks = (rows + warps_per_block - 1) / warps_per_block;
+    const long long rows_per_block = warps_per_block * (32 / (D / 8));      // D/8 lanes per row
+    const long long blocks = (rows + rows_per_block - 1) / rows_per_block;
     if (D == 64)
       attn_bwd_prep_kernel<64><<<(unsigned)blocks, warps_per_block * 32, 0, s>>>(
           (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, dq_acc, B, H, Lq, so[0], so[1], so[2], sdo[0],
