@@ -275,8 +275,7 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
   int bn = block_n;
   // block_n: 0 = choose; 64/128/256 = single-CTA kernel with that tile width; 512 = CTA-pair kernel
   // (256 x 256 tile per 2-CTA cluster).  The pair kernel is the default for anything wide enough.
-  if (bn == 0 && M > 128 && N > 128 && comm == nullptr) bn = 512;
-  if (comm != nullptr && bn == 512) bn = 256;     // the fused collectives live in the single-CTA kernel
+  if (bn == 0 && M > 128 && N > 128) bn = 512;     // (both kernels carry the fused all-gather)
   if (bn == 0) {
     // Heuristic: widest tile that still fills the SMs reasonably; narrow tiles for small N.
     const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);

@@ -53,6 +53,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
   const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
 
+  // fused all-gather (GemmComm mode 2): the clusters behind the compute clusters only move the peers'
+  // shards of A; both CTAs of such a cluster leave together, so no cluster barrier is left waiting
+  if (p.comm.mode == 2 && (int)blockIdx.x >= p.comm.gemm_ctas) {
+    comm_gather_role(p, smem, kPairStages * kPairStageBytes + kPairStagingBytes);
+    return;
+  }
+
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kPairStages; ++s) {
@@ -81,7 +88,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
 
   const int cluster_id = blockIdx.x >> 1;
-  const int num_clusters = gridDim.x >> 1;
+  const int num_clusters = (p.comm.mode == 2 ? p.comm.gemm_ctas : (int)gridDim.x) >> 1;
   const int num_units = p.num_m_blocks * p.num_n_blocks * p.num_splits;
 
   if (warp == 0) {
@@ -93,10 +100,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
         int m_blk, n_blk;
         tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        m_blk = comm_perm_m(p, m_blk, kPairBlockM);
         const int m0 = m_blk * kPairBlockM + (int)cta * 128;
         const int n0 = n_blk * kPairBlockN + (int)cta * (kPairBlockN / 2);
         const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        if (p.comm.mode == 2 && m0 < p.M) {       // this CTA's 128 rows of A must have arrived
+          ok = comm_wait_rows(p, m0, 128, abort_flag);
+          if (!ok) break;
+        }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
           if (!ok) break;
@@ -177,6 +189,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++iter) {
       int m_blk, n_blk;
       tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      m_blk = comm_perm_m(p, m_blk, kPairBlockM);
       const bool split_k = p.num_splits > 1;
       const bool first_split = (unit % p.num_splits) == 0;
       const int acc = iter & 1;
@@ -275,10 +288,21 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   p.kb_per_split = (p.num_k_blocks + p.num_splits - 1) / p.num_splits;
   p.num_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   const int units = tiles * p.num_splits;
-  const int clusters = units < max_clusters ? units : max_clusters;
+  int clusters = units < max_clusters ? units : max_clusters;
+  int gather_clusters = 0;
+  if (p.comm.mode == 2) {
+    // compute clusters + gather clusters, all resident at once: the former wait for the latter
+    gather_clusters = (p.comm.gemm_ctas + 1) / 2;       // the caller passes the number of gather CTAs here
+    MRK_REQUIRE(gather_clusters >= 1 && gather_clusters < max_clusters, "gemm: bad number of gather CTAs");
+    const int room = max_clusters - gather_clusters;
+    clusters = units < room ? units : room;
+    p.comm.gemm_ctas = 2 * clusters;
+  }
+  if (p.comm.mode != 0 && p.comm.perm)
+    p.comm.perm = (p.comm.seg_rows % kPairBlockM == 0 && p.num_m_blocks % p.comm.n == 0 && p.M % kPairBlockM == 0) ? 1 : 0;
 
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.gridDim = dim3(2 * (clusters + gather_clusters), 1, 1);
   cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = kPairSmemTotal;
   cfg.stream = stream;

@@ -117,7 +117,7 @@ class TPComm:
         window = gemm_s * (self.n - 1) / self.n
         remote = 2.0 * M * K * (self.n - 1) / self.n
         need = int(remote / max(window, 1e-6) / 20e9) + 1
-        return max(2, min(GATHER_CTAS, need))
+        return max(2, min(GATHER_CTAS, (need + 1) // 2 * 2))       # even: the pair kernel gathers with whole clusters
 
     def gather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], seg_rows: int,
                     b_mn: bool = False, act: int = G.ACT_NONE, want_preact: bool = False):
