@@ -18,6 +18,7 @@ namespace mrk {
 // Rows of the full [M, *] matrix are grouped in segments of `seg_rows`; segment s belongs to rank
 // s % n and is that rank's local segment s / n (batch-first sequence sharding).
 constexpr int kGemmMaxPeers = 8;
+constexpr int kGatherWorkers = 2;     // issuing threads per gather CTA (lane 0 of warps 0..W-1), each with its own slots
 struct GemmComm {
   int mode, n, rank;
   int seg_rows;
@@ -29,7 +30,8 @@ struct GemmComm {
   uint32_t* seg_flags;         // mode 2: local, one counter per segment
   void* ctrl[kGemmMaxPeers];   // control blocks (entry barrier of mode 2)
   uint32_t epoch;              // barrier epoch of this call
-  uint32_t flag_target;        // mode 2: value a segment counter reaches once the segment is complete
+  uint32_t flag_target;        // mode 2: gather CTAs of all calls so far; a segment is complete when its
+                               // counter reaches flag_target * kGatherWorkers
   long long budget;            // wait budget in SM cycles
 };
 
@@ -76,7 +78,7 @@ __device__ __forceinline__ bool comm_wait_rows(const GemmParams& p, int m0, int 
   const int s0 = m0 / c.seg_rows, s1 = last_row / c.seg_rows;
   for (int s = s0; s <= s1; ++s) {
     const long long t0 = clock64();
-    while ((int32_t)(ld_acquire_sys_u32(c.seg_flags + s) - c.flag_target) < 0) {
+    while ((int32_t)(ld_acquire_sys_u32(c.seg_flags + s) - c.flag_target * kGatherWorkers) < 0) {
       if (*abort_flag || clock64() - t0 > c.budget) {
         *abort_flag = 1;
         raise_status(p.status, kStatusFlagTimeout);
@@ -93,7 +95,7 @@ __device__ __forceinline__ bool comm_wait_rows(const GemmParams& p, int m0, int 
 // One thread per CTA drives a ring of shared-memory slots with bulk async copies (peer or local
 // global -> shared, then shared -> local global), so that about 190 KB per CTA are in flight over
 // NVLink; plain loads from a few CTAs cannot cover the link latency.
-constexpr int kGatherChunk = 16384;
+constexpr int kGatherChunk = 32768;
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -107,20 +109,25 @@ __device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t 
 
 __device__ __forceinline__ void comm_gather_role(const GemmParams& p, uint8_t* smem, int smem_bytes) {
   const GemmComm& c = p.comm;
-  const int g = blockIdx.x - c.gemm_ctas, G = gridDim.x - c.gemm_ctas;
+  const int cta_g = blockIdx.x - c.gemm_ctas;
+  const int worker = threadIdx.x >> 5;
+  const int g = cta_g * kGatherWorkers + worker, G = (gridDim.x - c.gemm_ctas) * kGatherWorkers;
   SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(c.ctrl[c.rank]);
   PeerPtrs ctrls;
 #pragma unroll
   for (int k = 0; k < kGemmMaxPeers; ++k) ctrls.p[k] = c.ctrl[k];
   // every rank has staged its shard (and is done with the previous use of its buffers)
-  if (g == 0) symm_signal(ctrls, c.n, c.rank, 4, c.epoch);
+  if (cta_g == 0) symm_signal(ctrls, c.n, c.rank, 4, c.epoch);
   const bool ok = symm_wait(mine, c.n, 4, c.epoch, c.budget, p.status);
-  if (!ok || threadIdx.x != 0) return;     // on a timeout the consumers run out on the segment counters
+  // on a timeout the consumers run out on the segment counters
+  if (!ok || worker >= kGatherWorkers || (threadIdx.x & 31) != 0) return;
 
-  int slots = (smem_bytes - 512) / kGatherChunk;
-  if (slots > 12) slots = 12;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + slots * kGatherChunk);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 16);
+  const int total_slots = (smem_bytes - 512) / kGatherChunk;
+  const int slots = total_slots / kGatherWorkers;
+  uint8_t* bar_area = smem + total_slots * kGatherChunk;
+  smem += worker * slots * kGatherChunk;            // this worker's ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bar_area) + worker * 8;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_area + 256) + worker;
   *abort_flag = 0;
   for (int s = 0; s < slots; ++s) mbar_init(smem_u32(&bars[s]), 1);
   fence_mbar_init();
@@ -146,13 +153,13 @@ __device__ __forceinline__ void comm_gather_role(const GemmParams& p, uint8_t* s
   long long head = 0, tail = 0;
   bool good = true;
   while (tail < total && good) {
-    // At most slots - 4 loads are in flight, so the slot a new load lands in was last read by a store
-    // issued at least four stores ago: waiting until no more than three stores are still reading
-    // shared memory frees it without draining the store queue.
-    while (head < total && head - tail < slots - 4) {
+    // At most slots - 2 loads are in flight, so the slot a new load lands in was last read by a store
+    // issued at least two stores ago: waiting until no more than one store is still reading shared
+    // memory frees it without draining the store queue.
+    while (head < total && head - tail < slots - 1) {
       const int slot = (int)(head % slots);
       if (head >= slots)
-        asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       const uint8_t* src; uint8_t* dst; uint32_t bytes; int seg;
       locate(head, src, dst, bytes, seg);
       mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);

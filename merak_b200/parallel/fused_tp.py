@@ -111,12 +111,12 @@ class TPComm:
     # -- all-gather -> GEMM ---------------------------------------------------------------------------
     def _gather_ctas(self, M: int, N: int, K: int) -> int:
         """CTAs taken from the GEMM grid to stream the peers' shards: enough for the remote bytes to
-        arrive while the tiles that do not need them are computed (one SM sustains about 20 GB/s of
+        arrive while the tiles that do not need them are computed (one SM sustains about 35 GB/s of
         global -> shared -> global bulk copies), no more."""
         gemm_s = 2.0 * M * N * K / 1.3e15
         window = gemm_s * (self.n - 1) / self.n
         remote = 2.0 * M * K * (self.n - 1) / self.n
-        need = int(remote / max(window, 1e-6) / 20e9) + 1
+        need = int(remote / max(window, 1e-6) / 35e9) + 1
         return max(2, min(GATHER_CTAS, (need + 1) // 2 * 2))       # even: the pair kernel gathers with whole clusters
 
     def gather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], seg_rows: int,
