@@ -292,3 +292,18 @@ def test_ulysses_sequence_parallel_fused_matches_nccl_two_gpus(tmp_path):
     assert fused[-1] < fused[0]
     for a, b in zip(fused, ref):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (fused, ref)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_flag_barriers_with_skewed_ranks_two_gpus(tmp_path):
+    """Signal-flag protocol with one rank arriving 0.4 s late at every step: no timeout, right sums."""
+    import json
+    out = str(tmp_path / "skew.json")
+    script = os.path.join(HERE, "dist_scripts", "symm_barrier_skew.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), script, out]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert res.returncode == 0, res.stderr[-3000:]
+    with open(out) as f:
+        r = json.load(f)
+    assert r["ok"] == 1 and r["status"] == 0, r
