@@ -68,7 +68,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * 8 * 32);   // epilogue threads of both CTAs
+      mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * 8);        // one arrival per epilogue warp of both CTAs
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -232,7 +232,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k, first_split,
                     staged ? stage : nullptr, row_in_tile, two_pass ? 2 : 0);
       tc_fence_before();
-      mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));    // TMEM is free; stores go on below
+      __syncwarp();            // every lane's TMEM reads are complete: one (possibly remote) arrival per warp
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));   // TMEM is free
       if (staged) {
         fence_proxy_async_smem();
         named_bar_sync(1 + half, 128);
