@@ -1,12 +1,13 @@
 """Tensor-parallel linears whose collective is fused into the GEMM kernel.
 
-* ``row_linear_fused``    ``Y = sum_ranks(X_r W_r^T)``: the GEMM epilogue adds every output row over
-  NVLink into the fp32 accumulator of the rank that owns it (reduce-scatter while later tiles are
-  still computed); a small second kernel waits for all ranks, converts to bf16 (and, without
-  sequence parallelism, pulls the other ranks' rows: all-reduce).
+* ``row_linear_fused``    ``Y = sum_ranks(X_r W_r^T)``: the GEMM writes its bf16 partial product into a
+  peer-mapped buffer; the rank that owns a sequence segment pulls that segment's rows of every
+  rank's partial over NVLink (coalesced 16-byte loads), sums them in fp32 and adds the bias
+  (reduce-scatter); without sequence parallelism a second kernel pulls the other ranks' reduced
+  rows (all-reduce).
 * ``column_linear_fused`` ``Y = gather(X) W^T`` under Megatron sequence parallelism: a few CTAs of
-  the GEMM grid copy the peers' sequence shards into the local gathered matrix while the other
-  CTAs already multiply this rank's own rows.
+  the GEMM grid stream the peers' sequence shards into the local gathered matrix (bulk async
+  copies) while the other CTAs already multiply this rank's own rows.
 
 The backward passes use the mirror-image kernel (column: dgrad GEMM -> reduce-scatter / all-reduce;
 row: all-gather -> dgrad GEMM) and the weight gradients reuse the gathered operand.
