@@ -228,21 +228,31 @@ def run_ours(o):
     ini.destroy()
 
 
-def run_reference(o):
-    """The reference needs transformers<=4.47 (its tracer is built on transformers.utils.fx, and it
-    imports transformers.file_utils.cached_property); neither exists in the installed
-    transformers 5.x and no older wheel is available offline."""
-    ref = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
+def run_reference(o, small=None):
+    """The reference arm: the unmodified reference package under ``baseline/_ref`` drives a
+    plain-PyTorch BERT-large through its own trainer and engine (``baseline/ref_bench.py``).  The
+    names it needs from ``transformers`` 4.x are registered from outside its tree
+    (``baseline/compat.py``).  Any failure is reported as the ``unavailable`` line with the
+    location of the failing frame."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(here, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref, "Merak")):
         why = "baseline/_ref is not installed"
     else:
-        sys.path.insert(0, ref)
+        # this repository's ``Merak`` alias package must not shadow the reference
+        sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != here]
+        sys.path.insert(0, os.path.join(here, "baseline"))
         try:
-            import Merak  # noqa: F401
-            why = "reference imports but no runner is wired for it"
+            import ref_bench
+            ref_bench.run(o, ref, ClockSampler, METRIC, small=small)
+            return
         except Exception as exc:   # pragma: no cover - depends on the image
-            why = "import Merak fails: %s: %s" % (type(exc).__name__, str(exc).splitlines()[0][:160])
+            import traceback
+            tb = traceback.extract_tb(exc.__traceback__)
+            where = "%s:%d" % (os.path.relpath(tb[-1].filename, here), tb[-1].lineno) if tb else "?"
+            why = "%s at %s: %s" % (type(exc).__name__, where, (str(exc).splitlines() or [""])[0][:200])
+            traceback.print_exc(file=sys.stderr)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
