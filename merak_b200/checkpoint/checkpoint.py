@@ -87,7 +87,7 @@ class CheckpointSaver:
                 sd["torch_rng_state"] = torch.get_rng_state()
                 sd["cuda_rng_state"] = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
                 sd["rng_tracker_states"] = get_rng_tracker().get_states()
-                sd["dropout_state"] = {"seed": dropout_state().seed}
+                sd["dropout_state"] = dropout_state().state_dict()
             if engine is not None and engine.loss_scaler is not None:
                 sd["loss_scaler"] = engine.loss_scaler.state_dict()
             torch.save(sd, name, _use_new_zipfile_serialization=False)
@@ -100,6 +100,7 @@ class CheckpointSaver:
         if engine is not None and getattr(engine, "flat_expert", None) is not None:
             # expert-parallel parameters differ per rank of the expert-parallel group: one file each
             ename = _expert_file(name)
+            U.ensure_directory_exists(ename)      # dp ranks > 0 may get here before dp rank 0 made it
             esd = {"model": {k: v.detach().cpu() for k, v in model.state_dict().items() if _is_expert_key(model, k)}}
             if not a.no_save_optim:
                 esd["optimizer"] = _cpu(engine.optimizer_expert.state_dict())
@@ -217,6 +218,8 @@ class CheckpointLoader:
                 torch.cuda.set_rng_state(sd["cuda_rng_state"])
             if sd.get("rng_tracker_states"):
                 get_rng_tracker().set_states(sd["rng_tracker_states"])
+            if sd.get("dropout_state"):
+                dropout_state().load_state_dict(sd["dropout_state"])
         _barrier()
         if verbose:
             log_dist("loaded checkpoint %s (iteration %s)" % (name, iteration), ranks=[0])

@@ -86,7 +86,9 @@ dp_reduce_scatter_kernel(PeerPtrs grads, PeerPtrs ctrls, int n_rt, int rank, lon
   const float totbad = block_sum(bad, red);
   if (threadIdx.x == 0) {
     atomicAdd(&mine->local_acc[0], tot);
-    atomicAdd(&mine->local_acc[1], totbad);
+    // a block whose bounded wait ran out skipped its part of the shard: count it as a bad value so
+    // that whichever block finishes last posts a non-zero "bad" and every rank skips the update
+    atomicAdd(&mine->local_acc[1], ok ? totbad : totbad + 1.f);
     __threadfence();
     s_last = atomicAdd(&mine->done[0], 1u) == gridDim.x - 1;
   }

@@ -1,53 +1,122 @@
 """Device-resident state of the counter-based dropout generator.
 
 A dropout call draws its mask from ``philox(seed, offset + call_id, element)``.  ``seed`` and
-``offset`` live in a 2-element int64 tensor on the device so that advancing the step (``offset``)
-is a device-side add, which keeps a captured CUDA graph valid across steps.  ``call_id`` numbers
-the dropout call sites inside one step; activation recomputation restores it so the replayed
-forward regenerates identical masks (the role ``RNGStatesTracker`` plays in the reference,
-Merak/core/recompute/checkpointing.py:106-184).
+``offset`` live in a 2-element int64 tensor on the device so that advancing the step or the
+micro-batch (``offset``) is a device-side add, which keeps a captured CUDA graph valid across
+replays.  ``call_id`` numbers the dropout call sites inside one micro-batch; activation
+recomputation restores it so the replayed forward regenerates identical masks (the role
+``RNGStatesTracker`` plays in the reference, Merak/core/recompute/checkpointing.py:106-184).
+
+Two generators are kept, as the reference keeps a default CUDA generator and a model-parallel one
+(Merak/core/recompute/checkpointing.py:196-251):
+
+* ``replicated``: the same seed on every rank of a tensor-parallel group.  Dropout on activations
+  that every tensor-parallel rank holds in full (after a row-parallel all-reduce, on the embedding
+  output) must draw the same mask on all of them, or the replicated residual streams and the
+  gradients of replicated parameters drift apart.
+* ``sharded``: a seed that depends on the tensor-parallel (and sequence-parallel) rank, for
+  dropout on tensors each rank holds a different part of: attention probabilities of the rank's
+  own heads, sequence-sharded activations under Megatron-style sequence parallelism.
+
+``offset = step * _STEP_STRIDE + micro_batch * _MICRO_STRIDE``.
 """
 from __future__ import annotations
+
+import contextlib
 
 import torch
 
 _STEP_STRIDE = 1 << 20
+_MICRO_STRIDE = 1 << 12          # graph replays: 256 micro-batches per step, 4095 call sites each
+KINDS = ("replicated", "sharded")
 
 
 class DropoutState:
     def __init__(self):
-        self._state = {}      # device -> tensor [seed, offset]
+        self._state = {}      # (device, kind) -> tensor [seed, offset]
         self.call_id = 0
-        self.seed = 1234
+        self.seeds = {"replicated": 1234, "sharded": 1234}
+        self.default_kind = "replicated"
+        self.step = 0
+        self.micro = 0
 
-    def manual_seed(self, seed: int):
-        self.seed = int(seed)
-        for t in self._state.values():
-            t[0] = self.seed
-            t[1] = 0
-        self.call_id = 0
+    # --- seeds ----------------------------------------------------------------------------------
+    @property
+    def seed(self) -> int:
+        return self.seeds["sharded"]
 
-    def tensor(self, device) -> torch.Tensor:
-        key = str(device)
+    def manual_seed(self, seed: int, replicated_seed: int | None = None):
+        """``seed`` keys the sharded generator; ``replicated_seed`` (default: the same value) the
+        replicated one."""
+        self.seeds["sharded"] = int(seed)
+        self.seeds["replicated"] = int(seed if replicated_seed is None else replicated_seed)
+        self.step, self.micro, self.call_id = 0, 0, 0
+        self.default_kind = "replicated"
+        self._write_all()
+
+    def _offset(self) -> int:
+        return self.step * _STEP_STRIDE + self.micro * _MICRO_STRIDE
+
+    def _write_all(self):
+        for (_, kind), t in self._state.items():
+            t.copy_(torch.tensor([self.seeds[kind], self._offset()], dtype=torch.int64))
+
+    def tensor(self, device, sharded: bool | None = None) -> torch.Tensor:
+        kind = self.default_kind if sharded is None else ("sharded" if sharded else "replicated")
+        key = (str(device), kind)
         if key not in self._state:
-            self._state[key] = torch.tensor([self.seed, 0], dtype=torch.int64, device=device)
+            self._state[key] = torch.tensor([self.seeds[kind], self._offset()], dtype=torch.int64, device=device)
         return self._state[key]
 
+    @contextlib.contextmanager
+    def sharded_region(self, on: bool = True):
+        """Dropout calls inside draw from the rank-dependent generator."""
+        prev = self.default_kind
+        self.default_kind = "sharded" if on else "replicated"
+        try:
+            yield
+        finally:
+            self.default_kind = prev
+
+    # --- call numbering -------------------------------------------------------------------------
     def next_call_id(self) -> int:
         self.call_id += 1
         return self.call_id
-
-    def advance_step(self):
-        """Moves every device state to the next step and restarts call numbering."""
-        for t in self._state.values():
-            t[1:2].add_(_STEP_STRIDE)
-        self.call_id = 0
 
     def get_call_id(self) -> int:
         return self.call_id
 
     def set_call_id(self, v: int):
         self.call_id = int(v)
+
+    # --- advancing ------------------------------------------------------------------------------
+    def advance_micro(self):
+        """Next micro-batch of the same step: a device-side add, legal between graph replays.  Only
+        the graph path uses it (a replay bakes its call ids in); the eager schedules keep one
+        offset per step and let ``call_id`` run on across micro-batches, because a recomputation
+        must find the offset its forward pass saw."""
+        self.micro += 1
+        for t in self._state.values():
+            t[1:2].add_(_MICRO_STRIDE)
+
+    def advance_step(self):
+        """Moves every device state to the next step and restarts micro-batch and call numbering."""
+        delta = _STEP_STRIDE - self.micro * _MICRO_STRIDE
+        self.step += 1
+        self.micro = 0
+        for t in self._state.values():
+            t[1:2].add_(delta)
+        self.call_id = 0
+
+    # --- persistence ----------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return {"seed": self.seeds["sharded"], "replicated_seed": self.seeds["replicated"], "step": self.step}
+
+    def load_state_dict(self, sd: dict):
+        self.seeds["sharded"] = int(sd["seed"])
+        self.seeds["replicated"] = int(sd.get("replicated_seed", sd["seed"]))
+        self.step, self.micro, self.call_id = int(sd.get("step", 0)), 0, 0
+        self._write_all()
 
 
 _state = DropoutState()

@@ -232,6 +232,9 @@ def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, me
                     setattr(m, attr, v // tp)
     if megatron_sp:
         _enter_sequence_parallel(model, seq_dim)
+        # activations between the blocks are sequence shards: their dropout is rank-dependent
+        from ..ops.rng import dropout_state
+        dropout_state().default_kind = "sharded"
     if vocab_parallel:
         apply_vocab_parallel(model, megatron_sp, seq_dim)
     return replaced

@@ -378,6 +378,8 @@ class PipelineEngine:
                     self._exec_schedule(sched)
                     return
             self._graph_copy_in(batch)
+            if mb > 0:
+                dropout_state().advance_micro()     # the replay bakes its call ids in: move the offset
             self._graph.replay()
             self.graph_replay_launches = getattr(self, "graph_replay_launches", 0) + self._graph_launches
             det = self._g_loss.float().clone()
@@ -794,21 +796,35 @@ class PipelineEngine:
         opt = self.optimizer
         ss = opt.grad_sumsq().clone()
         tp = mpu.get_model_parallel_world_size()
+        lo, hi = (opt.start, opt.end) if self.zero else (0, self.flat.numel)
+        offset_of = {id(p): o for p, o in zip(self.flat.params, self.flat.offsets)}
+
+        def owned_sumsq(p):
+            # ``ss`` covers [lo, hi) of the flat gradient buffer only (the reduce-scattered shard
+            # under ZeRO-1): subtract the part of ``p`` inside it, never the unreduced remainder
+            o = offset_of.get(id(p))
+            if o is None:
+                return None
+            s, e = max(o, lo), min(o + p.numel(), hi)
+            if s >= e:
+                return None
+            return self.flat.grad[s:e].float().pow(2).sum()
+
         if tp > 1 and mpu.get_model_parallel_rank() != 0:
             # replicated (non model-parallel) parameters are counted by tp rank 0 only
-            dup = torch.zeros_like(ss)
             for p in self.flat.params:
                 if not getattr(p, "model_parallel", False):
-                    dup[0] += p.main_grad.float().pow(2).sum()
-            ss[0] = ss[0] - dup[0]
+                    v = owned_sumsq(p)
+                    if v is not None:
+                        ss[0] = ss[0] - v
         # a weight shared between stages (tied embeddings) is counted by its first owner only
         for spec in self.module.tied_local.values():
             already_excluded = tp > 1 and mpu.get_model_parallel_rank() != 0 and \
                 not getattr(spec["param"], "model_parallel", False)
-            if self.stage_id != spec["stages"][0] and not self.zero and not already_excluded:
-                mg = getattr(spec["param"], "main_grad", None)
-                if mg is not None:
-                    ss[0] = ss[0] - mg.float().pow(2).sum()
+            if self.stage_id != spec["stages"][0] and not already_excluded:
+                v = owned_sumsq(spec["param"])
+                if v is not None:
+                    ss[0] = ss[0] - v
         if self.zero:
             dist.all_reduce(ss, group=mpu.get_data_parallel_group())
         if tp > 1:

@@ -103,8 +103,11 @@ def get_rng_tracker() -> RNGStatesTracker:
 
 def model_parallel_manual_seed(seed: int):
     """Default generators get ``seed`` (identical inside a tensor-parallel group); the tracker's
-    model-parallel state gets a rank-dependent seed; the dropout kernels' generator is keyed by the
-    rank-dependent seed as well."""
+    model-parallel state gets a rank-dependent seed.  The dropout kernels keep the same pair: a
+    replicated seed without the tensor-parallel rank (activations every tensor-parallel rank
+    holds in full must get one mask) and a sharded seed with it (reference:
+    Merak/core/recompute/checkpointing.py:196-251).  Both differ per data-parallel rank, pipeline
+    stage and sequence-parallel rank, which hold different samples / layers / tokens."""
     tp_rank, tp_size = mpu.get_model_parallel_rank(), mpu.get_model_parallel_world_size()
     sp_rank = mpu.get_sequence_parallel_rank()
     mp_seed = seed + 2718 + tp_size * sp_rank + tp_rank
@@ -113,7 +116,8 @@ def model_parallel_manual_seed(seed: int):
     if torch.cuda.is_available():
         torch.cuda.manual_seed(seed)
     _TRACKER.add(_MODEL_PARALLEL_RNG, mp_seed)
-    dropout_state().manual_seed(mp_seed + 7919 * mpu.get_data_parallel_rank())
+    spread = 7919 * mpu.get_data_parallel_rank() + 104729 * mpu.get_pipe_parallel_rank()
+    dropout_state().manual_seed(mp_seed + spread, replicated_seed=seed + 2718 + tp_size * sp_rank + spread + 15485863)
     return mp_seed
 
 

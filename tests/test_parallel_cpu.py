@@ -65,6 +65,15 @@ def test_dp2_zero1_matches_single(tmp_path, baseline):
     assert_close(run_layout(tmp_path, "dp2z", 2, ["--dp", "2", "--gas", "2", "--zero", "1"]), baseline["gpt2"])
 
 
+def test_dp2_tp2_zero1_clipped_4ranks(tmp_path, baseline):
+    """ZeRO-1 with tensor parallelism and gradient clipping: the global norm counts replicated
+    parameters once, using only the part of each that lies inside the rank's reduce-scattered
+    shard of the flat gradient buffer."""
+    got = run_layout(tmp_path, "dp2tp2z", 4, ["--dp", "2", "--tp", "2", "--gas", "2", "--zero", "1", "--clip", "0.5"])
+    ref = run_layout(tmp_path, "single_clip", 1, ["--clip", "0.5"])
+    assert_close(got, ref)
+
+
 @pytest.mark.parametrize("model", ["gpt2", "bert", "llama"])
 def test_tp2_matches_single(tmp_path, baseline, model):
     assert_close(run_layout(tmp_path, "tp2_" + model, 2, ["--tp", "2", "--model", model]), baseline[model])
