@@ -94,7 +94,9 @@ class MerakArguments:
     no_save_optim: bool = False
     no_load_optim: bool = False
     no_load_rng: bool = False
-    split_inputs: bool = False
+    split_inputs: bool = field(default=False, metadata={
+        "help": "accepted for command-line compatibility; nothing reads it (the same holds for the reference, "
+                "Merak/merak_args/args.py:344)"})
     save_total_limit: int = -1
 
     # ---- tensor / sequence parallel -------------------------------------------------------------
@@ -146,6 +148,8 @@ class MerakArguments:
             self.train_schedule = "full_critical_path_1f1b"
         if not self.activation_checkpointing:
             self.checkpoint_num_layers = 0
+        if self.dealloc_pipeoutput:        # the reference's name for the same switch (args.py:372)
+            self.deallocate_pipeline_outputs = True
         if self.zero_stage not in (None, 0, 1):
             raise ValueError("zero_stage supports only 1 (optimizer-state sharding)")
         if self.tp_overlapping_level not in (0, 1, 2, 3):

@@ -27,10 +27,14 @@ NATIVE_LIB = os.path.join(HERE, "_mrk_native.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",
+    "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr",
 ]
+# Approximate division / exp / flush-to-zero only where the instruction count of an inner loop or
+# an epilogue depends on it (tensor-core kernels); norms, cross entropy, AdamW and the reductions
+# are memory-bound and keep IEEE division, sqrt and exp.
+FAST_MATH_SOURCES = {"gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "attention_fwd.cu", "attention_bwd.cu"}
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 
@@ -79,6 +83,8 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         objs.append(obj)
         if force or _stale(obj, [src], hdr_mtime):
             flags = list(NVCC_FLAGS)
+            if os.path.basename(src) in FAST_MATH_SOURCES:
+                flags.append("--use_fast_math")
             if ptxas_info:
                 flags += ["-Xptxas", "-v"]
             jobs.append([nvcc] + flags + ["-I", CSRC, "-c", src, "-o", obj])

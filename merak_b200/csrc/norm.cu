@@ -424,7 +424,10 @@ MRK_API int mrk_norm_bwd_noalloc(const void* dy, const void* z, const void* dz_e
   const long long cap = (long long)sm_count() * 8;
   const unsigned grid = (unsigned)(M < cap ? M : cap);
   // Blocks add their partial sums into the kNormSlots accumulator rows; the reduction kernel sums
-  // the rows and clears them, so the array is zero again when the next call starts.
+  // the rows and clears them, so a completed call leaves the array zero.  A call whose second
+  // launch failed would leave partial sums behind, so the rows are also cleared up front (a
+  // memset on the caller's stream; it allocates nothing).
+  MRK_CUDA_OK(cudaMemsetAsync(scratch, 0, sizeof(float) * kNormSlots * 2 * kNoAllocMaxH, s));
   if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
   else launch_norm_bwd<128, 2>(p, grid, s);
   MRK_CHECK_LAUNCH();

@@ -15,8 +15,10 @@
 //   * the first call on each device looks up the device address of the built-in array; make that
 //     first call with the device current and before any stream capture is started;
 //   * all calls share the one array: two calls that may overlap on the same GPU (different
-//     streams, different threads) race on it and must be ordered by the caller.  The array is
-//     zero when the library is loaded and every call leaves it zero again.
+//     streams, different threads) race on it and must be ordered by the caller.  Every call
+//     clears the array on the caller's stream before it accumulates into it and a completed call
+//     leaves it zero again, so a call that failed between its two launches (the return code says
+//     so) does not spoil later calls;
 //   * it calls no cudaMalloc / cudaFree and no allocating library routine.
 #pragma once
 #ifdef __cplusplus

@@ -22,45 +22,13 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops.optim import FlatBuffers, FusedAdamW
+from ..amp.loss_scaler import DynamicLossScaler
 from ..ops.rng import dropout_state
 from ..parallel import mpu, p2p
 from ..printer import SynchronizedWallClockTimer, log_dist, see_memory_usage, set_timer_log_rank
 from ..recompute import RNGManager, checkpoint, pre_checkpoint, run_pending_recomputes
 from . import schedules as S
 from .module import PipelineModule
-
-
-class DynamicLossScaler:
-    """fp16 loss scaling with hysteresis (Merak/core/zero/utils.py:232-384)."""
-
-    def __init__(self, init_scale=2.0 ** 16, scale_factor=2.0, scale_window=1000, min_scale=1.0, hysteresis=2,
-                 static: bool = False):
-        self.cur_scale = float(init_scale)
-        self.scale_factor, self.scale_window, self.min_scale = scale_factor, scale_window, min_scale
-        self.delayed_shift, self.cur_hysteresis = hysteresis, hysteresis
-        self.last_overflow_iter, self.cur_iter = -1, 0
-        self.static = static
-
-    def update_scale(self, overflow: bool):
-        if self.static:
-            return
-        if overflow:
-            if self.delayed_shift == 1 or self.cur_hysteresis == 1:
-                self.cur_scale = max(self.cur_scale / self.scale_factor, self.min_scale)
-            else:
-                self.cur_hysteresis -= 1
-            self.last_overflow_iter = self.cur_iter
-        else:
-            if (self.cur_iter - self.last_overflow_iter) % self.scale_window == 0:
-                self.cur_hysteresis = self.delayed_shift
-                self.cur_scale *= self.scale_factor
-        self.cur_iter += 1
-
-    def state_dict(self):
-        return dict(self.__dict__)
-
-    def load_state_dict(self, sd):
-        self.__dict__.update(sd)
 
 
 def _as_dict(batch, names: Sequence[str]) -> Dict[str, torch.Tensor]:
@@ -131,15 +99,9 @@ class PipelineEngine:
     # set-up
     # ------------------------------------------------------------------------------------------
     def _configure_precision(self):
-        a = self.args
-        self.loss_scaler = None
-        if a.fp16:
-            if a.loss_scale and a.loss_scale > 0:
-                self.loss_scaler = DynamicLossScaler(init_scale=a.loss_scale, static=True)
-            else:
-                self.loss_scaler = DynamicLossScaler(init_scale=2.0 ** min(a.initial_scale_power, 24),
-                                                     scale_window=a.loss_scale_window, min_scale=a.min_loss_scale,
-                                                     hysteresis=a.hysteresis)
+        from ..amp import MixedPrecisionConfig
+        self.amp = MixedPrecisionConfig(self.args)
+        self.loss_scaler = self.amp.make_loss_scaler()
 
     def _unique_params(self) -> List[nn.Parameter]:
         seen, out = set(), []
@@ -194,13 +156,28 @@ class PipelineEngine:
                                         eps=a.adam_epsilon, weight_decay=a.weight_decay, shard=shard,
                                         max_grad_norm=a.max_grad_norm)
         else:
-            self.optimizer = optimizer if optimizer is not None else optimizer_factory(params)
-            self.zero = False
+            inner = optimizer if optimizer is not None else optimizer_factory(params)
+            self.flat_expert, self.optimizer_expert, self.fused_dp = None, None, None
+            low_precision = params[0].dtype in (torch.bfloat16, torch.float16)
+            if (self.zero or low_precision) and isinstance(inner, torch.optim.Optimizer):
+                # a user optimizer gets fp32 master weights (bf16 / fp16 parameters) and, with
+                # zero_stage 1, optimizer-state sharding on the same flat buffers the fused path uses
+                # (Merak/core/zero/stage1.py:42-75, Merak/core/amp/fp16_optimizer.py:36-358)
+                from ..zero.stage1 import ShardedMasterOptimizer
+                self.optimizer = ShardedMasterOptimizer(
+                    inner, dp_rank=self.dp_rank, dp_size=self.dp_size, shard=self.zero,
+                    max_grad_norm=a.max_grad_norm, allow_untested=bool(a.zero_allow_untested_optimizer))
+                self.flat = self.optimizer.flat
+            else:
+                self.optimizer = inner
+                self.zero = False
         if getattr(self, "optimizer_expert", None) is not None:
             self.optimizer_expert.param_groups = self.optimizer.param_groups     # one learning-rate schedule
         self.lr_scheduler = lr_scheduler
         if self.lr_scheduler is None and lr_scheduler_factory is not None:
-            self.lr_scheduler = lr_scheduler_factory(self.optimizer)
+            # torch schedulers insist on a torch.optim.Optimizer: give them the wrapped one (the
+            # parameter-group dicts, hence the learning rates, are shared)
+            self.lr_scheduler = lr_scheduler_factory(getattr(self.optimizer, "optimizer", self.optimizer))
 
     def _norm_excluded_params(self) -> List[nn.Parameter]:
         """Parameters whose gradient this rank must not count in the global gradient norm: replicas of
@@ -758,6 +735,9 @@ class PipelineEngine:
                 self._grads_reduced = True
                 return
             g = self.flat.grad
+            pre = self._dp_pre_scale()
+            if pre != 1.0:
+                g.mul_(pre)
             if self.zero:
                 self._reduce_scatter_inplace(g, g.numel() // self.dp_size, group)
             else:
@@ -783,6 +763,40 @@ class PipelineEngine:
                     bucket.append(gr)
                     size += gr.numel()
         self._grads_reduced = True
+
+    def _dp_pre_scale(self) -> float:
+        """Factor applied to the gradients before the data-parallel collective
+        (``prescale_gradients`` / ``gradient_predivide_factor``, Merak/core/zero/stage1.py:614-668):
+        prescaling divides by the group size up front, a predivide factor ``f`` divides by ``f`` up
+        front and leaves ``f / dp`` for afterwards.  The fused kernels reduce in fp32 and fold
+        ``1 / dp`` into the optimizer's gradient scale, so they ignore both."""
+        if self.dp_size == 1 or getattr(self, "fused_dp", None) is not None or self.flat is None:
+            return 1.0
+        if getattr(self.args, "prescale_gradients", False):
+            return 1.0 / self.dp_size
+        f = float(getattr(self.args, "gradient_predivide_factor", 1.0) or 1.0)
+        return 1.0 / f
+
+    def _dp_post_scale(self) -> float:
+        return 1.0 / (self.dp_size * self._dp_pre_scale()) if self.dp_size > 1 else 1.0
+
+    def _zero_allgather(self):
+        """Parameter all-gather of the unfused ZeRO-1 step in buckets of
+        ``zero_allgather_bucket_size`` elements per rank (Merak/core/zero/stage1.py:734-757)."""
+        group = mpu.get_data_parallel_group()
+        per = self.optimizer.end - self.optimizer.start
+        bucket = max(1, min(per, int(getattr(self.args, "zero_allgather_bucket_size", per) or per)))
+        model = self.flat.model
+        if bucket >= per:
+            dist.all_gather_into_tensor(model, model[self.optimizer.start:self.optimizer.end].clone(), group=group)
+            return
+        tmp = torch.empty(self.dp_size * bucket, dtype=model.dtype, device=model.device)
+        for lo in range(0, per, bucket):
+            b = min(bucket, per - lo)
+            src = model[self.optimizer.start + lo:self.optimizer.start + lo + b].clone()
+            dist.all_gather_into_tensor(tmp[:self.dp_size * b], src, group=group)
+            for k in range(self.dp_size):
+                model[k * per + lo:k * per + lo + b].copy_(tmp[k * b:(k + 1) * b])
 
     def _reduce_scatter_inplace(self, g: torch.Tensor, per: int, group):
         out = torch.empty(per, dtype=g.dtype, device=g.device)
@@ -837,7 +851,7 @@ class PipelineEngine:
         if self.wall_clock_breakdown:
             self.timers("step").start()
         a = self.args
-        grad_scale = 1.0 / self.dp_size if self.dp_size > 1 else 1.0
+        grad_scale = self._dp_post_scale()
         if self.loss_scaler is not None:
             grad_scale /= self.loss_scaler.cur_scale
         if self.flat is not None:
@@ -867,8 +881,7 @@ class PipelineEngine:
                     sumsq = sumsq + expert_ss
                 self.optimizer.step(grad_scale=grad_scale, sumsq=sumsq)
                 if self.zero:
-                    dist.all_gather_into_tensor(self.flat.model, self.flat.model[self.optimizer.start:self.optimizer.end]
-                                                .clone(), group=mpu.get_data_parallel_group())
+                    self._zero_allgather()
             if getattr(self, "optimizer_expert", None) is not None:
                 self.optimizer_expert.step(grad_scale=grad_scale, sumsq=sumsq)
                 self.flat_expert.zero_grad()

@@ -45,6 +45,8 @@ def main():
     ap.add_argument("--dealloc", type=int, default=0)
     ap.add_argument("--comm", default="nccl")
     ap.add_argument("--clip", type=float, default=1.0)
+    ap.add_argument("--inject_overflow", type=int, default=-1, help="step whose gradients get an inf written in")
+    ap.add_argument("--user_opt", default="", help="sgd | adamw: a torch.optim optimizer built by the trainer hook")
     ap.add_argument("--out", required=True)
     o = ap.parse_args()
 
@@ -77,11 +79,13 @@ def main():
         no_cuda=(o.device == "cpu"), train_schedule=o.schedule, activation_checkpointing=bool(o.recompute),
         activation_checkpoint_ratio=[o.ratio] if o.ratio else None, zero_stage=1 if o.zero else None,
         parallel_vocab=bool(o.parallel_vocab), sequence_parallel=o.sp > 1, tp_overlapping_level=o.tp_overlap, megatron_sequence_parallel=bool(o.megatron_sp),
-        split_method=o.split, bf16=(o.dtype == "bf16"), seed=1234, save=bool(o.save_dir), save_steps=o.steps,
+        split_method=o.split, bf16=(o.dtype == "bf16"), fp16=(o.dtype == "fp16"), initial_scale_power=8, hysteresis=1,
+        loss_scale_window=3, seed=1234, save=bool(o.save_dir), save_steps=o.steps,
         resume_from_checkpoint=o.resume, comm_mode=o.comm, max_grad_norm=o.clip,
         deallocate_pipeline_outputs=bool(o.dealloc))
     # every data-parallel layout must see the same global batch per step: dataset order is by index
     ds = SyntheticTokenDataset(V, L, 16, task=task, seed=7)      # two global batches, revisited
+    FixedOrderTrainer.user_opt = o.user_opt
     trainer = FixedOrderTrainer(model, args, train_dataset=ds)
     losses = []
     engine = trainer.init_engine()
@@ -92,14 +96,27 @@ def main():
     if o.resume:
         for _ in range(it * o.gas):        # the fixed-order loader restarts at 0: skip what was consumed
             next(data_iter)
-    for _ in range(o.steps):
+    scales, skipped = [], []
+    reduce_grads = engine._exec_reduce_grads
+    for step in range(o.steps):
+        if step == o.inject_overflow:
+            def poisoned():
+                engine.flat.grad[3] = float("inf")        # host-injected overflow
+                reduce_grads()
+            engine._exec_reduce_grads = poisoned
+        else:
+            engine._exec_reduce_grads = reduce_grads
+        before = engine.flat.model.clone() if engine.flat is not None else None
         losses.append(float(engine.train_batch(data_iter)))
+        if engine.loss_scaler is not None:
+            scales.append(engine.loss_scaler.cur_scale)
+            skipped.append(bool(torch.equal(before, engine.flat.model)))
         trainer.params.step()
     if o.save_dir:
         trainer.save_checkpoint()
     if torch.distributed.get_rank() == 0:
         with open(o.out, "w") as f:
-            json.dump({"losses": losses}, f)
+            json.dump({"losses": losses, "scales": scales, "skipped": skipped}, f)
     torch.distributed.barrier()
     Merak.initialize.destroy()
 
@@ -125,6 +142,20 @@ class _SequentialSampler:
 
 
 class FixedOrderTrainer(Merak.MerakTrainer):
+    user_opt = ""
+
+    def _wants_custom_optimizer(self):
+        return bool(self.user_opt)
+
+    def create_optimizer(self, params):
+        params = list(params)
+        decay = [p for p in params if p.dim() > 1]
+        rest = [p for p in params if p.dim() <= 1]
+        groups = [{"params": decay, "weight_decay": 0.01}, {"params": rest, "weight_decay": 0.0}]
+        if self.user_opt == "sgd":
+            return torch.optim.SGD(groups, lr=0.05, momentum=0.9)
+        return torch.optim.AdamW(groups, lr=self.args.learning_rate)
+
     def create_dataloader(self, dataset, batch_size, train=True):
         from torch.utils.data import DataLoader
         from merak_b200.parallel import mpu

@@ -65,6 +65,17 @@ def test_dp2_zero1_matches_single(tmp_path, baseline):
     assert_close(run_layout(tmp_path, "dp2z", 2, ["--dp", "2", "--gas", "2", "--zero", "1"]), baseline["gpt2"])
 
 
+@pytest.mark.parametrize("opt", ["sgd", "adamw"])
+def test_dp2_zero1_user_optimizer_matches_single(tmp_path, opt):
+    """An optimizer built by the ``create_optimizer`` hook (two parameter groups) is sharded over the
+    data-parallel group by the ZeRO-1 wrapper and reproduces its single-process run."""
+    single = run_layout(tmp_path, "uo_single_" + opt, 1, ["--user_opt", opt, "--steps", "5"])
+    assert single[-1] < single[0]
+    z = run_layout(tmp_path, "uo_dp2z_" + opt, 2, ["--user_opt", opt, "--steps", "5", "--dp", "2", "--gas", "2",
+                                                   "--zero", "1"])
+    assert_close(z, single)
+
+
 def test_dp2_tp2_zero1_clipped_4ranks(tmp_path, baseline):
     """ZeRO-1 with tensor parallelism and gradient clipping: the global norm counts replicated
     parameters once, using only the part of each that lies inside the rank's reduce-scattered

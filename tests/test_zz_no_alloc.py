@@ -5,8 +5,8 @@ Some users of the kernel library cannot allocate device memory when they need th
 run under an allocator lock, inside a pre-partitioned memory budget, or are simply forbidden to
 call cudaMalloc), so the library offers a variant whose partial-sum workspace is a fixed array
 inside the shared object.  The test drives it the way such a caller would: through the exported C
-symbol, with caller-owned input and output buffers only, twice in a row so that the second call
-runs on a scratch array that still holds the first call's partial sums.
+symbol, with caller-owned input and output buffers only, twice in a row with different shapes so
+that the second call reuses the array the first one accumulated into and cleared.
 """
 import ctypes
 import os

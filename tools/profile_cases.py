@@ -1,7 +1,7 @@
 """Small stand-alone cases of the hot kernels, sized for a profiler capture: inputs larger than the
 126 MB L2 so DRAM figures mean something, a few hundred MB on the device, a handful of launches.
 
-    python -m merak_b200.ops.profile_cases <case> [--iters N]
+    python tools/profile_cases.py <case> [--iters N]
 
 Cases: gemm, gemm_gelu, gemm_k1024, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce,
 cross_entropy, rope, swiglu, embedding, colsum, moe_push.
@@ -14,10 +14,15 @@ from __future__ import annotations
 import argparse
 import ctypes
 
+import os
+import sys
+
 import torch
 
-from . import _lib
-from . import gemm as G
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from merak_b200.ops import _lib          # noqa: E402
+from merak_b200.ops import gemm as G     # noqa: E402
 
 
 def _time(fn, iters):
@@ -63,7 +68,7 @@ def main():
         ms = _time(lambda: G.gemm(dy, x, a_mn=True, b_mn=True, out=dw, accumulate=True), it)
         print("wgrad %dx%dx%d: %.3f ms  %.1f TFLOP/s" % (N, K, M, ms, 2.0 * M * N * K / ms / 1e9))
     elif o.case in ("attn_fwd", "attn_bwd"):
-        from .attention import flash_attention
+        from merak_b200.ops.attention import flash_attention
         B, H, L, D = 32, 16, 512, 64
         q, k, v = (torch.randn(B, L, H, D, device=dev, dtype=bf, requires_grad=True) for _ in range(3))
         fl = 4.0 * B * H * L * L * D
@@ -77,7 +82,7 @@ def main():
             ms = _time(lambda: torch.autograd.grad(out, (q, k, v), do, retain_graph=True), it)
             print("attn_bwd B%d H%d L%d D%d: %.3f ms  %.1f TFLOP/s" % (B, H, L, D, ms, 2.5 * fl / ms / 1e9))
     elif o.case == "norm":
-        from .norm import fused_norm
+        from merak_b200.ops.norm import fused_norm
         M, H = 65536, 1024
         x = torch.randn(M, H, device=dev, dtype=bf, requires_grad=True)
         res = torch.randn(M, H, device=dev, dtype=bf)
@@ -141,7 +146,7 @@ def main():
                                                                  0, 50, _lib.stream_ptr()), "pull"), it)
             print("tp_reduce_pull %dx%d from %d ranks: %.3f ms  %.0f GB/s" % (M // n, N, n, ms, (n + 1) * (M // n) * N * 2 / ms / 1e6))
     elif o.case == "cross_entropy":
-        from .cross_entropy import softmax_cross_entropy
+        from merak_b200.ops.cross_entropy import softmax_cross_entropy
         M, V = 8192, 30522
         logits = (torch.randn(M, V, device=dev, dtype=bf) * 2).requires_grad_(True)
         labels = torch.randint(0, V, (M,), device=dev)
@@ -154,7 +159,7 @@ def main():
         # forward reads the logits once, backward reads them again and writes the gradient
         print("cross_entropy fwd+bwd %dx%d: %.3f ms  %.0f GB/s" % (M, V, ms, 3.0 * M * V * 2 / ms / 1e6))
     elif o.case == "rope":
-        from .elementwise import apply_rope, rope_tables
+        from merak_b200.ops.elementwise import apply_rope, rope_tables
         B, L, H, D = 8, 4096, 32, 128
         x = torch.randn(B, L, H, D, device=dev, dtype=bf)
         cos, sin = rope_tables(L, D, 10000.0, dev)
@@ -162,7 +167,7 @@ def main():
             ms = _time(lambda: apply_rope(x, cos, sin), it)
         print("rope B%d L%d H%d D%d: %.3f ms  %.0f GB/s" % (B, L, H, D, ms, 2.0 * x.numel() * 2 / ms / 1e6))
     elif o.case == "swiglu":
-        from .elementwise import swiglu
+        from merak_b200.ops.elementwise import swiglu
         M, F = 16384, 11008
         gu = torch.randn(M, 2 * F, device=dev, dtype=bf, requires_grad=True)
         with torch.no_grad():
@@ -173,7 +178,7 @@ def main():
         ms = _time(lambda: torch.autograd.grad(y, gu, dy, retain_graph=True), it)
         print("swiglu bwd %dx%d: %.3f ms  %.0f GB/s" % (M, F, ms, 5.0 * M * F * 2 / ms / 1e6))
     elif o.case == "embedding":
-        from .elementwise import embedding_sum
+        from merak_b200.ops.elementwise import embedding_sum
         T, H, V = 65536, 1024, 30522
         table = torch.randn(V, H, device=dev, dtype=bf, requires_grad=True)
         ids = torch.randint(0, V, (64, T // 64), device=dev)
@@ -185,7 +190,7 @@ def main():
         ms = _time(lambda: torch.autograd.grad(out, table, dy, retain_graph=True), it)
         print("embedding bwd %d tokens x %d: %.3f ms" % (T, H, ms))
     elif o.case == "colsum":
-        from .elementwise import colsum
+        from merak_b200.ops.elementwise import colsum
         M, N = 16384, 4096
         x = torch.randn(M, N, device=dev, dtype=bf)
         out = torch.zeros(N, device=dev)
