@@ -7,8 +7,10 @@ nodes are the coarse blocks the sharder works with:
   builtin, every class the user lists, and the framework's own block classes are leaves).  This
   replaces the Hugging Face tracer the reference depends on
   (Merak/core/fx/tracer/_symbolic_trace.py:32-127), which no longer exists in transformers 5.x.
-* ``method='dynamo'``: ``torch.export`` (Merak/core/fx/tracer/_dynamo_trace.py:22-60); the flat
-  ATen graph has no module nodes, so only tensor-parallel degree 1 is supported on that path.
+* ``method='dynamo'``: ``torch.export`` (Merak/core/fx/tracer/_dynamo_trace.py:22-60) followed by
+  folding the flat ATen graph back into calls of the model's leaf modules
+  (``fx/export_trace.py``); this is also what ``'fx'`` falls back to for models symbolic tracing
+  rejects, which with transformers 5.x is every Hugging Face model.
 
 ``make_dummy_inputs`` builds small CPU inputs from a model config for tracing
 (Merak/core/fx/tracer/utils.py:62-191).
@@ -94,20 +96,38 @@ def fx_trace(model: nn.Module, input_names: Sequence[str], leaf_modules: Iterabl
     return gm
 
 
-def dynamo_trace(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor]) -> fx.GraphModule:
-    """``torch.export`` based tracing for models plain fx cannot handle."""
-    exported = torch.export.export(model, args=(), kwargs=dict(dummy_inputs), strict=False)
-    return exported.module()
+def dynamo_trace(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor],
+                 leaf_modules: Iterable[type] = ()) -> fx.GraphModule:
+    """``torch.export`` based tracing for models plain fx cannot handle; the flat ATen graph is
+    folded back into ``call_module`` nodes on the model's leaf modules (``fx.export_trace``)."""
+    from ..parallel import mpu
+    from .export_trace import export_trace
+    # a symbolic batch size yields integer values in the graph; between pipeline stages only tensors
+    # travel, so with more than one stage the batch size of the dummy inputs is baked in
+    dynamic = mpu.get_pipe_parallel_world_size() == 1
+    return export_trace(model, dummy_inputs, tuple(leaf_modules) + framework_leaf_classes(), dynamic_batch=dynamic)
 
 
 def trace_model(model: nn.Module, input_names: Sequence[str], method: str = "fx",
                 leaf_modules: Iterable[type] = (), dummy_inputs: Optional[Dict[str, torch.Tensor]] = None):
+    """``method='fx'`` tries symbolic tracing first and, when the model defeats it (Hugging Face
+    models: decorators, mask helpers, data-dependent Python), falls back to the export path if dummy
+    inputs are at hand; ``method='dynamo'`` goes to the export path directly."""
     if method == "fx":
-        return fx_trace(model, input_names, leaf_modules)
+        try:
+            return fx_trace(model, input_names, leaf_modules)
+        except Exception as exc:
+            if dummy_inputs is None:
+                raise
+            from ..printer import log_dist
+            log_dist("torch.fx could not trace %s (%s: %s); using torch.export" % (
+                type(model).__name__, type(exc).__name__, str(exc).splitlines()[0][:120] if str(exc) else ""), ranks=[0])
+            method = "dynamo"
     if method == "dynamo":
         if dummy_inputs is None:
             raise ValueError("trace_method='dynamo' needs dummy inputs")
-        return dynamo_trace(model, dummy_inputs)
+        dummy = {k: dummy_inputs[k] for k in input_names if k in dummy_inputs} or dict(dummy_inputs)
+        return dynamo_trace(model, dummy, leaf_modules)
     raise ValueError("unknown trace method %r" % method)
 
 

@@ -12,6 +12,8 @@ Every primitive is a no-op when its group has one rank, so single-process code p
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 
@@ -29,9 +31,25 @@ def _tp():
     return mpu.get_model_parallel_group(), mpu.get_model_parallel_world_size(), mpu.get_model_parallel_rank()
 
 
+_SHAPE_ONLY = [False]
+
+
+@contextlib.contextmanager
+def shape_only_collectives():
+    """While a model is being exported to a graph only output shapes matter: every collective of
+    this module becomes a local operation with the same output shape (all-reduce: identity;
+    all-gather: the local tensor repeated; reduce-scatter: the first chunk).  The folded graph calls
+    the real wrappers afterwards (``fx.export_trace``)."""
+    prev, _SHAPE_ONLY[0] = _SHAPE_ONLY[0], True
+    try:
+        yield
+    finally:
+        _SHAPE_ONLY[0] = prev
+
+
 def _reduce(x):
     group, n, _ = _tp()
-    if n == 1:
+    if n == 1 or _SHAPE_ONLY[0]:
         return x
     x = x.contiguous()
     dist.all_reduce(x, group=group)
@@ -42,6 +60,8 @@ def _all_gather_stacked(x, group, n):
     """All-gather into a ``[n, *x.shape]`` tensor (allocated as the flat concatenation every
     backend accepts)."""
     x = x.contiguous()
+    if _SHAPE_ONLY[0]:
+        return x.unsqueeze(0).expand((n,) + tuple(x.shape)).contiguous()
     flat = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
     dist.all_gather_into_tensor(flat, x, group=group)
     return flat.view((n,) + tuple(x.shape))
@@ -83,6 +103,8 @@ def _reduce_scatter_dim(x, dim, group, n):
     if n == 1:
         return x
     assert x.shape[dim] % n == 0
+    if _SHAPE_ONLY[0]:
+        return x.chunk(n, dim=dim)[0].contiguous()
     parts = torch.cat([c.contiguous() for c in x.chunk(n, dim=dim)], 0)     # [n*chunk0, ...]
     out = torch.empty((parts.shape[0] // n,) + tuple(parts.shape[1:]), dtype=x.dtype, device=x.device)
     dist.reduce_scatter_tensor(out, parts, group=group)

@@ -80,6 +80,9 @@ def communicate(send_next: Sequence[torch.Tensor] = (), send_prev: Sequence[torc
     next_rank = mpu.get_pipeline_model_parallel_next_rank()
     ops, keep = [], []
     dev = None
+    # a shard may hand over a view (a transposed or sliced activation): the wire wants dense memory
+    send_prev = [t if t.is_contiguous() else t.contiguous() for t in send_prev]
+    send_next = [t if t.is_contiguous() else t.contiguous() for t in send_next]
     # Order: sends toward prev, receives from prev, sends toward next, receives from next - every
     # rank uses the same order so neighbouring batches match up.
     for t in send_prev:

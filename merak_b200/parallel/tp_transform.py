@@ -198,6 +198,35 @@ def feature_lists(model_type: Optional[str]):
     return feats["col"], feats["row"]
 
 
+def convert_conv1d(model: nn.Module, fragments: Sequence[str]) -> int:
+    """Hugging Face GPT-2 style ``Conv1D`` layers (``y = x @ W + b`` with ``W`` of shape [in, out])
+    named in the feature lists become ``nn.Linear`` layers holding ``W^T``, the form the column /
+    row wrappers slice (the reference lists ``Conv1D`` next to ``nn.Linear``,
+    Merak/core/tensor_parallel/mp_attrs.py:22,43-147).  A fused query/key/value projection
+    (``out = 3 * in``) is marked so that each of its three parts is split separately."""
+    try:
+        from transformers.pytorch_utils import Conv1D
+    except Exception:
+        return 0
+    n = 0
+    for parent_name, parent in list(model.named_modules()):
+        for child_name, child in list(parent.named_children()):
+            full = (parent_name + "." if parent_name else "") + child_name
+            if not isinstance(child, Conv1D) or not _matches(full, fragments):
+                continue
+            in_f, out_f = child.weight.shape
+            lin = nn.Linear(in_f, out_f, bias=child.bias is not None, device="meta")
+            lin.weight = nn.Parameter(child.weight.data.t().contiguous())
+            if child.bias is not None:
+                lin.bias = nn.Parameter(child.bias.data)
+            lin.from_conv1d = True
+            if out_f == 3 * in_f:
+                lin.fused_parts = 3
+            setattr(parent, child_name, lin)
+            n += 1
+    return n
+
+
 def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, megatron_sp: bool = False,
                           seq_dim: int = 1, vocab_parallel: bool = False, skip: Sequence[str] = ("lm_head",)):
     """In-place transform; returns the list of replaced module names."""
@@ -207,6 +236,7 @@ def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, me
     model_type = model_type or getattr(getattr(model, "config", None), "model_type", None)
     col, row = feature_lists(model_type)
     replaced = []
+    convert_conv1d(model, col + row)
     for parent_name, parent in list(model.named_modules()):
         for child_name, child in list(parent.named_children()):
             full = (parent_name + "." if parent_name else "") + child_name

@@ -184,7 +184,9 @@ class MerakTrainer:
     def get_dummy_inputs(self) -> Optional[Dict[str, torch.Tensor]]:
         if self.train_dataset is None:
             return None
-        sample = self.data_collator([self.train_dataset[0], self.train_dataset[min(1, len(self.train_dataset) - 1)]])
+        # one micro-batch of real samples: a graph exported with static shapes bakes this batch size in
+        n = max(1, min(int(self.args.per_device_train_batch_size), len(self.train_dataset)))
+        sample = self.data_collator([self.train_dataset[i] for i in range(n)])
         if isinstance(sample, dict):
             names = self.args.input_names or [k for k in sample if k not in ("labels", "label")]
             return {k: sample[k] for k in names if k in sample}
