@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--dropout", type=float, default=0.1)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--cuda-graph", type=int, default=1)
+    ap.add_argument("--dp-overlap", type=int, default=1, help="reduce gradients while the backward pass runs")
     return ap.parse_args()
 
 
@@ -118,7 +119,8 @@ def build_ours(o, device):
         per_device_train_batch_size=o.mbs, gradient_accumulation_steps=1, max_steps=10 ** 9,
         learning_rate=1e-4, weight_decay=0.01, max_grad_norm=1.0, lr_scheduler_type="constant",
         logging_steps=0, wall_clock_breakdown=False, report_to="none", activation_checkpointing=False,
-        split_method="layer_split", comm_mode=o.comm, cuda_graph=bool(o.cuda_graph), seed=0)
+        split_method="layer_split", comm_mode=o.comm, cuda_graph=bool(o.cuda_graph), seed=0,
+        overlap_dp_reduce=bool(o.dp_overlap))
     ds = SyntheticTokenDataset(cfg.vocab_size, o.seq, 1 << 20, task="mlm", seed=0)
     trainer = Merak.MerakTrainer(model, args, train_dataset=ds)
     engine = trainer.init_engine()
@@ -216,6 +218,7 @@ def run_ours(o):
                        "seq_len": o.seq, "micro_batch_per_gpu": o.mbs, "parallelism": "dp%d" % world,
                        "hidden_dropout": o.dropout, "attention_dropout": 0.0, "optimizer": "AdamW fp32 master, clip 1.0",
                        "comm": o.comm, "cuda_graph": bool(o.cuda_graph),
+                       "dp_reduce": "overlapped with the backward pass" if (o.dp_overlap and world > 1) else "after backward",
                        "l2_policy": "no flush: one step touches >20 GB (weights, activations, optimizer state), "
                                     "far more than the 126 MB L2"},
             "clocks": clocks, "gpu_launches": int(launches),

@@ -138,6 +138,8 @@ class MerakArguments:
     # ---- B200 runtime ---------------------------------------------------------------------------
     cuda_graph: bool = field(default=False, metadata={"help": "Capture each stage's micro-batch step in a CUDA graph."})
     overlap_dp_reduce: bool = field(default=True, metadata={"help": "Reduce DP gradients during the last backward."})
+    dp_overlap_bucket_elems: int = field(default=8 << 20, metadata={
+        "help": "smallest piece of the gradient buffer (elements) worth its own overlapped reduction launch"})
 
     # filled by the trainer
     params_dtype: Any = field(default=None, repr=False)

@@ -87,6 +87,7 @@ def _declare(lib):
     sig("mrk_dp_reduce_scatter", c_int, P, P, c_int, c_int, c_ll, c_ll, P, c_uint, c_int, c_int, P)
     sig("mrk_dp_adamw_allgather", c_int, P, P, c_int, c_int, c_ll, c_ll, P, P, P, P, P, P, c_float, c_float,
         P, P, P, c_uint, c_int, c_int, c_int, P)
+    sig("mrk_dp_reduce_region", c_int, P, P, c_int, c_int, c_ll, c_ll, c_ll, c_ll, P, P, c_uint, c_int, c_int, P)
     sig("mrk_dp_norm_gather", c_int, P, c_int, c_int, P, c_uint, c_int, c_int, P)
     sig("mrk_tp_reduce_pull", c_int, P, P, c_int, c_int, P, c_ll, c_int, c_int, P, c_uint, c_int, c_int, P)
     sig("mrk_tp_gather_rows", c_int, P, P, c_int, c_int, P, c_ll, c_int, c_int, c_uint, c_int, c_int, P)
@@ -133,6 +134,27 @@ def use_kernels(*tensors) -> bool:
     """True when the inputs live on a CUDA device, i.e. the sm_100a kernels must run."""
     return len(tensors) > 0 and all(t is None or t.is_cuda for t in tensors) and any(
         t is not None for t in tensors)
+
+
+_FALLBACK_SEEN = set()
+
+
+def note_library_fallback(op: str, x) -> None:
+    """A CUDA tensor reached an op whose sm_100a kernel does not take its dtype / shape (the kernels
+    are bf16), so a PyTorch library op runs instead.  Said once per (op, dtype) so it is never
+    silent; ``MERAK_STRICT_KERNELS=1`` turns it into an error."""
+    if x is None or not getattr(x, "is_cuda", False):
+        return                                        # CPU tensors: the PyTorch formulation is the path
+    key = (op, str(x.dtype), tuple(x.shape[-1:]))
+    if key in _FALLBACK_SEEN:
+        return
+    _FALLBACK_SEEN.add(key)
+    msg = ("%s: no sm_100a kernel for dtype %s / last dim %d on a CUDA tensor; running the PyTorch library op"
+           % (op, x.dtype, x.shape[-1]))
+    if os.environ.get("MERAK_STRICT_KERNELS", "0") == "1":
+        raise KernelError(msg)
+    import warnings
+    warnings.warn(msg, RuntimeWarning, stacklevel=3)
 
 
 def check(rc: int, what: str):

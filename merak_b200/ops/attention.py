@@ -149,12 +149,13 @@ def flash_attention_packed(qkv: torch.Tensor, num_q_heads: int, num_kv_heads: in
     """Self-attention on ``qkv`` of shape ``[B, L, Hq + 2*Hkv, D]``; returns ``[B, L, Hq, D]``."""
     D = qkv.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if flop_counter.enabled():
-        flop_counter.add(4 * qkv.shape[0] * num_q_heads * qkv.shape[1] * qkv.shape[1] * D // (2 if causal else 1))
     if not _lib.use_kernels(qkv) or qkv.dtype != torch.bfloat16 or D not in (64, 128):
+        _lib.note_library_fallback("attention", qkv)
         q, k, v = (qkv[:, :, :num_q_heads], qkv[:, :, num_q_heads:num_q_heads + num_kv_heads],
                    qkv[:, :, num_q_heads + num_kv_heads:])
         return attention_reference(q, k, v, key_bias, causal, scale)
+    if flop_counter.enabled():
+        flop_counter.add(4 * qkv.shape[0] * num_q_heads * qkv.shape[1] * qkv.shape[1] * D // (2 if causal else 1))
     return _FlashAttentionPacked.apply(qkv, num_q_heads, num_kv_heads, key_bias, causal, scale)
 
 
@@ -168,10 +169,10 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     """
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if flop_counter.enabled():
-        flop_counter.add(4 * q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1] * D // (2 if causal else 1))
     if not _lib.use_kernels(q, k, v):
         return attention_reference(q, k, v, key_bias, causal, scale)
+    if flop_counter.enabled():
+        flop_counter.add(4 * q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1] * D // (2 if causal else 1))
     assert q.dtype == torch.bfloat16, "tcgen05 attention takes bf16"
     assert D in (64, 128), "head_dim must be 64 or 128 on the sm_100a path"
     return _FlashAttention.apply(q, k, v, key_bias, causal, scale)

@@ -105,11 +105,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     assert K == Kb, "inner dimensions differ: %d vs %d" % (K, Kb)
-    if flop_counter.enabled():
-        flop_counter.add(2 * M * N * K)
     if not _lib.use_kernels(a, b):
         return _reference(a, b, a_mn, b_mn, bias, act, aux_in, aux_mode, alpha, out, accumulate,
                           out.dtype if out is not None else out_dtype, want_preact)
+    if flop_counter.enabled():
+        flop_counter.add(2 * M * N * K)
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
     if a.stride(1) != 1 or (a.stride(0) * 2) % 16 != 0 or a.data_ptr() % 16 != 0:
         a = a.contiguous()

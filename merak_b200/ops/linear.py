@@ -93,10 +93,11 @@ class _Linear(torch.autograd.Function):
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     if not _lib.use_kernels(x, weight) or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
-        if flop_counter.enabled():
-            flop_counter.add(2 * (x.numel() // x.shape[-1]) * weight.shape[0] * weight.shape[1])
+        _lib.note_library_fallback("linear", x)
         y = F.linear(x, weight, bias)
         return y + residual if residual is not None else y
+    if flop_counter.enabled():          # the kernel's work is invisible to the ATen-level counter
+        flop_counter.add(2 * (x.numel() // x.shape[-1]) * weight.shape[0] * weight.shape[1])
     return _Linear.apply(x, weight, bias, residual, False)
 
 
@@ -150,11 +151,12 @@ class _MLP(torch.autograd.Function):
 def mlp(x, w1, b1, w2, b2, act: int = G.ACT_GELU_ERF, residual=None):
     """``act(x w1^T + b1) w2^T + b2 (+ residual)``."""
     if not _lib.use_kernels(x, w1, w2) or x.dtype != torch.bfloat16:
-        if flop_counter.enabled():
-            flop_counter.add(2 * (x.numel() // x.shape[-1]) * (w1.numel() + w2.numel()))
+        _lib.note_library_fallback("mlp", x)
         hdn = G.act_forward(act, F.linear(x, w1, b1))
         y = F.linear(hdn, w2, b2)
         return y + residual if residual is not None else y
+    if flop_counter.enabled():
+        flop_counter.add(2 * (x.numel() // x.shape[-1]) * (w1.numel() + w2.numel()))
     return _MLP.apply(x, w1, b1, w2, b2, act, residual, False)
 
 

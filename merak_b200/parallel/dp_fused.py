@@ -76,15 +76,34 @@ class FusedDataParallel:
         self.lo = self.rank * self.per
         self._norm_tmp = torch.zeros(2, dtype=torch.float32, device=flat.model.device)
 
+        # step counter on the device for the pieces reduced during the backward pass (their launches
+        # may sit in a captured graph, so the epoch cannot be a launch argument)
+        self.region_epoch = torch.zeros(1, dtype=torch.int32, device=flat.model.device)
+
     @property
     def shard(self):
         return self.lo, self.lo + self.per
 
-    def reduce_scatter(self):
-        """Kernel 1 on the current stream."""
+    def begin_step(self):
+        """Advances the device-side step counter of the overlapped reduction (a device add, legal
+        inside a captured graph).  Every rank calls it once per step before its first piece."""
+        self.region_epoch.add_(1)
+
+    def reduce_region(self, reg_lo: int, reg_hi: int, seq: int, max_blocks: int = 16):
+        """The piece ``[reg_lo, reg_hi)`` of the flat gradient buffer is final on this rank: tell the
+        group and reduce the part of it this rank owns (current stream)."""
+        _lib.check(_lib.kernels().mrk_dp_reduce_region(
+            self.grad_buf.table, self.symm.ctrl.table, self.n, self.rank, int(reg_lo), int(reg_hi), self.lo,
+            self.lo + self.per, self.flags.data_ptr(), self.region_epoch.data_ptr(), int(seq), int(max_blocks),
+            self.budget_ms, _lib.stream_ptr()), "mrk_dp_reduce_region")
+
+    def reduce_scatter(self, upto: Optional[int] = None):
+        """Kernel 1 on the current stream.  ``upto``: only ``[0, upto)`` of the flat buffer is still
+        unreduced (the rest went through ``reduce_region`` during the backward pass)."""
         self._epoch += 1
+        cnt = self.per if upto is None else max(0, min(self.lo + self.per, int(upto)) - self.lo)
         _lib.check(_lib.kernels().mrk_dp_reduce_scatter(
-            self.grad_buf.table, self.symm.ctrl.table, self.n, self.rank, self.lo, self.per,
+            self.grad_buf.table, self.symm.ctrl.table, self.n, self.rank, self.lo, cnt,
             self.flags.data_ptr(), self._epoch, 1, self.budget_ms, _lib.stream_ptr()), "mrk_dp_reduce_scatter")
 
     def gathered_sumsq(self) -> torch.Tensor:

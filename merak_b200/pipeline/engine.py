@@ -74,6 +74,7 @@ class PipelineEngine:
         model.tie_modules()
         self._configure_precision()
         self._configure_optimizer(optimizer, lr_scheduler, optimizer_factory, lr_scheduler_factory, tuning_params)
+        self._setup_dp_overlap()
 
         if args.train_schedule == "last_no_recompute_1f1b" and self.is_last:
             model._force_no_recompute = True
@@ -223,6 +224,9 @@ class PipelineEngine:
         self.data_iter = data_iter
         self.total_loss = None
         self._grads_reduced = False
+        self._bwd_done = 0
+        if getattr(self, "_ov", None) is not None and not self._graph_capable():
+            self._ov["used"] = False
         if getattr(self.args, "failure_detection_timeout", 0) and dist.is_initialized() and dist.get_world_size() > 1:
             if getattr(self, "_failure_detector", None) is None:
                 from ..utils.failure import FailureDetector
@@ -292,11 +296,19 @@ class PipelineEngine:
                 and self.flat is not None and self.loss_scaler is None and not getattr(self, "_graph_failed", False)
                 and getattr(self, "flat_expert", None) is None and not hasattr(self.module, "_has_moe"))
 
-    def _graph_step_body(self):
+    def _graph_step_body(self, overlap: bool = False):
+        ov = getattr(self, "_ov", None)
+        overlap = overlap and ov is not None and self.micro_batches == 1
+        if overlap:
+            self._dp_overlap_begin()
+            ov["armed"] = True
         out = self.module((), self._g_ext)
         loss = self.loss_fn(out, self._g_labels)
         loss = loss[0] if isinstance(loss, (tuple, list)) else loss
         (loss * (1.0 / self.micro_batches)).backward()
+        if overlap:
+            ov["armed"] = False
+            self._dp_overlap_join()
         self._collect_main_grads()
         return loss.detach()
 
@@ -323,7 +335,7 @@ class PipelineEngine:
         before = _lib.launch_count()
         try:
             with torch.cuda.graph(graph):
-                self._g_loss = self._graph_step_body()
+                self._g_loss = self._graph_step_body(overlap=True)
         except Exception as exc:        # capture is an optimisation: fall back to eager execution
             log_dist("CUDA graph capture failed (%s); running eagerly" % str(exc).splitlines()[0], ranks=[-1])
             self._graph_failed = True
@@ -487,6 +499,12 @@ class PipelineEngine:
     def _exec_backward_pass(self, buf: int):
         if self.wall_clock_breakdown:
             self.timers("backward").start()
+        self._bwd_done = getattr(self, "_bwd_done", 0) + 1
+        ov = getattr(self, "_ov", None)
+        overlap = ov is not None and self._training_pass and self._bwd_done == self.micro_batches
+        if overlap:                 # the last micro-batch: gradients become final as this pass walks back
+            self._dp_overlap_begin()
+            ov["armed"] = True
         if self.is_last:
             loss = self.buf_loss[buf]
             scale = 1.0 / self.micro_batches
@@ -521,6 +539,8 @@ class PipelineEngine:
             self.buf_in_grads[buf] = [t.grad if (isinstance(t, torch.Tensor) and t.grad is not None) else
                                       (torch.zeros_like(t) if t.is_floating_point() else None) for t in ins]
             self.buf_inputs[buf] = None
+        if overlap:
+            ov["armed"] = False
         self._collect_main_grads()
         self.module.pending_records.pop(buf, None)
         if self.wall_clock_breakdown:
@@ -731,7 +751,13 @@ class PipelineEngine:
         group = mpu.get_data_parallel_group()
         if self.flat is not None:
             if getattr(self, "fused_dp", None) is not None:
-                self.fused_dp.reduce_scatter()
+                ov = getattr(self, "_ov", None)
+                if ov is not None and ov["used"]:
+                    self._dp_overlap_join()
+                    self.fused_dp.reduce_scatter(upto=ov["starts"][ov["next"]])
+                    ov["armed"] = False
+                else:
+                    self.fused_dp.reduce_scatter()
                 self._grads_reduced = True
                 return
             g = self.flat.grad
@@ -797,6 +823,80 @@ class PipelineEngine:
             dist.all_gather_into_tensor(tmp[:self.dp_size * b], src, group=group)
             for k in range(self.dp_size):
                 model[k * per + lo:k * per + lo + b].copy_(tmp[k * b:(k + 1) * b])
+
+    # -- data-parallel reduction overlapped with the backward pass -----------------------------------
+    def _setup_dp_overlap(self):
+        """The backward pass finalises the flat gradient buffer from its end (last layer) towards
+        its start.  Each local layer's input is watched (a tensor hook): when its gradient arrives,
+        every later layer's parameter gradients are complete and their piece of the buffer is
+        reduced on a side stream while the backward pass goes on (``csrc/fused_comm.cu``,
+        ``dp_reduce_region_kernel``).  What is left when the backward pass ends goes through the
+        regular reduce-scatter kernel.  The reference reduces everything after the last
+        micro-batch (Merak/core/pipeline/schedule.py:246-250)."""
+        self._ov = None
+        if getattr(self, "fused_dp", None) is None or not getattr(self.args, "overlap_dp_reduce", True):
+            return
+        layers = self.module.local_layers
+        offset_of = {id(p): o for p, o in zip(self.flat.params, self.flat.offsets)}
+        seen, firsts, owned = set(), [], []
+        for layer in layers:
+            mine = [p for p in layer.parameters() if id(p) in offset_of and id(p) not in seen]
+            seen.update(id(p) for p in layer.parameters())
+            firsts.append(min(offset_of[id(p)] for p in mine) if mine else None)
+            owned.append(mine)
+        starts, nxt = [0] * (len(layers) + 1), self.flat.numel
+        starts[len(layers)] = self.flat.numel
+        for i in reversed(range(len(layers))):
+            if firsts[i] is not None:
+                if firsts[i] > nxt:
+                    return                  # parameters are not laid out in layer order: keep the serial path
+                nxt = firsts[i]
+            starts[i] = nxt
+        self._ov = {"starts": starts, "owned": owned, "next": len(layers), "seq": 0, "armed": False, "used": False,
+                    "side": torch.cuda.Stream(device=self.device),
+                    "min_elems": int(getattr(self.args, "dp_overlap_bucket_elems", 8 << 20))}
+        self.module.layer_input_hook = self._watch_layer_input
+
+    def _watch_layer_input(self, layer_idx: int, carried):
+        for t in carried:
+            if isinstance(t, torch.Tensor) and t.requires_grad:
+                t.register_hook(lambda g, i=layer_idx: self._dp_overlap_flush(i + 1))
+                return
+
+    def _dp_overlap_begin(self):
+        ov = self._ov
+        ov["next"], ov["seq"], ov["used"] = len(self.module.local_layers), 0, True
+        self.fused_dp.begin_step()
+
+    def _dp_overlap_flush(self, upto: int, force: bool = False):
+        """Layers ``upto ..`` have all their gradients: reduce the not yet reduced part of them."""
+        ov = self._ov
+        if ov is None or not ov["armed"] or upto >= ov["next"]:
+            return None
+        lo, hi = ov["starts"][upto], ov["starts"][ov["next"]]
+        if hi - lo < ov["min_elems"] and not force:
+            return None                     # too small to be worth a launch: wait for more layers
+        for i in range(upto, ov["next"]):
+            for p in ov["owned"][i]:
+                if p.grad is not None:      # a gradient autograd produced itself joins the flat buffer first
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                    p.grad = None
+        ov["next"] = upto
+        if hi <= lo:
+            return None
+        ov["seq"] += 1
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        ov["side"].wait_event(ev)
+        with torch.cuda.stream(ov["side"]):
+            self.fused_dp.reduce_region(lo, hi, ov["seq"])
+        return None
+
+    def _dp_overlap_join(self):
+        """The side stream's pieces are done before anything later on the current stream."""
+        if self._ov is not None and self._ov["used"]:
+            torch.cuda.current_stream().wait_stream(self._ov["side"])
 
     def _reduce_scatter_inplace(self, g: torch.Tensor, per: int, group):
         out = torch.empty(per, dtype=g.dtype, device=g.device)

@@ -199,8 +199,12 @@ class PipelineModule(nn.Module):
         layers = self.local_layers[lo:hi]
         externals = self._externals
 
+        hook = getattr(self, "layer_input_hook", None)
+
         def run(*carried):
-            for layer in layers:
+            for k, layer in enumerate(layers):
+                if hook is not None and torch.is_grad_enabled():
+                    hook(lo + k, carried)             # the engine watches for this layer's input gradient
                 ext = [externals[n] for n in getattr(layer, "external_inputs", [])]
                 out = layer(*carried, *ext)
                 carried = out if isinstance(out, tuple) else (out,)

@@ -45,6 +45,9 @@ def main():
     ap.add_argument("--dealloc", type=int, default=0)
     ap.add_argument("--comm", default="nccl")
     ap.add_argument("--clip", type=float, default=1.0)
+    ap.add_argument("--cuda_graph", type=int, default=0)
+    ap.add_argument("--dp_overlap", type=int, default=1)
+    ap.add_argument("--dp_bucket", type=int, default=8 << 20)
     ap.add_argument("--inject_overflow", type=int, default=-1, help="step whose gradients get an inf written in")
     ap.add_argument("--user_opt", default="", help="sgd | adamw: a torch.optim optimizer built by the trainer hook")
     ap.add_argument("--out", required=True)
@@ -82,7 +85,8 @@ def main():
         split_method=o.split, bf16=(o.dtype == "bf16"), fp16=(o.dtype == "fp16"), initial_scale_power=8, hysteresis=1,
         loss_scale_window=3, seed=1234, save=bool(o.save_dir), save_steps=o.steps,
         resume_from_checkpoint=o.resume, comm_mode=o.comm, max_grad_norm=o.clip,
-        deallocate_pipeline_outputs=bool(o.dealloc))
+        deallocate_pipeline_outputs=bool(o.dealloc), cuda_graph=bool(o.cuda_graph),
+        overlap_dp_reduce=bool(o.dp_overlap), dp_overlap_bucket_elems=o.dp_bucket)
     # every data-parallel layout must see the same global batch per step: dataset order is by index
     ds = SyntheticTokenDataset(V, L, 16, task=task, seed=7)      # two global batches, revisited
     FixedOrderTrainer.user_opt = o.user_opt

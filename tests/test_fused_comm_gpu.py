@@ -86,6 +86,58 @@ def test_dp_kernels_emulated_ranks(n):
         torch.testing.assert_close(models[k].float(), p_ref.bfloat16().float(), rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("n", [2, 3, 4])
+def test_dp_overlapped_regions_emulated_ranks(n):
+    """The gradient buffer is reduced in pieces from its end towards its start (the order the backward
+    pass finalises it in), then the rest by the regular reduce-scatter kernel, which also posts the
+    norm accumulated by the pieces.  The ranks run one after the other on one GPU, so the readiness
+    flags the pieces wait for are set beforehand."""
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    torch.manual_seed(10 + n)
+    numel = 64 * n * 41
+    per = numel // n
+    grads = [torch.randn(numel, device=dev) * 0.1 for _ in range(n)]
+    total = torch.stack(grads).sum(0)
+    ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(n)]
+
+    def announce_all():
+        # the ranks run one after the other: whoever waits finds every piece already announced (each
+        # kernel overwrites its own rank's entry with the real value first, hence before every launch)
+        for c in ctrls:
+            c.view(torch.int32)[3 * 16: 3 * 16 + 16] = 1 << 30
+    flags = torch.zeros(numel // 64 + 1, dtype=torch.uint8, device=dev)
+    flags[numel // 64 - 2: numel // 64] |= 2                          # not counted in the norm
+    epoch = torch.ones(1, dtype=torch.int32, device=dev)
+    gt, ct = _table([g.data_ptr() for g in grads]), _table([c.data_ptr() for c in ctrls])
+    st = _lib.stream_ptr()
+    # pieces: uneven cuts that straddle shard boundaries, last piece first
+    cuts = sorted({0, numel, 64 * 7, per + 64 * 3, numel - 64 * 9, (numel // 2) // 64 * 64})
+    pieces = list(zip(cuts, cuts[1:]))[::-1]
+    left_upto = pieces[-1][1]                                          # the first piece stays for the tail kernel
+    for seq, (lo, hi) in enumerate(pieces[:-1], start=1):
+        for r in range(n):
+            announce_all()
+            _lib.check(lib.mrk_dp_reduce_region(gt, ct, n, r, lo, hi, r * per, (r + 1) * per, flags.data_ptr(),
+                                                epoch.data_ptr(), seq, 4, 100, st), "region")
+    for r in range(n):
+        cnt = max(0, min((r + 1) * per, left_upto) - r * per)
+        _lib.check(lib.mrk_dp_reduce_scatter(gt, ct, n, r, r * per, cnt, flags.data_ptr(), 1, 0, 100, st), "tail")
+    torch.cuda.synchronize()
+    assert _lib.status() == 0
+    counted = total.clone()
+    counted[(numel // 64 - 2) * 64:] = 0
+    want = counted.double().pow(2).sum().item()
+    for r in range(n):
+        sl = slice(r * per, (r + 1) * per)
+        torch.testing.assert_close(grads[r][sl], total[sl], rtol=1e-5, atol=1e-6)
+        slots = ctrls[r].view(torch.float32)[16 * 16: 16 * 16 + 4 * n].view(n, 4)   # posted (sumsq, bad) per source
+        got = slots[:, 0].double().sum().item()
+        assert abs(got - want) < 1e-4 * want, (got, want)
+        assert slots[:, 1].abs().sum().item() == 0
+
+
 def test_nonfinite_gradient_skips_update():
     from merak_b200.ops import _lib
     lib = _lib.kernels()
@@ -160,6 +212,20 @@ def test_fused_dp_matches_nccl_two_gpus(tmp_path, model):
     assert fused[-1] < fused[0]
     for a, b in zip(fused, ref):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (fused, ref)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("graph,gas", [(0, 2), (1, 1)])
+def test_fused_dp_overlapped_with_backward_two_gpus(tmp_path, graph, gas):
+    """Pieces of the gradient buffer are reduced while the backward pass runs (eagerly on the last
+    micro-batch, or as a side branch of the captured graph): same losses as the serial reduction."""
+    base = ["--model", "gpt2", "--dp", "2", "--steps", "6", "--gas", str(gas), "--comm", "fused",
+            "--cuda_graph", str(graph)]
+    serial = _run(tmp_path, "serial", 2, base + ["--dp_overlap", "0"])
+    overlapped = _run(tmp_path, "overlap", 2, base + ["--dp_overlap", "1", "--dp_bucket", "4096"])
+    assert overlapped[-1] < overlapped[0]
+    for a, b in zip(overlapped, serial):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (overlapped, serial)
 
 
 # ---- tensor-parallel fused GEMMs, ranks emulated on one GPU --------------------------------------
