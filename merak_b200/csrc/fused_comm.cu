@@ -114,92 +114,6 @@ dp_reduce_scatter_kernel(PeerPtrs grads, PeerPtrs ctrls, int n_rt, int rank, lon
   }
 }
 
-// Gradient reduction overlapped with the backward pass.  The backward pass finalises the flat
-// gradient buffer from its end towards its start; whenever a further piece [reg_lo, reg_hi) is final
-// on this rank, this kernel is launched on a side stream.  It (1) tells every rank so, by storing
-// epoch * kRegionSeqStride + seq (a value that only grows during a run) into barrier slot 3 of
-// every peer, and (2) if part of the region lies in this rank's own shard, waits until every rank
-// has published at least the same value and sums that part out of all ranks' buffers, adding its
-// squared norm to the local accumulators that dp_reduce_scatter_kernel (run once after the backward
-// pass for whatever is left) posts to the group.  The epoch is read from device memory, so the
-// launch can be part of a captured graph.  The reference reduces only after the last micro-batch
-// (Merak/core/pipeline/schedule.py:246-250, Merak/core/merak_engine.py:552-621).
-//
-// The kernel runs next to the backward pass's GEMM and attention kernels, which hold one CTA per SM
-// with almost all of its shared memory and most of its registers.  It therefore uses no shared
-// memory of its own and few threads, so that its CTAs fit beside them instead of keeping a
-// persistent GEMM grid from becoming resident.
-constexpr uint32_t kRegionSeqStride = 4096;
-constexpr int kRegionThreads = 128;
-
-// symm_wait without the block-wide vote in shared memory: warp 0 polls, the result travels through
-// a barrier that carries a predicate (no shared memory).
-__device__ __forceinline__ bool symm_wait_nosmem(SymmCtrl* mine, int n, int which, uint32_t target, long long budget,
-                                                 unsigned* status) {
-  int ok = 1;
-  if ((int)threadIdx.x < n) {
-    const uint32_t* f = &mine->flags[which][threadIdx.x];
-    const long long t0 = clock64();
-    while ((int32_t)(ld_acquire_sys_u32(f) - target) < 0) {
-      if (clock64() - t0 > budget) {
-        raise_status(status, kStatusFlagTimeout);
-        ok = 0;
-        break;
-      }
-      __nanosleep(200);
-    }
-  }
-  return __syncthreads_and(ok) != 0;
-}
-
-template <int N>
-__global__ void __launch_bounds__(kRegionThreads)
-dp_reduce_region_kernel(PeerPtrs grads, PeerPtrs ctrls, int n_rt, int rank, long long reg_lo, long long reg_hi,
-                        long long own_lo, long long own_hi, const unsigned char* __restrict__ flags,
-                        const uint32_t* __restrict__ epoch_ptr, uint32_t seq, long long budget, unsigned* status) {
-  const int n = N > 0 ? N : n_rt;
-  SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(ctrls.p[rank]);
-  const uint32_t target = (*epoch_ptr) * kRegionSeqStride + seq;
-  if (blockIdx.x == 0) symm_signal(ctrls, n, rank, 3, target);
-  const long long lo = reg_lo > own_lo ? reg_lo : own_lo;
-  const long long hi = reg_hi < own_hi ? reg_hi : own_hi;
-  if (lo >= hi) return;                                   // nothing of this region is mine
-  const bool ok = symm_wait_nosmem(mine, n, 3, target, budget, status);
-  float acc = 0.f, bad = 0.f;
-  if (ok) {
-    float* dst = reinterpret_cast<float*>(grads.p[rank]) + lo;
-    const long long nvec = (hi - lo) >> 2;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
-         i += (long long)gridDim.x * blockDim.x) {
-      float4 s = ld_relaxed_sys_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[0]) + lo) + i);
-#pragma unroll
-      for (int k = 1; k < (N > 0 ? N : kSymmMaxRanks); ++k) {
-        if (k < n) {
-          const float4 t = ld_relaxed_sys_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[k]) + lo) + i);
-          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-        }
-      }
-      reinterpret_cast<float4*>(dst)[i] = s;
-      const unsigned f = flags ? flags[(lo + (i << 2)) >> 6] : 0u;
-      if (!(f & kFlagNoNorm)) {
-        acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
-        bad += (isfinite(s.x) ? 0.f : 1.f) + (isfinite(s.y) ? 0.f : 1.f) + (isfinite(s.z) ? 0.f : 1.f) +
-               (isfinite(s.w) ? 0.f : 1.f);
-      }
-    }
-  }
-  if (!ok) bad += 1.f;                                    // a timed-out piece poisons the step
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    bad += __shfl_xor_sync(0xffffffffu, bad, o);
-  }
-  if ((threadIdx.x & 31) == 0) {
-    atomicAdd(&mine->local_acc[0], acc);
-    if (bad != 0.f) atomicAdd(&mine->local_acc[1], bad);
-  }
-}
-
 template <int N>
 __global__ void __launch_bounds__(kDpThreads)
 dp_adamw_allgather_kernel(PeerPtrs models, PeerPtrs ctrls, int n_rt, int rank, long long lo, long long cnt,
@@ -399,36 +313,13 @@ MRK_API int mrk_dp_reduce_scatter(void* const* grad_ptrs, void* const* ctrl_ptrs
   return 0;
 }
 
-MRK_API int mrk_dp_reduce_region(void* const* grad_ptrs, void* const* ctrl_ptrs, int n, int rank, long long reg_lo,
-                                 long long reg_hi, long long own_lo, long long own_hi, const unsigned char* flags,
-                                 const unsigned* epoch_ptr, unsigned seq, int max_blocks, int budget_ms, void* stream) {
-  MRK_REQUIRE(n >= 1 && n <= kSymmMaxRanks && rank >= 0 && rank < n, "dp_reduce_region: bad group (%d ranks)", n);
-  MRK_REQUIRE(reg_lo >= 0 && reg_hi > reg_lo && (reg_lo % 8) == 0 && (reg_hi % 8) == 0 && (own_lo % 8) == 0 &&
-              (own_hi % 8) == 0, "dp_reduce_region: ranges must be multiples of 8 elements");
-  MRK_REQUIRE(epoch_ptr != nullptr && seq >= 1 && seq < kRegionSeqStride, "dp_reduce_region: bad epoch / sequence");
-  PeerPtrs g, c;
-  fill_peers(&g, grad_ptrs, n);
-  fill_peers(&c, ctrl_ptrs, n);
-  unsigned* status = status_word_device();
-  MRK_REQUIRE(status != nullptr, "dp_reduce_region: status word unavailable");
-  const long long lo = reg_lo > own_lo ? reg_lo : own_lo, hi = reg_hi < own_hi ? reg_hi : own_hi;
-  long long blocks = hi > lo ? ((hi - lo) / 4 + kRegionThreads * 8 - 1) / (kRegionThreads * 8) : 1;
-  if (max_blocks < 1) max_blocks = 16;         // a few SMs' worth: the backward pass keeps the rest
-  if (blocks > max_blocks) blocks = max_blocks;
-  if (blocks < 1) blocks = 1;
-  const long long b = budget_cycles(budget_ms);
-  cudaStream_t s = (cudaStream_t)stream;
-#define MRK_RR(NN) dp_reduce_region_kernel<NN><<<(unsigned)blocks, kRegionThreads, 0, s>>>( \
-    g, c, n, rank, reg_lo, reg_hi, own_lo, own_hi, flags, epoch_ptr, seq, b, status)
-  switch (n) {
-    case 1: MRK_RR(1); break;
-    case 2: MRK_RR(2); break;
-    case 4: MRK_RR(4); break;
-    case 8: MRK_RR(8); break;
-    default: MRK_RR(0); break;
-  }
-#undef MRK_RR
-  MRK_CHECK_LAUNCH();
+// One device-to-device copy on `stream` (a copy-engine transfer; `dst` may be peer-mapped memory).
+// The overlapped data-parallel reduction pushes finished pieces of the gradient buffer to their
+// owner's staging buffer with it while the backward pass keeps every SM: the copy engines move the
+// bytes over NVLink, no thread block is spent and none can get in the way of a persistent GEMM grid.
+MRK_API int mrk_memcpy_d2d_async(void* dst, const void* src, unsigned long long bytes, void* stream) {
+  MRK_REQUIRE(dst != nullptr && src != nullptr && bytes > 0, "memcpy_d2d_async: bad arguments");
+  MRK_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
   return 0;
 }
 

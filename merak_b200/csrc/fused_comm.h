@@ -14,11 +14,8 @@ int mrk_ipc_open(const unsigned char* handle, void** out);
 int mrk_ipc_close(void* p);
 int mrk_dp_reduce_scatter(void* const* grad_ptrs, void* const* ctrl_ptrs, int n, int rank, long long lo, long long cnt,
                           const unsigned char* flags, unsigned epoch, int sync, int budget_ms, void* stream);
-// Reduction of one piece of the gradient buffer while the backward pass is still running; `epoch_ptr`
-// is a device word (the step counter), `seq` numbers the pieces of one step from 1.
-int mrk_dp_reduce_region(void* const* grad_ptrs, void* const* ctrl_ptrs, int n, int rank, long long reg_lo,
-                         long long reg_hi, long long own_lo, long long own_hi, const unsigned char* flags,
-                         const unsigned* epoch_ptr, unsigned seq, int max_blocks, int budget_ms, void* stream);
+// One device-to-device copy on `stream` (copy engine; either side may be peer-mapped memory).
+int mrk_memcpy_d2d_async(void* dst, const void* src, unsigned long long bytes, void* stream);
 int mrk_dp_adamw_allgather(void* const* model_ptrs, void* const* ctrl_ptrs, int n, int rank, long long lo,
                            long long cnt, const float* grad_shard, float* master, float* m, float* v,
                            const unsigned char* flags, const float* hp, float grad_scale, float max_norm,

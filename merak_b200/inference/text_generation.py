@@ -58,8 +58,10 @@ class text_generation_pipeline:
         self.device = self.engine.device
 
     def _last_rank(self) -> int:
-        grid = mpu.get_grid()
-        return grid.stage_to_global(grid.pipe_parallel_size - 1) if grid is not None else 0
+        """The rank every other rank takes the new token from: the last global rank, which sits on
+        the last pipeline stage (the pipeline axis is the outermost one), as in the reference
+        (Merak/inference/text_generation_inference.py:238-270).  Every rank must name the same one."""
+        return dist.get_world_size() - 1 if dist.is_initialized() else 0
 
     @torch.no_grad()
     def generate(self, prompts, max_new_tokens: Optional[int] = None, greedy: bool = False, seed: Optional[int] = None):

@@ -87,7 +87,7 @@ def _declare(lib):
     sig("mrk_dp_reduce_scatter", c_int, P, P, c_int, c_int, c_ll, c_ll, P, c_uint, c_int, c_int, P)
     sig("mrk_dp_adamw_allgather", c_int, P, P, c_int, c_int, c_ll, c_ll, P, P, P, P, P, P, c_float, c_float,
         P, P, P, c_uint, c_int, c_int, c_int, P)
-    sig("mrk_dp_reduce_region", c_int, P, P, c_int, c_int, c_ll, c_ll, c_ll, c_ll, P, P, c_uint, c_int, c_int, P)
+    sig("mrk_memcpy_d2d_async", c_int, P, P, ctypes.c_ulonglong, P)
     sig("mrk_dp_norm_gather", c_int, P, c_int, c_int, P, c_uint, c_int, c_int, P)
     sig("mrk_tp_reduce_pull", c_int, P, P, c_int, c_int, P, c_ll, c_int, c_int, P, c_uint, c_int, c_int, P)
     sig("mrk_tp_gather_rows", c_int, P, P, c_int, c_int, P, c_ll, c_int, c_int, c_uint, c_int, c_int, P)

@@ -4,7 +4,9 @@ The flat bf16 model buffer and the flat fp32 gradient buffer of every data-paral
 peer-mapped memory.  One step is two kernels (``csrc/fused_comm.cu``):
 
 1. reduce-scatter: each rank sums its shard of the gradient out of all ranks' buffers and posts the
-   shard's squared norm to everyone;
+   shard's squared norm to everyone.  With the reduction overlapped with the backward pass, the
+   pieces of the gradient buffer travel to their owner's staging buffer on the copy engines as soon
+   as the backward pass has finished them, and this kernel sums local memory only;
 2. clip + AdamW on the shard (optimizer state sharded as in ZeRO-1) + all-gather: the owner stores
    the new bf16 parameters into every rank's model buffer.
 
@@ -76,34 +78,48 @@ class FusedDataParallel:
         self.lo = self.rank * self.per
         self._norm_tmp = torch.zeros(2, dtype=torch.float32, device=flat.model.device)
 
-        # step counter on the device for the pieces reduced during the backward pass (their launches
-        # may sit in a captured graph, so the epoch cannot be a launch argument)
-        self.region_epoch = torch.zeros(1, dtype=torch.int32, device=flat.model.device)
+        self.stage_buf = None
+        self._staged_table = None
 
     @property
     def shard(self):
         return self.lo, self.lo + self.per
 
-    def begin_step(self):
-        """Advances the device-side step counter of the overlapped reduction (a device add, legal
-        inside a captured graph).  Every rank calls it once per step before its first piece."""
-        self.region_epoch.add_(1)
+    # -- reduction overlapped with the backward pass ------------------------------------------------
+    def enable_staging(self):
+        """Collective over the group: a staging buffer of ``n`` slots of one shard each.  Slot ``s`` of
+        rank ``r`` receives rank ``s``'s contribution to ``r``'s shard of the gradient."""
+        if self.stage_buf is None:
+            self.stage_buf = self.symm.alloc(self.n * self.per * 4, torch.float32)
+            # pointer table for the summing kernel, which reads ``table[k] + lo + i``: its own gradient
+            # buffer for k == rank, staging slot k (local memory) for the others
+            own = self.grad_buf.ptrs[self.rank]
+            base = self.stage_buf.local_ptr
+            self._staged_table = (ctypes.c_void_p * self.n)(*[
+                own if k == self.rank else base + 4 * (k * self.per - self.lo) for k in range(self.n)])
 
-    def reduce_region(self, reg_lo: int, reg_hi: int, seq: int, max_blocks: int = 16):
-        """The piece ``[reg_lo, reg_hi)`` of the flat gradient buffer is final on this rank: tell the
-        group and reduce the part of it this rank owns (current stream)."""
-        _lib.check(_lib.kernels().mrk_dp_reduce_region(
-            self.grad_buf.table, self.symm.ctrl.table, self.n, self.rank, int(reg_lo), int(reg_hi), self.lo,
-            self.lo + self.per, self.flags.data_ptr(), self.region_epoch.data_ptr(), int(seq), int(max_blocks),
-            self.budget_ms, _lib.stream_ptr()), "mrk_dp_reduce_region")
+    def push_region(self, reg_lo: int, reg_hi: int):
+        """The piece ``[reg_lo, reg_hi)`` of the flat gradient buffer is final on this rank: copy the
+        parts other ranks own into their staging buffers (copy engines over NVLink, current
+        stream; no thread block is involved, so the backward pass keeps every SM)."""
+        lib = _lib.kernels()
+        st = _lib.stream_ptr()
+        src = self.grad_buf.ptrs[self.rank]
+        for r in range(self.n):
+            a, b = max(int(reg_lo), r * self.per), min(int(reg_hi), (r + 1) * self.per)
+            if r == self.rank or a >= b:
+                continue
+            dst = self.stage_buf.ptrs[r] + 4 * (self.rank * self.per + a - r * self.per)
+            _lib.check(lib.mrk_memcpy_d2d_async(dst, src + 4 * a, 4 * (b - a), st), "mrk_memcpy_d2d_async")
 
-    def reduce_scatter(self, upto: Optional[int] = None):
-        """Kernel 1 on the current stream.  ``upto``: only ``[0, upto)`` of the flat buffer is still
-        unreduced (the rest went through ``reduce_region`` during the backward pass)."""
+    def reduce_scatter(self, staged: bool = False):
+        """Kernel 1 on the current stream.  ``staged``: every rank has pushed its contributions into
+        the staging buffers (``push_region``), so the sum reads local memory only; the kernel's
+        barrier then means "every rank's pushes have landed"."""
         self._epoch += 1
-        cnt = self.per if upto is None else max(0, min(self.lo + self.per, int(upto)) - self.lo)
+        table = self._staged_table if staged else self.grad_buf.table
         _lib.check(_lib.kernels().mrk_dp_reduce_scatter(
-            self.grad_buf.table, self.symm.ctrl.table, self.n, self.rank, self.lo, cnt,
+            table, self.symm.ctrl.table, self.n, self.rank, self.lo, self.per,
             self.flags.data_ptr(), self._epoch, 1, self.budget_ms, _lib.stream_ptr()), "mrk_dp_reduce_scatter")
 
     def gathered_sumsq(self) -> torch.Tensor:

@@ -753,8 +753,11 @@ class PipelineEngine:
             if getattr(self, "fused_dp", None) is not None:
                 ov = getattr(self, "_ov", None)
                 if ov is not None and ov["used"]:
+                    # what the backward pass did not send itself (the first layers) goes now
                     self._dp_overlap_join()
-                    self.fused_dp.reduce_scatter(upto=ov["starts"][ov["next"]])
+                    if ov["starts"][ov["next"]] > 0:
+                        self.fused_dp.push_region(0, ov["starts"][ov["next"]])
+                    self.fused_dp.reduce_scatter(staged=True)
                     ov["armed"] = False
                 else:
                     self.fused_dp.reduce_scatter()
@@ -829,9 +832,9 @@ class PipelineEngine:
         """The backward pass finalises the flat gradient buffer from its end (last layer) towards
         its start.  Each local layer's input is watched (a tensor hook): when its gradient arrives,
         every later layer's parameter gradients are complete and their piece of the buffer is
-        reduced on a side stream while the backward pass goes on (``csrc/fused_comm.cu``,
-        ``dp_reduce_region_kernel``).  What is left when the backward pass ends goes through the
-        regular reduce-scatter kernel.  The reference reduces everything after the last
+        copied, on a side stream, into the staging buffers of the ranks that own it (copy engines
+        over NVLink: no SM is taken from the backward pass).  After the backward pass the rest is
+        sent and the reduce-scatter kernel sums local memory only.  The reference reduces everything after the last
         micro-batch (Merak/core/pipeline/schedule.py:246-250)."""
         self._ov = None
         if getattr(self, "fused_dp", None) is None or not getattr(self.args, "overlap_dp_reduce", True):
@@ -852,7 +855,8 @@ class PipelineEngine:
                     return                  # parameters are not laid out in layer order: keep the serial path
                 nxt = firsts[i]
             starts[i] = nxt
-        self._ov = {"starts": starts, "owned": owned, "next": len(layers), "seq": 0, "armed": False, "used": False,
+        self.fused_dp.enable_staging()
+        self._ov = {"starts": starts, "owned": owned, "next": len(layers), "armed": False, "used": False,
                     "side": torch.cuda.Stream(device=self.device),
                     "min_elems": int(getattr(self.args, "dp_overlap_bucket_elems", 8 << 20))}
         self.module.layer_input_hook = self._watch_layer_input
@@ -865,17 +869,16 @@ class PipelineEngine:
 
     def _dp_overlap_begin(self):
         ov = self._ov
-        ov["next"], ov["seq"], ov["used"] = len(self.module.local_layers), 0, True
-        self.fused_dp.begin_step()
+        ov["next"], ov["used"] = len(self.module.local_layers), True
 
     def _dp_overlap_flush(self, upto: int, force: bool = False):
-        """Layers ``upto ..`` have all their gradients: reduce the not yet reduced part of them."""
+        """Layers ``upto ..`` have all their gradients: send the not yet sent part of them."""
         ov = self._ov
         if ov is None or not ov["armed"] or upto >= ov["next"]:
             return None
         lo, hi = ov["starts"][upto], ov["starts"][ov["next"]]
         if hi - lo < ov["min_elems"] and not force:
-            return None                     # too small to be worth a launch: wait for more layers
+            return None                     # too small to be worth its copies: wait for more layers
         for i in range(upto, ov["next"]):
             for p in ov["owned"][i]:
                 if p.grad is not None:      # a gradient autograd produced itself joins the flat buffer first
@@ -884,13 +887,12 @@ class PipelineEngine:
         ov["next"] = upto
         if hi <= lo:
             return None
-        ov["seq"] += 1
         main = torch.cuda.current_stream()
         ev = torch.cuda.Event()
         ev.record(main)
         ov["side"].wait_event(ev)
         with torch.cuda.stream(ov["side"]):
-            self.fused_dp.reduce_region(lo, hi, ov["seq"])
+            self.fused_dp.push_region(lo, hi)
         return None
 
     def _dp_overlap_join(self):

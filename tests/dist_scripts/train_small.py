@@ -45,6 +45,11 @@ def main():
     ap.add_argument("--dealloc", type=int, default=0)
     ap.add_argument("--comm", default="nccl")
     ap.add_argument("--clip", type=float, default=1.0)
+    ap.add_argument("--vocab", type=int, default=512)
+    ap.add_argument("--seq", type=int, default=32)
+    ap.add_argument("--lr", type=float, default=0.0)
+    ap.add_argument("--data_seed", type=int, default=7)
+    ap.add_argument("--data_size", type=int, default=16)
     ap.add_argument("--cuda_graph", type=int, default=0)
     ap.add_argument("--dp_overlap", type=int, default=1)
     ap.add_argument("--dp_bucket", type=int, default=8 << 20)
@@ -55,7 +60,7 @@ def main():
 
     Merak.init(o.pp, o.tp, o.dp, sp=o.sp, ep=o.ep, backend="gloo" if o.device == "cpu" else "nccl")
     torch.manual_seed(1234)
-    V, L = 512, 32
+    V, L = o.vocab, o.seq
     import contextlib
     build_ctx = Merak.init_empty_weights() if o.meta else contextlib.nullcontext()
     build_ctx.__enter__()
@@ -77,7 +82,7 @@ def main():
     build_ctx.__exit__(None, None, None)
     args = Merak.MerakArguments(
         output_dir=o.save_dir or "/tmp/merak_b200_test", per_device_train_batch_size=o.mbs,
-        gradient_accumulation_steps=o.gas, max_steps=o.steps, logging_steps=0, learning_rate=1e-3 if o.model == "gpt2" else 3e-3,
+        gradient_accumulation_steps=o.gas, max_steps=o.steps, logging_steps=0, learning_rate=o.lr or (1e-3 if o.model == "gpt2" else 3e-3),
         lr_scheduler_type="constant", weight_decay=0.01, wall_clock_breakdown=False, report_to="none",
         no_cuda=(o.device == "cpu"), train_schedule=o.schedule, activation_checkpointing=bool(o.recompute),
         activation_checkpoint_ratio=[o.ratio] if o.ratio else None, zero_stage=1 if o.zero else None,
@@ -88,7 +93,7 @@ def main():
         deallocate_pipeline_outputs=bool(o.dealloc), cuda_graph=bool(o.cuda_graph),
         overlap_dp_reduce=bool(o.dp_overlap), dp_overlap_bucket_elems=o.dp_bucket)
     # every data-parallel layout must see the same global batch per step: dataset order is by index
-    ds = SyntheticTokenDataset(V, L, 16, task=task, seed=7)      # two global batches, revisited
+    ds = SyntheticTokenDataset(V, L, o.data_size, task=task, seed=o.data_seed)   # default: two global batches, revisited
     FixedOrderTrainer.user_opt = o.user_opt
     trainer = FixedOrderTrainer(model, args, train_dataset=ds)
     losses = []

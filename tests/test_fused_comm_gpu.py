@@ -87,11 +87,10 @@ def test_dp_kernels_emulated_ranks(n):
 
 
 @pytest.mark.parametrize("n", [2, 3, 4])
-def test_dp_overlapped_regions_emulated_ranks(n):
-    """The gradient buffer is reduced in pieces from its end towards its start (the order the backward
-    pass finalises it in), then the rest by the regular reduce-scatter kernel, which also posts the
-    norm accumulated by the pieces.  The ranks run one after the other on one GPU, so the readiness
-    flags the pieces wait for are set beforehand."""
+def test_dp_staged_reduce_emulated_ranks(n):
+    """Overlapped reduction: every rank copies the pieces of its gradient buffer that other ranks own
+    into the owners' staging slots (device-to-device copies, piece after piece from the end of the
+    buffer), then the reduce-scatter kernel sums its own buffer and its staging slots."""
     from merak_b200.ops import _lib
     lib = _lib.kernels()
     dev = torch.device("cuda")
@@ -100,30 +99,24 @@ def test_dp_overlapped_regions_emulated_ranks(n):
     per = numel // n
     grads = [torch.randn(numel, device=dev) * 0.1 for _ in range(n)]
     total = torch.stack(grads).sum(0)
+    stages = [torch.zeros(n * per, device=dev) for _ in range(n)]
     ctrls = [torch.zeros(lib.mrk_symm_ctrl_bytes(), dtype=torch.uint8, device=dev) for _ in range(n)]
-
-    def announce_all():
-        # the ranks run one after the other: whoever waits finds every piece already announced (each
-        # kernel overwrites its own rank's entry with the real value first, hence before every launch)
-        for c in ctrls:
-            c.view(torch.int32)[3 * 16: 3 * 16 + 16] = 1 << 30
     flags = torch.zeros(numel // 64 + 1, dtype=torch.uint8, device=dev)
     flags[numel // 64 - 2: numel // 64] |= 2                          # not counted in the norm
-    epoch = torch.ones(1, dtype=torch.int32, device=dev)
-    gt, ct = _table([g.data_ptr() for g in grads]), _table([c.data_ptr() for c in ctrls])
+    ct = _table([c.data_ptr() for c in ctrls])
     st = _lib.stream_ptr()
-    # pieces: uneven cuts that straddle shard boundaries, last piece first
     cuts = sorted({0, numel, 64 * 7, per + 64 * 3, numel - 64 * 9, (numel // 2) // 64 * 64})
-    pieces = list(zip(cuts, cuts[1:]))[::-1]
-    left_upto = pieces[-1][1]                                          # the first piece stays for the tail kernel
-    for seq, (lo, hi) in enumerate(pieces[:-1], start=1):
-        for r in range(n):
-            announce_all()
-            _lib.check(lib.mrk_dp_reduce_region(gt, ct, n, r, lo, hi, r * per, (r + 1) * per, flags.data_ptr(),
-                                                epoch.data_ptr(), seq, 4, 100, st), "region")
+    for lo, hi in list(zip(cuts, cuts[1:]))[::-1]:
+        for src in range(n):
+            for own in range(n):
+                a, b = max(lo, own * per), min(hi, (own + 1) * per)
+                if own != src and a < b:
+                    dst = stages[own].data_ptr() + 4 * (src * per + a - own * per)
+                    _lib.check(lib.mrk_memcpy_d2d_async(dst, grads[src].data_ptr() + 4 * a, 4 * (b - a), st), "copy")
     for r in range(n):
-        cnt = max(0, min((r + 1) * per, left_upto) - r * per)
-        _lib.check(lib.mrk_dp_reduce_scatter(gt, ct, n, r, r * per, cnt, flags.data_ptr(), 1, 0, 100, st), "tail")
+        table = _table([grads[r].data_ptr() if k == r else stages[r].data_ptr() + 4 * (k * per - r * per)
+                        for k in range(n)])
+        _lib.check(lib.mrk_dp_reduce_scatter(table, ct, n, r, r * per, per, flags.data_ptr(), 1, 0, 100, st), "sum")
     torch.cuda.synchronize()
     assert _lib.status() == 0
     counted = total.clone()
@@ -217,8 +210,9 @@ def test_fused_dp_matches_nccl_two_gpus(tmp_path, model):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("graph,gas", [(0, 2), (1, 1)])
 def test_fused_dp_overlapped_with_backward_two_gpus(tmp_path, graph, gas):
-    """Pieces of the gradient buffer are reduced while the backward pass runs (eagerly on the last
-    micro-batch, or as a side branch of the captured graph): same losses as the serial reduction."""
+    """Pieces of the gradient buffer travel to their owners while the backward pass runs (eagerly on
+    the last micro-batch, or as a side branch of the captured graph): same losses as the serial
+    reduction."""
     base = ["--model", "gpt2", "--dp", "2", "--steps", "6", "--gas", str(gas), "--comm", "fused",
             "--cuda_graph", str(graph)]
     serial = _run(tmp_path, "serial", 2, base + ["--dp_overlap", "0"])
