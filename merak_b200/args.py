@@ -137,6 +137,8 @@ class MerakArguments:
 
     # ---- B200 runtime ---------------------------------------------------------------------------
     cuda_graph: bool = field(default=False, metadata={"help": "Capture each stage's micro-batch step in a CUDA graph."})
+    nvtx_ranges: bool = field(default=False, metadata={
+        "help": "emit an NVTX range per pipeline instruction and per train_batch (also MERAK_NVTX=1)"})
     overlap_dp_reduce: bool = field(default=True, metadata={"help": "Reduce DP gradients during the last backward."})
     dp_overlap_bucket_elems: int = field(default=8 << 20, metadata={
         "help": "smallest piece of the gradient buffer (elements) worth its own overlapped reduction launch"})

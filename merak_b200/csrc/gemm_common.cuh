@@ -13,8 +13,15 @@ namespace mrk {
 //           segment and publish a counter per segment; the TMA producers of the compute CTAs wait
 //           for the segments their tile covers, starting with this rank's own rows.  Each remote
 //           element crosses NVLink once.
-//   (mode 1 is reserved: GEMM -> reduce-scatter runs as a plain GEMM into a peer-mapped partial
-//   buffer followed by the pull-and-sum kernel in fused_comm.cu.)
+//   mode 1  GEMM -> reduce-scatter (CTA-pair kernel): every rank multiplies its slice of the
+//           contraction and writes the bf16 partial product of each 128 x 128 sub-tile into its own
+//           peer-mapped buffer, then stores the call's epoch into the flag of that sub-tile in the
+//           control memory of the rank that owns those rows.  Row blocks are visited with this
+//           rank's own segments last, so what the peers need first is produced first.  When a CTA
+//           has finished its tiles, its epilogue warps turn to the sub-tiles this rank owns: they
+//           wait for the n flags of a sub-tile, pull the n partials (peer loads over NVLink), sum
+//           them in fp32, add the bias and write the reduced rows.  One launch, no barrier over the
+//           group: a sub-tile is reduced as soon as its last contribution exists.
 // Rows of the full [M, *] matrix are grouped in segments of `seg_rows`; segment s belongs to rank
 // s % n and is that rank's local segment s / n (batch-first sequence sharding).
 constexpr int kGemmMaxPeers = 8;
@@ -33,6 +40,13 @@ struct GemmComm {
   uint32_t flag_target;        // mode 2: gather CTAs of all calls so far; a segment is complete when its
                                // counter reaches flag_target * kGatherWorkers
   long long budget;            // wait budget in SM cycles
+  // mode 1
+  uint32_t* tile_flags[kGemmMaxPeers];   // per rank: [n sources][units_total] epochs, peer-mapped
+  int units_total;             // sub-tiles of the full output: num_m_blocks * num_n_blocks * 4
+  int own_last;                // row-block order ends (instead of starts) with this rank's own segments
+  int phase;                   // 3 = multiply and reduce; 1 = multiply only; 2 = reduce only (tests on one GPU)
+  void* rs_out;                // [M / n, N] bf16, this rank's reduced rows
+  const void* rs_bias;         // optional bf16 [N]
 };
 
 struct GemmParams {
@@ -66,7 +80,7 @@ __device__ __forceinline__ int comm_perm_m(const GemmParams& p, int i, int block
   const int per_owner = p.num_m_blocks / c.n;
   const int d = i / per_owner, j = i - d * per_owner;
   const int b = j / blocks_per_seg, w = j - b * blocks_per_seg;
-  int owner = c.rank + d;
+  int owner = c.rank + d + (c.own_last ? 1 : 0);
   if (owner >= c.n) owner -= c.n;
   return (b * c.n + owner) * blocks_per_seg + w;
 }

@@ -375,3 +375,34 @@ MRK_API int mrk_gemm_bf16_ag(void* gathered, void* const* peer_shards, const voi
   return gemm_entry(gathered, B, C, M, N, K, K, ldb, ldc, bias, nullptr, 0, aux_out, ld_aux_out, act, MRK_AUX_NONE,
                     flags, alpha, 0, &c, stream);
 }
+
+// GEMM -> reduce-scatter in one launch (see gemm_common.cuh, mode 1).  `parts[k]` is rank k's
+// [M, N] bf16 partial-product buffer (peer-mapped; entry `rank` is written here), `tile_flags[k]`
+// rank k's flag array of n * units uint32 (peer-mapped, zero before first use, shared by all calls
+// with growing `epoch`), `out` [M / n, N] bf16 receives this rank's rows of the sum (+ bias).
+// Requirements: M a multiple of 256 * ... see the checks; the caller falls back to the two-kernel
+// path (plain GEMM + pull-and-sum) otherwise.  phase: 3 normally; 1 / 2 split the multiplication
+// and the reduction into two launches for single-GPU tests.
+MRK_API int mrk_gemm_bf16_rs_units(int M, int N) {
+  return ((M + 255) / 256) * ((N + 255) / 256) * 4;
+}
+
+MRK_API int mrk_gemm_bf16_rs(const void* A, const void* B, void* const* parts, void* const* tile_flags, void* out,
+                             const void* bias, int M, int N, int K, long long lda, long long ldb, int flags, int n,
+                             int rank, int seg_rows, unsigned epoch, int phase, int budget_ms, void* stream) {
+  MRK_REQUIRE(M % 128 == 0 && seg_rows % 128 == 0 && N % 64 == 0 && M > 128 && N > 128,
+              "gemm_rs: shape %dx%d (segments of %d rows) is not tileable into 128-row sub-tiles", M, N, seg_rows);
+  MRK_REQUIRE(!(flags & (MRK_GEMM_OUT_F32 | MRK_GEMM_ACCUMULATE)), "gemm_rs: bf16 partial products only");
+  MRK_REQUIRE(phase >= 1 && phase <= 3 && out != nullptr, "gemm_rs: bad arguments");
+  GemmComm c;
+  int rc = fill_comm(&c, 1, n, rank, seg_rows, parts, N, nullptr, epoch, budget_ms, M);
+  if (rc) return rc;
+  for (int k = 0; k < n; ++k) c.tile_flags[k] = reinterpret_cast<uint32_t*>(tile_flags[k]);
+  c.units_total = mrk_gemm_bf16_rs_units(M, N);
+  c.own_last = 1;
+  c.phase = phase;
+  c.rs_out = out;
+  c.rs_bias = bias;
+  return gemm_entry(A, B, parts[rank], M, N, K, lda, ldb, N, nullptr, nullptr, 0, nullptr, 0, MRK_ACT_NONE,
+                    MRK_AUX_NONE, flags, 1.0f, 512, &c, stream);
+}

@@ -33,6 +33,11 @@ int mrk_gemm_bf16_ag(void* gathered, void* const* peer_shards, const void* B, vo
                      long long ldb, long long ldc, const void* bias, void* aux_out, long long ld_aux_out, int act,
                      int flags, float alpha, void* const* ctrls, unsigned* seg_flags, unsigned flag_target,
                      int gather_ctas, int n, int rank, int seg_rows, unsigned epoch, int budget_ms, void* stream);
+// GEMM -> reduce-scatter in one launch over peer-mapped partial-product buffers (gemm_common.cuh, mode 1).
+int mrk_gemm_bf16_rs_units(int M, int N);
+int mrk_gemm_bf16_rs(const void* A, const void* B, void* const* parts, void* const* tile_flags, void* out,
+                     const void* bias, int M, int N, int K, long long lda, long long ldb, int flags, int n, int rank,
+                     int seg_rows, unsigned epoch, int phase, int budget_ms, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,80 @@ constexpr int kPairStageBytes = kPairABytes + kPairBBytes;    // 32 KB
 constexpr int kPairStagingBytes = 2 * 32768;   // epilogue staging: two 128 x 128 bf16 blocks (TMA-store source)
 constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes + 1024 + 1024;
 
+// mode 1, store thread: the partial product of sub-tile `u` is complete in this rank's buffer.
+__device__ __forceinline__ void rs_publish(const GemmParams& p, int owner, int u) {
+  const GemmComm& c = p.comm;
+  __threadfence_system();
+  st_release_sys_u32(c.tile_flags[owner] + (size_t)c.rank * c.units_total + u, c.epoch);
+}
+
+// mode 1, the 256 epilogue threads of every CTA: sum the partial products of the 128 x 128 sub-tiles
+// whose rows this rank owns, as their flags arrive.  Bounded waits; on a timeout the CTA stops reducing.
+__device__ __noinline__ void rs_reduce_owned(const GemmParams& p, int cta_lin, int num_ctas, volatile int* abort_flag,
+                                             bool ok_in) {
+  const GemmComm& c = p.comm;
+  const int n = c.n;
+  const int tid = (int)threadIdx.x - 64;                   // 0..255
+  const int sub_per_row = (p.N + 127) / 128;
+  const int local_blocks = (p.M / n) / 128;
+  const int owned = local_blocks * sub_per_row;
+  const uint32_t* my_flags = c.tile_flags[c.rank];
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c.rs_out);
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(c.rs_bias);
+  if (!ok_in && tid == 0) *abort_flag = 1;
+  for (int q = cta_lin; q < owned; q += num_ctas) {
+    const int lb = q / sub_per_row, sn = q - lb * sub_per_row;
+    const long long lrow0 = (long long)lb * 128;
+    const long long b = lrow0 / c.seg_rows;
+    const long long grow0 = (b * n + c.rank) * c.seg_rows + (lrow0 - b * c.seg_rows);
+    const int m_blk = (int)(grow0 / kPairBlockM), cta_p = (int)((grow0 % kPairBlockM) / 128);
+    const int u = ((m_blk * p.num_n_blocks + (sn >> 1)) * 2 + cta_p) * 2 + (sn & 1);
+    if (tid < n) {
+      const uint32_t* f = my_flags + (size_t)tid * c.units_total + u;
+      const long long t0 = clock64();
+      while ((int32_t)(ld_acquire_sys_u32(f) - c.epoch) < 0) {
+        if (*abort_flag || clock64() - t0 > c.budget) {
+          *abort_flag = 1;
+          raise_status(p.status, kStatusFlagTimeout);
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    named_bar_sync(3, 256);
+    if (*abort_flag) break;
+    const int col0 = sn * 128;
+    const int chunks_per_row = min(128, p.N - col0) >> 3;          // 16-byte pieces of this sub-tile's rows
+    const int total = 128 * chunks_per_row;
+    for (int ch = tid; ch < total; ch += 256) {
+      const int r = ch / chunks_per_row, cv = ch - r * chunks_per_row;
+      const long long goff = (grow0 + r) * (long long)p.N + col0 + cv * 8;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      if (bias != nullptr) {
+        const uint4 bb = __ldg(reinterpret_cast<const uint4*>(bias + col0) + cv);
+        const uint32_t w[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] = f.x; acc[2 * e + 1] = f.y; }
+      }
+#pragma unroll
+      for (int k = 0; k < kGemmMaxPeers; ++k) {
+        if (k < n) {
+          const uint4 v = ld_relaxed_sys_u4(reinterpret_cast<const uint4*>(
+              reinterpret_cast<const __nv_bfloat16*>(c.peer[k]) + goff));
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+        }
+      }
+      *reinterpret_cast<uint4*>(out + (lrow0 + r) * (long long)p.N + col0 + cv * 8) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_aux,
@@ -89,7 +163,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = (p.comm.mode == 2 ? p.comm.gemm_ctas : (int)gridDim.x) >> 1;
-  const int num_units = p.num_m_blocks * p.num_n_blocks * p.num_splits;
+  const bool rs = p.comm.mode == 1;
+  // reduce-only launches (single-GPU tests of the reduce phase) skip the multiplication
+  const int num_units = (rs && p.comm.phase == 2) ? 0 : p.num_m_blocks * p.num_n_blocks * p.num_splits;
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) -------------------------------
@@ -186,6 +262,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     bool staged_before = false;
     int iter = 0;
     bool ok = true;
+    int pending_flag = -1, pending_owner = 0;     // mode 1: sub-tile whose stores are in flight (store thread)
     for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++iter) {
       int m_blk, n_blk;
       tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
@@ -207,7 +284,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       const bool staged = p.tma_store && !split_k && col_half < p.N &&
                           (col_half + kPairBlockN / 2 <= p.N || (p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr));
       if (staged_before) {       // the previous block's TMA stores must have read the staging buffer
-        if (store_thread) tma_store_wait_read<0>();
+        if (store_thread) {
+          if (rs) {              // ... and, under a fused reduce-scatter, have landed: tell the owner of the rows
+            tma_store_wait<0>();
+            if (pending_flag >= 0) rs_publish(p, pending_owner, pending_flag);
+            pending_flag = -1;
+          } else {
+            tma_store_wait_read<0>();
+          }
+        }
         named_bar_sync(1 + half, 128);
       }
       const bool two_pass = staged && p.tma_store_aux && p.aux_out != nullptr;
@@ -243,11 +328,24 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             if (col_half + b * 64 < p.N)
               tma_store_2d(&tma_c, smem_u32(stage + b * 16384), col_half + b * 64, (int32_t)row0);
           tma_store_commit();
+          if (rs && col_half < p.N) {
+            pending_flag = ((m_blk * p.num_n_blocks + n_blk) * 2 + (int)cta) * 2 + half;
+            pending_owner = (int)((row0 / p.comm.seg_rows) % p.comm.n);
+          }
         }
       }
       staged_before = staged;
     }
-    if (store_thread) tma_store_wait_read<0>();     // shared memory stays valid until the last store has read it
+    if (store_thread) {
+      if (rs) {
+        tma_store_wait<0>();
+        if (pending_flag >= 0) rs_publish(p, pending_owner, pending_flag);
+      } else {
+        tma_store_wait_read<0>();     // shared memory stays valid until the last store has read it
+      }
+    }
+    // ------------------- mode 1: reduce the sub-tiles this rank owns (all 8 epilogue warps) -------------------
+    if (rs && (p.comm.phase & 2)) rs_reduce_owned(p, (int)blockIdx.x, 2 * num_clusters, abort_flag, ok);
   }
 
   tc_fence_before();
@@ -301,6 +399,12 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   }
   if (p.comm.mode != 0 && p.comm.perm)
     p.comm.perm = (p.comm.seg_rows % kPairBlockM == 0 && p.num_m_blocks % p.comm.n == 0 && p.M % kPairBlockM == 0) ? 1 : 0;
+  if (p.comm.mode == 1) {
+    MRK_REQUIRE(p.tma_store && p.num_splits == 1, "gemm_rs: the partial product must leave through TMA stores");
+    MRK_REQUIRE(p.comm.units_total == p.num_m_blocks * p.num_n_blocks * 4, "gemm_rs: flag array does not match the tiling");
+    // every CTA reduces after its tiles: use the whole machine even for few tiles
+    if (p.comm.phase == 2) clusters = max_clusters;
+  }
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * (clusters + gather_clusters), 1, 1);

@@ -49,6 +49,9 @@ class TPComm:
         self.stage_elems = 0
         self.rs_calls = 0
         self.ag_calls = 0
+        self.tile_flags = None              # per-sub-tile epochs of the one-launch GEMM -> reduce-scatter
+        self.tile_flag_units = 0
+        self.fused_rs_calls = 0
         self.seg_flags = torch.zeros(1 << 14, dtype=torch.int32, device=self.device)
         self._flag_segs = 0
         self._flag_calls = 0
@@ -75,6 +78,21 @@ class TPComm:
             self.stage = [self.symm.alloc(self.stage_elems * 2, torch.bfloat16) for _ in range(2)]
 
     # -- GEMM -> reduce-scatter (or all-reduce) ----------------------------------------------------
+    @staticmethod
+    def one_launch_ok(M: int, N: int, seg_rows: int) -> bool:
+        """Shapes the one-launch kernel tiles: 128-row sub-tiles that do not straddle sequence
+        segments, 64-column TMA store boxes."""
+        return M % 128 == 0 and seg_rows % 128 == 0 and N % 64 == 0 and M > 128 and N > 128
+
+    def _ensure_tile_flags(self, units: int):
+        """The flag array only ever sees growing epochs, so one allocation serves every shape up to
+        its size; a larger shape re-allocates (collective, every rank takes the same path)."""
+        if units > self.tile_flag_units:
+            self._quiesce()
+            self.tile_flag_units = max(units, 1 << 14)
+            self.tile_flags = self.symm.alloc(4 * self.n * self.tile_flag_units, torch.int32)
+            self.fused_rs_calls = 0
+
     def gemm_reduce(self, x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], seg_rows: int,
                     all_rows: bool, b_mn: bool = False) -> torch.Tensor:
         """x2 [M, Kl] (this rank's slice of the contraction), w [N, Kl] (or [Kl, N] with ``b_mn``).
@@ -91,7 +109,6 @@ class TPComm:
         k = self.rs_calls
         self.rs_calls += 1
         part = self.part[k % 2]
-        G.gemm(x2, w, b_mn=b_mn, out=part.tensor[:M * N].view(M, N))
         st = _lib.stream_ptr()
         if all_rows:
             red = self.red[k % 2]
@@ -99,9 +116,21 @@ class TPComm:
         else:
             out = torch.empty(rows_local, N, dtype=torch.bfloat16, device=x2.device)
             dst_ptr = out.data_ptr()
-        _lib.check(lib.mrk_tp_reduce_pull(part.table, self.symm.ctrl.table, self.n, self.rank, dst_ptr, rows_local, N,
-                                          seg_rows, bias.data_ptr() if bias is not None else None, k + 1, 1,
-                                          self.budget_ms, st), "mrk_tp_reduce_pull")
+        if self.one_launch_ok(M, N, seg_rows) and x2.stride(1) == 1 and w.stride(1) == 1:
+            # one launch: sub-tile flags instead of a barrier, the sum starts while peers still multiply
+            units = int(lib.mrk_gemm_bf16_rs_units(M, N))
+            self._ensure_tile_flags(units)
+            self.fused_rs_calls += 1
+            _lib.check(lib.mrk_gemm_bf16_rs(
+                x2.data_ptr(), w.data_ptr(), part.table, self.tile_flags.table, dst_ptr,
+                bias.data_ptr() if bias is not None else None, M, N, K, x2.stride(0), w.stride(0),
+                _FLAG_B_MN if b_mn else 0, self.n, self.rank, seg_rows, self.fused_rs_calls, 3, self.budget_ms, st),
+                "mrk_gemm_bf16_rs")
+        else:
+            G.gemm(x2, w, b_mn=b_mn, out=part.tensor[:M * N].view(M, N))
+            _lib.check(lib.mrk_tp_reduce_pull(part.table, self.symm.ctrl.table, self.n, self.rank, dst_ptr, rows_local,
+                                              N, seg_rows, bias.data_ptr() if bias is not None else None, k + 1, 1,
+                                              self.budget_ms, st), "mrk_tp_reduce_pull")
         if not all_rows:
             return out
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)

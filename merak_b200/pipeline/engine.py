@@ -14,6 +14,8 @@ B200-specific choices:
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Callable, Dict, Iterator, List, Optional, Sequence, Tuple
 
@@ -60,6 +62,9 @@ class PipelineEngine:
         self.timers = SynchronizedWallClockTimer()
         self.rng_manager = RNGManager()
         self.wall_clock_breakdown = bool(args.wall_clock_breakdown)
+        # NVTX ranges around every pipeline instruction and every train_batch (for timeline profilers)
+        self._nvtx = bool(getattr(args, "nvtx_ranges", False) or os.environ.get("MERAK_NVTX") == "1") and \
+            self.device.type == "cuda"
         grid = mpu.get_grid()
         if grid is not None:
             topo = grid.topology
@@ -242,6 +247,8 @@ class PipelineEngine:
             check_device_status()
         if self.wall_clock_breakdown:
             self.timers("train_batch").start()
+        if self._nvtx:
+            torch.cuda.nvtx.range_push("train_batch %d" % self.global_steps)
         if self._graph_capable():
             self._train_batch_graphed()
         else:
@@ -250,6 +257,8 @@ class PipelineEngine:
                 self._reset_buffers(sched.num_pipe_buffers())
             self._exec_schedule(sched)
         self.agg_loss = self._aggregate_total_loss()
+        if self._nvtx:
+            torch.cuda.nvtx.range_pop()
         if self.wall_clock_breakdown:
             self.timers("train_batch").stop()
         self.global_steps += 1
@@ -395,13 +404,20 @@ class PipelineEngine:
             S.ReduceTiedGrads: self._exec_reduce_tied_grads, S.ReduceGrads: self._exec_reduce_grads,
             S.OptimizerStep: self._exec_optimizer_step,
         }
+        nvtx = self._nvtx
         for step_cmds in sched.steps():
             for cmd in step_cmds:
                 fn = table[type(cmd)]
-                if "buffer_id" in cmd.kwargs:
-                    fn(cmd.buffer_id)
-                else:
-                    fn()
+                if nvtx:                 # one range per pipeline instruction, named like the instruction
+                    torch.cuda.nvtx.range_push("%s(%s)" % (type(cmd).__name__, cmd.kwargs.get("buffer_id", "")))
+                try:
+                    if "buffer_id" in cmd.kwargs:
+                        fn(cmd.buffer_id)
+                    else:
+                        fn()
+                finally:
+                    if nvtx:
+                        torch.cuda.nvtx.range_pop()
 
     # -- data ------------------------------------------------------------------------------------
     def _exec_load_micro_batch(self, buf: int):

@@ -367,3 +367,58 @@ def test_flag_barriers_with_skewed_ranks_two_gpus(tmp_path):
     with open(out) as f:
         r = json.load(f)
     assert r["ok"] == 1 and r["status"] == 0, r
+
+
+@pytest.mark.parametrize("n,B,L,N,K", [(2, 1, 512, 512, 256), (4, 2, 512, 384, 192), (2, 3, 256, 1600, 128)])
+def test_gemm_reduce_scatter_one_launch_emulated(n, B, L, N, K):
+    """GEMM -> reduce-scatter kernel with the ranks emulated on one GPU: first every rank multiplies
+    and publishes its sub-tile flags (phase 1), then every rank reduces the sub-tiles it owns
+    (phase 2); in production both phases are one launch per rank.  Oracle: fp32 PyTorch."""
+    from merak_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = torch.device("cuda")
+    torch.manual_seed(n * 100 + N)
+    M, seg = B * L, L // n
+    xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) * 0.5 for _ in range(n)]
+    ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.5 for _ in range(n)]
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    parts = [torch.zeros(M, N, device=dev, dtype=torch.bfloat16) for _ in range(n)]
+    units = int(lib.mrk_gemm_bf16_rs_units(M, N))
+    flags = [torch.zeros(n * units, dtype=torch.int32, device=dev) for _ in range(n)]
+    outs = [torch.zeros(M // n, N, device=dev, dtype=torch.bfloat16) for _ in range(n)]
+    pt, ft = _table([p_.data_ptr() for p_ in parts]), _table([f.data_ptr() for f in flags])
+    st = _lib.stream_ptr()
+    torch.cuda.synchronize()
+    _lib.status(clear=True)
+    for epoch in (1, 2):                       # twice: flags of the first call must not satisfy the second
+        if epoch == 2:
+            xs = [x * 0.5 for x in xs]
+        for phase in (1, 2):
+            for r in range(n):
+                _lib.check(lib.mrk_gemm_bf16_rs(xs[r].data_ptr(), ws[r].data_ptr(), pt, ft, outs[r].data_ptr(),
+                                                bias.data_ptr(), M, N, K, K, K, 0, n, r, seg, epoch, phase, 200, st),
+                           "gemm_rs")
+        torch.cuda.synchronize()
+        assert _lib.status(clear=True) == 0
+        full = sum(x.float() @ w.float().t() for x, w in zip(xs, ws)) + bias.float()
+        ref = full.view(B, n, seg, N)
+        for r in range(n):
+            want = ref[:, r].reshape(M // n, N)
+            torch.testing.assert_close(outs[r].float(), want, rtol=3e-2, atol=3e-1)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_gemm_reduce_scatter_one_launch_two_gpus(tmp_path):
+    """The one-launch GEMM -> reduce-scatter on real peers: sub-tile flags cross NVLink, owners pull the
+    partial products while the other rank is still multiplying."""
+    import json
+    out = str(tmp_path / "rs.json")
+    script = os.path.join(HERE, "dist_scripts", "tp_gemm_rs.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), script, "--out", out, "--shapes",
+           "1x1024x512x256,2x512x1600x320,4x1024x4096x512"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert res.returncode == 0, res.stderr[-3000:]
+    with open(out) as f:
+        r = json.load(f)
+    assert r["status"] == 0 and all(x["ok"] for x in r["results"]), r
