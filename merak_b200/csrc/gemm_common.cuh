@@ -19,9 +19,12 @@ namespace mrk {
 //           control memory of the rank that owns those rows.  Row blocks are visited with this
 //           rank's own segments last, so what the peers need first is produced first.  When a CTA
 //           has finished its tiles, its epilogue warps turn to the sub-tiles this rank owns: they
-//           wait for the n flags of a sub-tile, pull the n partials (peer loads over NVLink), sum
-//           them in fp32, add the bias and write the reduced rows.  One launch, no barrier over the
-//           group: a sub-tile is reduced as soon as its last contribution exists.
+//           wait for the n flags of a sub-tile, pull the n partials (bulk copies over NVLink into
+//           shared memory), sum them in fp32, add the bias and write the reduced rows.  A few
+//           CTAs of the grid do nothing else from the start, so the sum of this rank's own
+//           segment (whose last contribution is this rank's own, by the order above) runs under
+//           the multiplication of the remaining tiles; pieces are claimed from a queue, which the
+//           compute CTAs join when their tiles are done.  One launch, no barrier over the group.
 // Rows of the full [M, *] matrix are grouped in segments of `seg_rows`; segment s belongs to rank
 // s % n and is that rank's local segment s / n (batch-first sequence sharding).
 constexpr int kGemmMaxPeers = 8;
@@ -45,6 +48,8 @@ struct GemmComm {
   int units_total;             // sub-tiles of the full output: num_m_blocks * num_n_blocks * 4
   int own_last;                // row-block order ends (instead of starts) with this rank's own segments
   int phase;                   // 3 = multiply and reduce; 1 = multiply only; 2 = reduce only (tests on one GPU)
+  int reduce_ctas;             // CTAs behind the compute CTAs that only reduce (resident from the start)
+  uint32_t* rs_queue;          // work queue of the reduce phase: next piece to claim (zero at launch)
   void* rs_out;                // [M / n, N] bf16, this rank's reduced rows
   const void* rs_bias;         // optional bf16 [N]
 };

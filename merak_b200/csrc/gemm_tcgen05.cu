@@ -389,7 +389,8 @@ MRK_API int mrk_gemm_bf16_rs_units(int M, int N) {
 
 MRK_API int mrk_gemm_bf16_rs(const void* A, const void* B, void* const* parts, void* const* tile_flags, void* out,
                              const void* bias, int M, int N, int K, long long lda, long long ldb, int flags, int n,
-                             int rank, int seg_rows, unsigned epoch, int phase, int budget_ms, void* stream) {
+                             int rank, int seg_rows, unsigned epoch, int phase, int reduce_ctas, unsigned* queue,
+                             int budget_ms, void* stream) {
   MRK_REQUIRE(M % 128 == 0 && seg_rows % 128 == 0 && N % 64 == 0 && M > 128 && N > 128,
               "gemm_rs: shape %dx%d (segments of %d rows) is not tileable into 128-row sub-tiles", M, N, seg_rows);
   MRK_REQUIRE(!(flags & (MRK_GEMM_OUT_F32 | MRK_GEMM_ACCUMULATE)), "gemm_rs: bf16 partial products only");
@@ -403,6 +404,8 @@ MRK_API int mrk_gemm_bf16_rs(const void* A, const void* B, void* const* parts, v
   c.phase = phase;
   c.rs_out = out;
   c.rs_bias = bias;
+  c.reduce_ctas = reduce_ctas;
+  c.rs_queue = queue;
   return gemm_entry(A, B, parts[rank], M, N, K, lda, ldb, N, nullptr, nullptr, 0, nullptr, 0, MRK_ACT_NONE,
                     MRK_AUX_NONE, flags, 1.0f, 512, &c, stream);
 }

@@ -37,7 +37,8 @@ int mrk_gemm_bf16_ag(void* gathered, void* const* peer_shards, const void* B, vo
 int mrk_gemm_bf16_rs_units(int M, int N);
 int mrk_gemm_bf16_rs(const void* A, const void* B, void* const* parts, void* const* tile_flags, void* out,
                      const void* bias, int M, int N, int K, long long lda, long long ldb, int flags, int n, int rank,
-                     int seg_rows, unsigned epoch, int phase, int budget_ms, void* stream);
+                     int seg_rows, unsigned epoch, int phase, int reduce_ctas, unsigned* queue, int budget_ms,
+                     void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -32,75 +32,219 @@ constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes
 // mode 1, store thread: the partial product of sub-tile `u` is complete in this rank's buffer.
 __device__ __forceinline__ void rs_publish(const GemmParams& p, int owner, int u) {
   const GemmComm& c = p.comm;
-  __threadfence_system();
+  // the caller has waited for its bulk stores to complete; the release store orders them before the flag
   st_release_sys_u32(c.tile_flags[owner] + (size_t)c.rank * c.units_total + u, c.epoch);
 }
 
-// mode 1, the 256 epilogue threads of every CTA: sum the partial products of the 128 x 128 sub-tiles
-// whose rows this rank owns, as their flags arrive.  Bounded waits; on a timeout the CTA stops reducing.
-__device__ __noinline__ void rs_reduce_owned(const GemmParams& p, int cta_lin, int num_ctas, volatile int* abort_flag,
-                                             bool ok_in) {
+// ---- mode 1: reduce phase ---------------------------------------------------------------------------
+// After its tiles, every CTA sums the sub-tiles this rank owns.  Peer loads take microseconds, so the
+// remote partial products are not read with register loads but streamed into the (now idle) operand
+// ring with bulk asynchronous copies, several pieces deep: the otherwise idle TMA thread is the
+// producer (waits for a piece's flags, issues one 256-byte row copy per row and remote rank, completion
+// on an mbarrier); the 256 epilogue threads are the consumer (remote rows from shared memory + the local
+// partial from global memory + bias -> bf16 rows of the result).  A piece is `rows` rows of one
+// 128-column sub-tile, sized so that the copies of all remote ranks fit one slot of the ring.
+struct RsPlan {
+  int rows;          // rows per piece: 128 (n = 2), 64 (n <= 4), 32 (n <= 8)
+  int pieces_per_unit;
+  int slot_bytes;    // (n - 1) * rows * 256
+  int slots;
+  int sub_per_row, owned_units;
+};
+
+__device__ __forceinline__ RsPlan rs_plan(const GemmParams& p, int ring_bytes) {
+  RsPlan q;
+  const int n = p.comm.n;
+  q.rows = n <= 2 ? 128 : (n <= 4 ? 64 : 32);
+  q.pieces_per_unit = 128 / q.rows;
+  q.slot_bytes = (n - 1) * q.rows * 256;
+  q.slots = ring_bytes / q.slot_bytes;
+  if (q.slots > 8) q.slots = 8;
+  q.sub_per_row = (p.N + 127) / 128;
+  q.owned_units = ((p.M / n) / 128) * q.sub_per_row;
+  return q;
+}
+
+// piece index -> rows and columns.  lrow0: first local row; grow0: the same row in the full matrix.
+__device__ __forceinline__ void rs_piece_coords(const GemmParams& p, const RsPlan& q, int piece, long long& lrow0,
+                                                long long& grow0, int& col0, int& row_bytes, int& unit_flag) {
+  const GemmComm& c = p.comm;
+  const int unit = piece / q.pieces_per_unit, part = piece - unit * q.pieces_per_unit;
+  const int lb = unit / q.sub_per_row, sn = unit - lb * q.sub_per_row;
+  const long long l0 = (long long)lb * 128;
+  const long long b = l0 / c.seg_rows;
+  const long long g0 = (b * c.n + c.rank) * c.seg_rows + (l0 - b * c.seg_rows);
+  const int m_blk = (int)(g0 / kPairBlockM), cta_p = (int)((g0 % kPairBlockM) / 128);
+  unit_flag = ((m_blk * p.num_n_blocks + (sn >> 1)) * 2 + cta_p) * 2 + (sn & 1);
+  lrow0 = l0 + part * q.rows;
+  grow0 = g0 + part * q.rows;
+  col0 = sn * 128;
+  row_bytes = min(128, p.N - col0) * 2;
+}
+
+// producer: one warp.  Lane 0 claims pieces from the queue, waits for their flags and for a free slot;
+// the claimed index (or -1 at the end) is handed to the consumers through `slot_piece`; all 32 lanes
+// issue the row copies (a single thread issuing 128 copies per piece was the bottleneck of this phase).
+// `drain_ring`: the caller is a compute CTA whose operand ring may still be read by UMMAs: continue
+// the ring's bookkeeping (`stage` / `phase`) until every stage has been released.
+__device__ __forceinline__ void rs_pull_producer(const GemmParams& p, uint8_t* ring, int ring_bytes,
+                                                 uint64_t* empty_bar, uint64_t* pull_full, uint64_t* pull_empty,
+                                                 volatile int* slot_piece, bool drain_ring, int stage, uint32_t phase,
+                                                 volatile int* abort_flag) {
   const GemmComm& c = p.comm;
   const int n = c.n;
-  const int tid = (int)threadIdx.x - 64;                   // 0..255
-  const int sub_per_row = (p.N + 127) / 128;
-  const int local_blocks = (p.M / n) / 128;
-  const int owned = local_blocks * sub_per_row;
+  const int lane = threadIdx.x & 31;
+  bool ok = true;
+  if (drain_ring && lane == 0) {
+    for (int i = 0; i < kPairStages && ok; ++i) {
+      ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
+      if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+    }
+  }
+  const RsPlan q = rs_plan(p, ring_bytes);
   const uint32_t* my_flags = c.tile_flags[c.rank];
-  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c.rs_out);
-  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(c.rs_bias);
-  if (!ok_in && tid == 0) *abort_flag = 1;
-  for (int q = cta_lin; q < owned; q += num_ctas) {
-    const int lb = q / sub_per_row, sn = q - lb * sub_per_row;
-    const long long lrow0 = (long long)lb * 128;
-    const long long b = lrow0 / c.seg_rows;
-    const long long grow0 = (b * n + c.rank) * c.seg_rows + (lrow0 - b * c.seg_rows);
-    const int m_blk = (int)(grow0 / kPairBlockM), cta_p = (int)((grow0 % kPairBlockM) / 128);
-    const int u = ((m_blk * p.num_n_blocks + (sn >> 1)) * 2 + cta_p) * 2 + (sn & 1);
-    if (tid < n) {
-      const uint32_t* f = my_flags + (size_t)tid * c.units_total + u;
-      const long long t0 = clock64();
-      while ((int32_t)(ld_acquire_sys_u32(f) - c.epoch) < 0) {
-        if (*abort_flag || clock64() - t0 > c.budget) {
-          *abort_flag = 1;
-          raise_status(p.status, kStatusFlagTimeout);
-          break;
+  const int total_pieces = q.owned_units * q.pieces_per_unit;
+  int slot = 0;
+  uint32_t sphase = 0;
+  while (true) {
+    int piece = -1;
+    long long lrow0 = 0, grow0 = 0;
+    int col0 = 0, row_bytes = 0, uf = 0;
+    if (lane == 0) {
+      piece = ok ? (int)atomicAdd(c.rs_queue, 1u) : total_pieces;
+      if (piece >= total_pieces) piece = -1;
+      if (!mbar_wait(smem_u32(&pull_empty[slot]), sphase ^ 1u, abort_flag, p.status)) piece = -2;   // give up silently
+      if (piece >= 0) {
+        rs_piece_coords(p, q, piece, lrow0, grow0, col0, row_bytes, uf);
+        for (int k = 0; k < n && ok; ++k) {          // every rank's partial product of this sub-tile exists
+          const uint32_t* f = my_flags + (size_t)k * c.units_total + uf;
+          const long long t0 = clock64();
+          while ((int32_t)(ld_acquire_sys_u32(f) - c.epoch) < 0) {
+            if (*abort_flag || clock64() - t0 > c.budget) {
+              *abort_flag = 1;
+              raise_status(p.status, kStatusFlagTimeout);
+              ok = false;
+              break;
+            }
+            __nanosleep(64);
+          }
         }
-        __nanosleep(64);
+        if (!ok) piece = -1;
+      }
+      if (piece >= -1) {
+        slot_piece[slot] = piece;
+        if (piece < 0) mbar_arrive(smem_u32(&pull_full[slot]));                 // tells the consumers to stop
+        else mbar_arrive_expect_tx(smem_u32(&pull_full[slot]), (uint32_t)((n - 1) * q.rows * row_bytes));
       }
     }
-    named_bar_sync(3, 256);
-    if (*abort_flag) break;
-    const int col0 = sn * 128;
-    const int chunks_per_row = min(128, p.N - col0) >> 3;          // 16-byte pieces of this sub-tile's rows
-    const int total = 128 * chunks_per_row;
-    for (int ch = tid; ch < total; ch += 256) {
-      const int r = ch / chunks_per_row, cv = ch - r * chunks_per_row;
-      const long long goff = (grow0 + r) * (long long)p.N + col0 + cv * 8;
-      float acc[8];
+    piece = __shfl_sync(0xffffffffu, piece, 0);
+    if (piece < 0) return;
+    grow0 = __shfl_sync(0xffffffffu, grow0, 0);
+    col0 = __shfl_sync(0xffffffffu, col0, 0);
+    row_bytes = __shfl_sync(0xffffffffu, row_bytes, 0);
+    const uint32_t fb = smem_u32(&pull_full[slot]);
+    uint32_t dst = smem_u32(ring + slot * q.slot_bytes);
+    for (int k = 0; k < n; ++k) {
+      if (k == c.rank) continue;
+      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(c.peer[k]) + grow0 * (long long)p.N + col0;
+      for (int r = lane; r < q.rows; r += 32)
+        bulk_g2s(dst + r * 256, src + (long long)r * p.N, (uint32_t)row_bytes, fb);
+      dst += q.rows * 256;
+    }
+    if (++slot == q.slots) { slot = 0; sphase ^= 1u; }
+  }
+}
+
+// consumer: the 256 threads of warps 2..9.
+__device__ __forceinline__ void rs_pull_consumer(const GemmParams& p, uint8_t* ring, int ring_bytes,
+                                                 uint64_t* pull_full, uint64_t* pull_empty, volatile int* slot_piece,
+                                                 volatile int* abort_flag) {
+  const GemmComm& c = p.comm;
+  const int n = c.n;
+  const int tid = (int)threadIdx.x - 64;
+  const RsPlan q = rs_plan(p, ring_bytes);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c.rs_out);
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(c.rs_bias);
+  const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(c.peer[c.rank]);
+  int slot = 0;
+  uint32_t sphase = 0;
+  while (true) {
+    bool ok = mbar_wait(smem_u32(&pull_full[slot]), sphase, abort_flag, p.status);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return;
+    const int piece = slot_piece[slot];
+    if (piece < 0) return;
+    long long lrow0, grow0;
+    int col0, row_bytes, uf;
+    rs_piece_coords(p, q, piece, lrow0, grow0, col0, row_bytes, uf);
+    const uint8_t* src = ring + slot * q.slot_bytes;
+    const int chunks_per_row = row_bytes >> 4;
+    const int total = q.rows * chunks_per_row;
+    for (int ch0 = tid; ch0 < total; ch0 += 256 * 4) {
+      // four independent 16-byte loads of the local partial product in flight per thread
+      uint4 own[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      if (bias != nullptr) {
-        const uint4 bb = __ldg(reinterpret_cast<const uint4*>(bias + col0) + cv);
-        const uint32_t w[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] = f.x; acc[2 * e + 1] = f.y; }
+      for (int bq = 0; bq < 4; ++bq) {
+        const int ch = ch0 + bq * 256;
+        if (ch < total) {
+          const int r = ch / chunks_per_row, cv = ch - r * chunks_per_row;
+          own[bq] = *reinterpret_cast<const uint4*>(mine + (grow0 + r) * (long long)p.N + col0 + cv * 8);
+        }
       }
 #pragma unroll
-      for (int k = 0; k < kGemmMaxPeers; ++k) {
-        if (k < n) {
-          const uint4 v = ld_relaxed_sys_u4(reinterpret_cast<const uint4*>(
-              reinterpret_cast<const __nv_bfloat16*>(c.peer[k]) + goff));
+      for (int bq = 0; bq < 4; ++bq) {
+        const int ch = ch0 + bq * 256;
+        if (ch >= total) continue;
+        const int r = ch / chunks_per_row, cv = ch - r * chunks_per_row;
+        float acc[8];
+        {
+          const uint32_t w[4] = {own[bq].x, own[bq].y, own[bq].z, own[bq].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] = f.x; acc[2 * e + 1] = f.y; }
+        }
+        if (bias != nullptr) {
+          const uint4 bb = __ldg(reinterpret_cast<const uint4*>(bias + col0) + cv);
+          const uint32_t w[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+        }
+        for (int k = 0; k < n - 1; ++k) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src + (k * q.rows + r) * 256 + cv * 16);
           const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
         }
+        *reinterpret_cast<uint4*>(out + (lrow0 + r) * (long long)p.N + col0 + cv * 8) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
       }
-      *reinterpret_cast<uint4*>(out + (lrow0 + r) * (long long)p.N + col0 + cv * 8) =
-          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                     pack_bf16x2(acc[6], acc[7]));
     }
+    mbar_arrive(smem_u32(&pull_empty[slot]));        // 256 arrivals free the slot
+    if (++slot == q.slots) { slot = 0; sphase ^= 1u; }
   }
+}
+
+// A CTA that only reduces (blockIdx >= comm.gemm_ctas): the whole dynamic shared memory is its ring.
+__device__ __forceinline__ void rs_reducer_role(const GemmParams& p, uint8_t* smem, int ring_bytes, uint8_t* bar_area) {
+  uint64_t* pull_full = reinterpret_cast<uint64_t*>(bar_area + 256);
+  uint64_t* pull_empty = pull_full + 8;
+  volatile int* slot_piece = reinterpret_cast<volatile int*>(bar_area + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_area + 640);
+  if (!(p.comm.phase & 2)) return;                   // multiply-only launch (single-GPU tests)
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(smem_u32(&pull_full[s]), 1);
+      mbar_init(smem_u32(&pull_empty[s]), 256);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0)
+    rs_pull_producer(p, smem, ring_bytes, nullptr, pull_full, pull_empty, slot_piece, false, 0, 0u, abort_flag);
+  else if (warp >= 2)
+    rs_pull_consumer(p, smem, ring_bytes, pull_full, pull_empty, slot_piece, abort_flag);
 }
 
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -119,6 +263,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;                     // used in the even CTA only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* pull_full = reinterpret_cast<uint64_t*>(bar_base + 256);   // mode 1, reduce phase (8 slots at most)
+  uint64_t* pull_empty = pull_full + 8;
+  volatile int* slot_piece = reinterpret_cast<volatile int*>(bar_base + 512);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();          // 0 = leader
@@ -133,6 +280,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     comm_gather_role(p, smem, kPairStages * kPairStageBytes + kPairStagingBytes);
     return;
   }
+  // fused reduce-scatter (mode 1): the clusters behind the compute clusters only reduce
+  if (p.comm.mode == 1 && (int)blockIdx.x >= p.comm.gemm_ctas) {
+    rs_reducer_role(p, smem, kPairStages * kPairStageBytes + kPairStagingBytes, bar_base);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -143,6 +295,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[s]), 2 * 8);        // one arrival per epilogue warp of both CTAs
+    }
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(smem_u32(&pull_full[s]), 1);
+      mbar_init(smem_u32(&pull_empty[s]), 256);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -162,13 +318,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
 
   const int cluster_id = blockIdx.x >> 1;
-  const int num_clusters = (p.comm.mode == 2 ? p.comm.gemm_ctas : (int)gridDim.x) >> 1;
+  const int num_clusters = (p.comm.mode != 0 ? p.comm.gemm_ctas : (int)gridDim.x) >> 1;
   const bool rs = p.comm.mode == 1;
   // reduce-only launches (single-GPU tests of the reduce phase) skip the multiplication
   const int num_units = (rs && p.comm.phase == 2) ? 0 : p.num_m_blocks * p.num_n_blocks * p.num_splits;
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) -------------------------------
+    int rs_stage = 0;
+    uint32_t rs_phase = 0;
+    bool rs_ok = true;
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -210,6 +369,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
       }
+      rs_stage = stage;
+      rs_phase = phase;
+      rs_ok = ok;
+    }
+    if (rs && (p.comm.phase & 2)) {               // reduce phase: the whole warp drives the pulls
+      __syncwarp();
+      rs_ok = __shfl_sync(0xffffffffu, (int)rs_ok, 0) != 0;
+      if (rs_ok)
+        rs_pull_producer(p, smem, kPairStages * kPairStageBytes, empty_bar, pull_full, pull_empty, slot_piece, true,
+                         rs_stage, rs_phase, abort_flag);
     }
   } else if (warp == 1) {
     // ------------------------------- UMMA issuer (leader CTA) -------------------------------
@@ -345,7 +514,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       }
     }
     // ------------------- mode 1: reduce the sub-tiles this rank owns (all 8 epilogue warps) -------------------
-    if (rs && (p.comm.phase & 2)) rs_reduce_owned(p, (int)blockIdx.x, 2 * num_clusters, abort_flag, ok);
+    if (rs && (p.comm.phase & 2) && ok)
+      rs_pull_consumer(p, smem, kPairStages * kPairStageBytes, pull_full, pull_empty, slot_piece, abort_flag);
   }
 
   tc_fence_before();
@@ -402,8 +572,15 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   if (p.comm.mode == 1) {
     MRK_REQUIRE(p.tma_store && p.num_splits == 1, "gemm_rs: the partial product must leave through TMA stores");
     MRK_REQUIRE(p.comm.units_total == p.num_m_blocks * p.num_n_blocks * 4, "gemm_rs: flag array does not match the tiling");
-    // every CTA reduces after its tiles: use the whole machine even for few tiles
-    if (p.comm.phase == 2) clusters = max_clusters;
+    MRK_REQUIRE(p.comm.rs_queue != nullptr, "gemm_rs: no work queue");
+    // compute clusters + reducer clusters, all resident at once (the reducers must run from the start)
+    gather_clusters = (p.comm.reduce_ctas + 1) / 2;
+    if (gather_clusters >= max_clusters) gather_clusters = max_clusters / 2;
+    const int room = max_clusters - gather_clusters;
+    clusters = units < room ? units : room;
+    if (p.comm.phase == 2) clusters = room;            // reduce-only launch: everybody reduces
+    p.comm.gemm_ctas = 2 * clusters;
+    MRK_CUDA_OK(cudaMemsetAsync(p.comm.rs_queue, 0, sizeof(uint32_t), stream));
   }
 
   cudaLaunchConfig_t cfg = {};

@@ -93,7 +93,7 @@ def _declare(lib):
     sig("mrk_tp_gather_rows", c_int, P, P, c_int, c_int, P, c_ll, c_int, c_int, c_uint, c_int, c_int, P)
     sig("mrk_gemm_bf16_rs_units", c_int, c_int, c_int)
     sig("mrk_gemm_bf16_rs", c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int, c_int, c_int,
-        c_uint, c_int, c_int, P)
+        c_uint, c_int, c_int, P, c_int, P)
     sig("mrk_gemm_bf16_ag", c_int, P, P, P, P, c_int, c_int, c_int, c_ll, c_ll, P, P, c_ll, c_int, c_int, c_float,
         P, P, c_uint, c_int, c_int, c_int, c_int, c_uint, c_int, P)
     sig("mrk_moe_alltoall_push", c_int, P, P, c_int, c_int, P, P, P, c_int, c_int, c_uint, c_int, c_int, P)

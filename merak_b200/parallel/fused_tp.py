@@ -18,6 +18,7 @@ Merak/core/mpu/mappings.py:30-120).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
@@ -28,6 +29,12 @@ from ..ops import gemm as G
 from ..ops.linear import _as2d, _bias_grad, _weight_grad
 from .symm import SymmGroup
 
+REDUCE_CTAS = 8      # CTAs of a fused GEMM -> reduce-scatter that only pull and sum (resident from the start)
+# GEMM -> reduce-scatter as ONE launch (sub-tile flags, reduce phase inside the GEMM kernel) or as the
+# GEMM followed by the pull-and-sum kernel.  Measured on two B200s the two-launch form is still the
+# faster one (0.319 ms against 0.353 ms at 8192 x 4096 x 5504; NCCL + matmul: 0.451 ms), so it is the
+# default; MERAK_TP_ONE_LAUNCH=1 selects the one-launch kernel.
+ONE_LAUNCH = os.environ.get("MERAK_TP_ONE_LAUNCH", "0") == "1"
 GATHER_CTAS = 16     # upper bound on the CTAs of a fused all-gather GEMM that only move data
 ENABLED = True      # cleared by the engine when ``comm_mode`` is not "fused"
 _FLAG_B_MN = 16
@@ -52,6 +59,8 @@ class TPComm:
         self.tile_flags = None              # per-sub-tile epochs of the one-launch GEMM -> reduce-scatter
         self.tile_flag_units = 0
         self.fused_rs_calls = 0
+        self.force_one_launch = False
+        self.rs_queue = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.seg_flags = torch.zeros(1 << 14, dtype=torch.int32, device=self.device)
         self._flag_segs = 0
         self._flag_calls = 0
@@ -116,7 +125,8 @@ class TPComm:
         else:
             out = torch.empty(rows_local, N, dtype=torch.bfloat16, device=x2.device)
             dst_ptr = out.data_ptr()
-        if self.one_launch_ok(M, N, seg_rows) and x2.stride(1) == 1 and w.stride(1) == 1:
+        if (ONE_LAUNCH or self.force_one_launch) and self.one_launch_ok(M, N, seg_rows) and x2.stride(1) == 1 and \
+                w.stride(1) == 1:
             # one launch: sub-tile flags instead of a barrier, the sum starts while peers still multiply
             units = int(lib.mrk_gemm_bf16_rs_units(M, N))
             self._ensure_tile_flags(units)
@@ -124,8 +134,8 @@ class TPComm:
             _lib.check(lib.mrk_gemm_bf16_rs(
                 x2.data_ptr(), w.data_ptr(), part.table, self.tile_flags.table, dst_ptr,
                 bias.data_ptr() if bias is not None else None, M, N, K, x2.stride(0), w.stride(0),
-                _FLAG_B_MN if b_mn else 0, self.n, self.rank, seg_rows, self.fused_rs_calls, 3, self.budget_ms, st),
-                "mrk_gemm_bf16_rs")
+                _FLAG_B_MN if b_mn else 0, self.n, self.rank, seg_rows, self.fused_rs_calls, 3, REDUCE_CTAS,
+                self.rs_queue.data_ptr(), self.budget_ms, st), "mrk_gemm_bf16_rs")
         else:
             G.gemm(x2, w, b_mn=b_mn, out=part.tensor[:M * N].view(M, N))
             _lib.check(lib.mrk_tp_reduce_pull(part.table, self.symm.ctrl.table, self.n, self.rank, dst_ptr, rows_local,

@@ -386,6 +386,7 @@ def test_gemm_reduce_scatter_one_launch_emulated(n, B, L, N, K):
     units = int(lib.mrk_gemm_bf16_rs_units(M, N))
     flags = [torch.zeros(n * units, dtype=torch.int32, device=dev) for _ in range(n)]
     outs = [torch.zeros(M // n, N, device=dev, dtype=torch.bfloat16) for _ in range(n)]
+    queue = torch.zeros(1, dtype=torch.int32, device=dev)
     pt, ft = _table([p_.data_ptr() for p_ in parts]), _table([f.data_ptr() for f in flags])
     st = _lib.stream_ptr()
     torch.cuda.synchronize()
@@ -396,7 +397,8 @@ def test_gemm_reduce_scatter_one_launch_emulated(n, B, L, N, K):
         for phase in (1, 2):
             for r in range(n):
                 _lib.check(lib.mrk_gemm_bf16_rs(xs[r].data_ptr(), ws[r].data_ptr(), pt, ft, outs[r].data_ptr(),
-                                                bias.data_ptr(), M, N, K, K, K, 0, n, r, seg, epoch, phase, 200, st),
+                                                bias.data_ptr(), M, N, K, K, K, 0, n, r, seg, epoch, phase, 8,
+                                                queue.data_ptr(), 200, st),
                            "gemm_rs")
         torch.cuda.synchronize()
         assert _lib.status(clear=True) == 0
