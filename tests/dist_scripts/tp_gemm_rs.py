@@ -33,6 +33,7 @@ def timed(fn, iters, group):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="1x1024x512x256")       # BxLxNxK(local) ; separated by commas
+    ap.add_argument("--ag_shapes", default="")                  # all-gather -> GEMM: BxLxN(local)xK
     ap.add_argument("--bench", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", required=True)
@@ -83,6 +84,33 @@ def main():
             flops = 2.0 * M * N * K
             bytes_link = 2.0 * M * N * (n - 1) / n
             rec["roofline_ms"] = max(flops / 1601.6e12, bytes_link / 770e9) * 1e3
+            rec["fraction_of_roofline"] = rec["roofline_ms"] / rec["fused_ms"]
+        results.append(rec)
+    for spec in [t for t in o.ag_shapes.split(",") if t]:
+        B, L, N, K = (int(v) for v in spec.split("x"))
+        M, seg = B * L, L // n
+        torch.manual_seed(4321 + rank)
+        xl = (torch.randn(B, seg, K, device="cuda", dtype=torch.bfloat16) * 0.3).view(B * seg, K)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.3
+        y, gathered, _ = comm.gather_gemm(xl, w, None, seg)
+        parts = [torch.empty_like(xl) for _ in range(n)]
+        dist.all_gather(parts, xl, group=group)
+        full = torch.stack([t.view(B, seg, K) for t in parts], 1).reshape(M, K)
+        ref = full.float() @ w.float().t()
+        err = float((y.float() - ref).abs().max())
+        tol = 3e-2 * float(ref.abs().max()) + 0.3
+        rec = {"shape": "ag " + spec, "max_err": err, "tol": tol, "ok": err <= tol and torch.equal(gathered, full)}
+        if o.bench:
+            rec["fused_ms"] = timed(lambda: comm.gather_gemm(xl, w, None, seg), o.iters, group)
+            buf = torch.empty(n * xl.numel(), device="cuda", dtype=torch.bfloat16)
+
+            def nccl_ag():
+                dist.all_gather_into_tensor(buf, xl.view(-1), group=group)
+                g = buf.view(n, B, seg, K).transpose(0, 1).reshape(M, K)
+                return torch.matmul(g, w.t())
+            rec["nccl_ms"] = timed(nccl_ag, o.iters, group)
+            rec["gemm_only_ms"] = timed(lambda: torch.matmul(full, w.t()), o.iters, group)
+            rec["roofline_ms"] = max(2.0 * M * N * K / 1601.6e12, 2.0 * M * K * (n - 1) / n / 770e9) * 1e3
             rec["fraction_of_roofline"] = rec["roofline_ms"] / rec["fused_ms"]
         results.append(rec)
     torch.cuda.synchronize()
