@@ -1,0 +1,17 @@
+"""DINOv2 image classification (examples/models/dinov2): the Hugging Face ``Dinov2ForImageClassification`` with random weights on generated data.
+
+    torchrun --nproc_per_node=4 --master-addr 127.0.0.1 examples/models/dinov2/run_dinov2.py \\
+        --output_dir ./out --per_device_train_batch_size 4 --gradient_accumulation_steps 4 --max_steps 50
+    PP=2 TP=2 ...   (degrees come from the environment; ``--tiny 1`` shrinks the model for a CPU run)
+"""
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+import transformers as T  # noqa: E402
+from _hf import run  # noqa: E402
+
+if __name__ == "__main__":
+    run(T.Dinov2Config, T.Dinov2ForImageClassification, mode="vision_only",
+        tp_lists=(['attention.query', 'attention.key', 'attention.value', 'mlp.fc1'],
+                  ['attention.output.dense', 'mlp.fc2']))

@@ -29,6 +29,7 @@ the model allows it (``dynamic_batch``), otherwise with the traced batch size ba
 """
 from __future__ import annotations
 
+import contextlib
 import inspect
 import operator
 import re
@@ -81,6 +82,56 @@ def _resolve(root: nn.Module, path: str):
     return obj
 
 
+class _no_layerdrop:
+    """LayerDrop (BART / OPT / wav2vec2 families: ``if torch.rand([]) < self.layerdrop: skip the
+    layer``) is a coin toss per layer and step that a static graph cannot hold.  While exporting,
+    the scalar draw is a constant 1.0, i.e. every layer is kept (LayerDrop off), which is also what
+    the reference's traced graphs do."""
+
+    def __enter__(self):
+        self._rand = torch.rand
+
+        def rand(*size, **kw):
+            if len(size) == 1 and isinstance(size[0], (list, tuple)) and len(size[0]) == 0 and not kw:
+                return 1.0
+            return self._rand(*size, **kw)
+        torch.rand = rand
+        return self
+
+    def __exit__(self, *exc):
+        torch.rand = self._rand
+        return False
+
+
+class _all_on_meta:
+    """A model built under ``init_empty_weights`` has its large weights on the meta device and the rest
+    (norm weights, rotary tables) in host memory; tracing needs one device.  For the duration of the
+    export every parameter and buffer is swapped for a meta stand-in (shared tensors share one),
+    then the original objects are put back, so identities, values and tied weights are untouched."""
+
+    def __init__(self, model: nn.Module):
+        self.model, self.saved = model, []
+
+    def __enter__(self):
+        stand_in = {}
+        for mod in self.model.modules():
+            for store in (mod._parameters, mod._buffers):
+                for name, t in list(store.items()):
+                    if t is None or t.is_meta:
+                        continue
+                    if id(t) not in stand_in:
+                        m = torch.empty_like(t, device="meta")
+                        stand_in[id(t)] = nn.Parameter(m, requires_grad=t.requires_grad) if isinstance(t, nn.Parameter) else m
+                    self.saved.append((store, name, t))
+                    store[name] = stand_in[id(t)]
+        return self
+
+    def __exit__(self, *exc):
+        for store, name, t in self.saved:
+            store[name] = t
+        return False
+
+
 def export_flat(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor], dynamic_batch: bool = True) -> fx.GraphModule:
     """Flat ATen graph over the model's own attributes; placeholders are named like the inputs."""
     from ..parallel import fused_tp
@@ -89,9 +140,12 @@ def export_flat(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor], dynamic
     names = list(dummy_inputs)
     wrapper = _TensorInputsOnly(model, names, _constant_kwargs(model, names))
     args = tuple(dummy_inputs[n] for n in names)
+    on_meta = any(p.is_meta for p in model.parameters())
+    if on_meta:
+        args = tuple(t.to("meta") for t in args)
     fused_saved, fused_tp.ENABLED = fused_tp.ENABLED, False
     try:
-        with shape_only_collectives():
+        with shape_only_collectives(), _no_layerdrop(), (_all_on_meta(model) if on_meta else contextlib.nullcontext()):
             ep = None
             if dynamic_batch and all(t.dim() >= 1 and t.shape[0] == args[0].shape[0] and t.shape[0] > 1 for t in args):
                 try:
@@ -135,15 +189,43 @@ def export_flat(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor], dynamic
             new = graph.node_copy(node, lambda a: env[a])
         new.meta = dict(node.meta)
         env[node] = new
-    # run-time assertions on dtypes / devices / shape guards carry no data
-    for node in list(graph.nodes):
-        if node.op == "call_function" and "_assert" in str(node.target) and not node.users:
-            graph.erase_node(node)
+    _clean_graph(graph, on_meta)
+    for name, sub in list(model.named_children()):
+        if name.startswith("_exported_attr_") and isinstance(sub, fx.GraphModule):     # bodies of higher-order ops
+            _clean_graph(sub.graph, on_meta)
+            sub.recompile()
     gm = fx.GraphModule(model, graph, class_name=type(model).__name__)
     gm.graph.eliminate_dead_code()
     gm.recompile()
     gm.exported_dynamic_batch = bool(ep.range_constraints)
     return gm
+
+
+def _clean_graph(graph: fx.Graph, devices_are_placeholders: bool):
+    """Drops run-time assertions (dtype / device / shape guards carry no data).  A graph exported on the
+    meta device has ``device=meta`` baked into its tensor factories and copies; those arguments are
+    rewired to the device of the graph's first tensor input, whatever that is at run time (the
+    reference rewrites device arguments of exported graphs too,
+    Merak/core/fx/graph_shard/split_module.py:200-204)."""
+    for node in list(graph.nodes):
+        if node.op == "call_function" and "_assert" in str(node.target) and not node.users:
+            graph.erase_node(node)
+    if not devices_are_placeholders:
+        return
+    first = next((n for n in graph.nodes if n.op == "placeholder"), None)
+    dev_node = None
+    for node in list(graph.nodes):
+        if node.op != "call_function":
+            continue
+        is_meta = lambda a: isinstance(a, torch.device) and a.type == "meta"
+        if first is None or not (any(is_meta(a) for a in node.args) or any(is_meta(v) for v in node.kwargs.values())):
+            continue
+        if dev_node is None:
+            last_ph = [n for n in graph.nodes if n.op == "placeholder"][-1]
+            with graph.inserting_after(last_ph):
+                dev_node = graph.call_function(getattr, (first, "device"))
+        node.args = tuple(dev_node if is_meta(a) else a for a in node.args)
+        node.kwargs = {k: (dev_node if is_meta(v) else v) for k, v in node.kwargs.items()}
 
 
 # ---------------------------------------------------------------------------------------------

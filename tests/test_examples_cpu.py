@@ -17,6 +17,11 @@ COMMON = ["--per_device_train_batch_size", "2", "--gradient_accumulation_steps",
                                          "--num_labels", "10", "--dataset_size", "32"]),
     ("unet/run_unet.py", ["--image_size", "32", "--width", "8", "--dataset_size", "32"]),
     ("lora/run_lora.py", ["--model_size", "llama-tiny", "--seq_length", "32", "--dataset_size", "32"]),
+    # Hugging Face model families through torch.export tracing (tiny random configurations)
+    ("models/albert/run_albert.py", ["--tiny", "1", "--dataset_size", "32"]),
+    ("models/opt/run_opt.py", ["--tiny", "1", "--dataset_size", "32"]),
+    ("models/bart/run_bart.py", ["--tiny", "1", "--dataset_size", "32"]),
+    ("models/resnet/run_resnet.py", ["--tiny", "1", "--dataset_size", "32"]),
 ])
 def test_example_runs(tmp_path, script, extra):
     cmd = [sys.executable, os.path.join(ROOT, "examples", script), "--output_dir", str(tmp_path)] + extra + COMMON
