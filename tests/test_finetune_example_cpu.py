@@ -49,7 +49,7 @@ def test_lora_sft_from_hf_safetensors_pp2(tmp_path):
     assert abs(losses[0] - math.log(256)) < 2e-3, losses          # base weights came from the safetensors file
     assert all(math.isfinite(l) for l in losses)    # (adapter learning itself: tests/test_examples_cpu.py, run_lora)
     ckpt = [os.path.join(d, f) for d, _, fs in os.walk(out_dir) for f in fs]
-    lora_files = [f for f in ckpt if f.endswith("lora_model_optim.pt")]
+    lora_files = [f for f in ckpt if f.endswith("lora_partial_model_optim.pt")]
     assert len(lora_files) == 2, ckpt                               # one adapter file per pipeline stage
     assert any(f.endswith("lora_config.json") for f in ckpt)
     sd = torch.load(lora_files[0], map_location="cpu", weights_only=False)["model"]
