@@ -34,6 +34,10 @@ int mrk_rope(const void* x, void* y, const float* cosb, const float* sinb, const
 int mrk_swiglu_fwd(const void* gu, void* out, long long M, int F, long long ld, void* stream);
 int mrk_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long M, int F, long long ld, void* stream);
 int mrk_colsum(const void* x, float* out, long long M, int N, long long ld, void* stream);
+// Next-token sampling (csrc/sampling.cu): temperature / top-k (1..1024) / top-p / draw for a batch of rows.
+int mrk_sample_topk_topp(const void* logits, int is_bf16, long long rows, int V, long long row_stride, int top_k,
+                         float top_p, float temperature, int greedy, const float* uniforms, unsigned long long seed,
+                         unsigned long long step, long long* out_token, float* out_prob, void* stream);
 int mrk_dropout(const void* x, void* y, long long n, float p, const void* rng, unsigned long long call_id, void* stream);
 int mrk_scaled_cast(const void* x, void* y, long long n, const float* scale_ptr, float scale, int in_f32, int out_f32,
                     int accumulate, void* stream);

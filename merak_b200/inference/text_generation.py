@@ -38,11 +38,32 @@ def top_k_top_p_filter(logits: torch.Tensor, top_k: int = 0, top_p: float = 0.0,
 
 
 def sample_next_token(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 0.0,
-                      greedy: bool = False, generator: Optional[torch.Generator] = None) -> torch.Tensor:
+                      greedy: bool = False, generator: Optional[torch.Generator] = None,
+                      uniforms: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Next token per row of ``logits`` ``[batch, vocab]``.  On CUDA with ``1 <= top_k <= 1024`` the whole
+    chain (temperature, top-k, top-p, softmax, draw) is one kernel launch (``csrc/sampling.cu``); other
+    settings and CPU tensors take the PyTorch formulation.  ``uniforms`` (one number in [0, 1) per row)
+    fixes the draw."""
     if greedy or temperature <= 0:
         return logits.argmax(-1)
+    if logits.is_cuda and 1 <= top_k <= 1024 and logits.dtype in (torch.float32, torch.bfloat16) and logits.dim() == 2:
+        from ..ops import _lib
+        x = logits if logits.stride(1) == 1 else logits.contiguous()
+        if uniforms is None:
+            uniforms = torch.rand(x.shape[0], device=x.device, generator=generator)
+        out = torch.empty(x.shape[0], dtype=torch.long, device=x.device)
+        _lib.check(_lib.kernels().mrk_sample_topk_topp(
+            x.data_ptr(), int(x.dtype == torch.bfloat16), x.shape[0], x.shape[1], x.stride(0), int(top_k), float(top_p),
+            float(temperature), 0, uniforms.float().contiguous().data_ptr(), 0, 0, out.data_ptr(), None,
+            _lib.stream_ptr()), "mrk_sample_topk_topp")
+        return out
     logits = top_k_top_p_filter(logits.float() / temperature, top_k, top_p)
-    return torch.multinomial(F.softmax(logits, dim=-1), 1, generator=generator).squeeze(-1)
+    probs = F.softmax(logits, dim=-1)
+    if uniforms is not None:             # inverse CDF over the descending order, like the kernel
+        sp, si = torch.sort(probs, descending=True, dim=-1, stable=True)
+        pick = (torch.cumsum(sp, -1) <= uniforms[:, None].to(sp.dtype)).sum(-1).clamp(max=probs.shape[-1] - 1)
+        return si.gather(-1, pick[:, None]).squeeze(-1)
+    return torch.multinomial(probs, 1, generator=generator).squeeze(-1)
 
 
 class text_generation_pipeline:

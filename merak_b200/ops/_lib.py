@@ -87,6 +87,8 @@ def _declare(lib):
     sig("mrk_dp_reduce_scatter", c_int, P, P, c_int, c_int, c_ll, c_ll, P, c_uint, c_int, c_int, P)
     sig("mrk_dp_adamw_allgather", c_int, P, P, c_int, c_int, c_ll, c_ll, P, P, P, P, P, P, c_float, c_float,
         P, P, P, c_uint, c_int, c_int, c_int, P)
+    sig("mrk_sample_topk_topp", c_int, P, c_int, c_ll, c_int, c_ll, c_int, c_float, c_float, c_int, P,
+        ctypes.c_ulonglong, ctypes.c_ulonglong, P, P, P)
     sig("mrk_memcpy_d2d_async", c_int, P, P, ctypes.c_ulonglong, P)
     sig("mrk_dp_norm_gather", c_int, P, c_int, c_int, P, c_uint, c_int, c_int, P)
     sig("mrk_tp_reduce_pull", c_int, P, P, c_int, c_int, P, c_ll, c_int, c_int, P, c_uint, c_int, c_int, P)
