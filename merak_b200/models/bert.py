@@ -71,6 +71,7 @@ class BertSelfAttention(nn.Module):
         self.num_attention_heads = config.num_attention_heads
         self.attention_head_size = config.hidden_size // config.num_attention_heads
         self.all_head_size = config.hidden_size
+        self.p_attn = float(config.attention_probs_dropout_prob or 0.0)
         self.qkv = Linear(config.hidden_size, 3 * config.hidden_size)
         self.qkv.fused_parts = 3
         expose_fused_projection(self, "qkv", ("query", "key", "value"))
@@ -87,7 +88,8 @@ class BertSelfAttention(nn.Module):
         local = qkv.shape[-1] // 3
         heads = local // self.attention_head_size
         qkv = qkv.view(B, L, 3 * heads, self.attention_head_size)
-        ctx = flash_attention_packed(qkv, heads, heads, key_bias=key_bias, causal=False)
+        ctx = flash_attention_packed(qkv, heads, heads, key_bias=key_bias, causal=False,
+                                     dropout_p=self.p_attn if self.training else 0.0)
         ctx = ctx.reshape(B, L, local)
         return (ctx, x_res) if fork else ctx
 

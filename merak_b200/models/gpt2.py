@@ -71,13 +71,15 @@ class GPT2Attention(nn.Module):
         self.c_proj = Linear(self.embed_dim, self.embed_dim)
         self.c_attn.tp_unit = self.c_proj.tp_unit = self.head_dim     # heads are never split between ranks
         self.resid_pdrop = config.resid_pdrop
+        self.attn_pdrop = float(config.attn_pdrop or 0.0)
 
     def forward(self, x, residual=None):
         qkv = self.c_attn(x)
         B, L = qkv.shape[0], qkv.shape[1]     # the projection may have gathered the sequence
         local = qkv.shape[-1] // 3
         heads = local // self.head_dim
-        ctx = flash_attention_packed(qkv.view(B, L, 3 * heads, self.head_dim), heads, heads, causal=True)
+        ctx = flash_attention_packed(qkv.view(B, L, 3 * heads, self.head_dim), heads, heads, causal=True,
+                                     dropout_p=self.attn_pdrop if self.training else 0.0)
         ctx = ctx.reshape(B, L, local)
         if residual is not None and not (self.training and self.resid_pdrop > 0):
             return self.c_proj(ctx, residual)

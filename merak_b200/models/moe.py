@@ -104,6 +104,8 @@ def _mla_attention(q, k, v, scale):
     until the kernel grows a split-key variant."""
     if q.shape[-1] == v.shape[-1] and q.shape[-1] in (64, 128):
         return flash_attention(q, k, v, causal=True, scale=scale)
+    from ..ops import _lib
+    _lib.note_library_fallback("attention with a 192-wide key", q)
     out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                                          scale=scale)
     return out.transpose(1, 2)

@@ -16,6 +16,7 @@ import math
 from typing import Optional
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib, flop_counter
 
@@ -40,6 +41,29 @@ def attention_reference(q, k, v, key_bias=None, causal=False, scale=None):
         s = s.masked_fill(~keep, float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p):
+    """Attention with dropout on the probabilities (the eager ``matmul -> softmax -> dropout -> matmul``
+    of the reference's models).  The flash kernels have no dropout, so this is PyTorch's
+    ``scaled_dot_product_attention`` (announced once through ``note_library_fallback`` on CUDA); tensors are
+    ``[B, L, H, D]`` as everywhere in this module."""
+    _lib.note_library_fallback("attention with dropout on the probabilities", q)
+    B, Lq, H, D = q.shape
+    Hkv = k.shape[2]
+    qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+    if Hkv != H:
+        kh = kh.repeat_interleave(H // Hkv, dim=1)
+        vh = vh.repeat_interleave(H // Hkv, dim=1)
+    mask = None
+    if key_bias is not None:
+        mask = key_bias.to(q.dtype)[:, None, None, :].expand(B, 1, Lq, k.shape[1])
+        if causal:
+            keep = torch.ones(Lq, k.shape[1], dtype=torch.bool, device=q.device).tril(k.shape[1] - Lq)
+            mask = mask.masked_fill(~keep, float("-inf"))
+    out = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, dropout_p=float(dropout_p),
+                                         is_causal=bool(causal and mask is None), scale=scale)
+    return out.permute(0, 2, 1, 3)
 
 
 def _strides3(t):
@@ -145,10 +169,15 @@ class _FlashAttentionPacked(torch.autograd.Function):
 
 def flash_attention_packed(qkv: torch.Tensor, num_q_heads: int, num_kv_heads: int,
                            key_bias: Optional[torch.Tensor] = None, causal: bool = False,
-                           scale: Optional[float] = None) -> torch.Tensor:
-    """Self-attention on ``qkv`` of shape ``[B, L, Hq + 2*Hkv, D]``; returns ``[B, L, Hq, D]``."""
+                           scale: Optional[float] = None, dropout_p: float = 0.0) -> torch.Tensor:
+    """Self-attention on ``qkv`` of shape ``[B, L, Hq + 2*Hkv, D]``; returns ``[B, L, Hq, D]``.
+    ``dropout_p`` > 0 (pass it in training mode only) drops attention probabilities."""
     D = qkv.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if dropout_p > 0.0:
+        q, k, v = (qkv[:, :, :num_q_heads], qkv[:, :, num_q_heads:num_q_heads + num_kv_heads],
+                   qkv[:, :, num_q_heads + num_kv_heads:])
+        return attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p)
     if not _lib.use_kernels(qkv) or qkv.dtype != torch.bfloat16 or D not in (64, 128):
         _lib.note_library_fallback("attention", qkv)
         q, k, v = (qkv[:, :, :num_q_heads], qkv[:, :, num_q_heads:num_q_heads + num_kv_heads],
@@ -161,7 +190,7 @@ def flash_attention_packed(qkv: torch.Tensor, num_q_heads: int, num_kv_heads: in
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                     key_bias: Optional[torch.Tensor] = None, causal: bool = False,
-                    scale: Optional[float] = None) -> torch.Tensor:
+                    scale: Optional[float] = None, dropout_p: float = 0.0) -> torch.Tensor:
     """``softmax(scale * q k^T + key_bias + causal mask) v``.
 
     q ``[B, Lq, H, D]``; k, v ``[B, Lk, Hkv, D]`` with ``H % Hkv == 0`` (grouped-query attention);
@@ -169,6 +198,8 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     """
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if dropout_p > 0.0:
+        return attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p)
     if not _lib.use_kernels(q, k, v):
         return attention_reference(q, k, v, key_bias, causal, scale)
     if flop_counter.enabled():

@@ -70,7 +70,8 @@ def main():
                                             **over))
         task = "causal"
     elif o.model == "bert":
-        model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=0.0))
+        model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=0.0,
+                                            attention_probs_dropout_prob=0.0))
         task = "mlm"
     elif o.model == "moe":
         from merak_b200.models.moe import DeepseekV2ForCausalLM, deepseek_v2_config
