@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--cuda-graph", type=int, default=1)
     ap.add_argument("--dp-overlap", type=int, default=1, help="reduce gradients while the backward pass runs")
+    ap.add_argument("--check", action="store_true",
+                    help="before timing, train 5 steps from the same seed with --comm as given and with NCCL "
+                         "collectives and require the two loss curves to agree")
     return ap.parse_args()
 
 
@@ -103,14 +106,17 @@ class ClockSampler:
         return out
 
 
-def build_ours(o, device):
+def build_ours(o, device, comm=None):
     import torch
 
     import merak_b200 as Merak
     from merak_b200.models.bert import BertForMaskedLM, bert_config
     from merak_b200.utils.datasets import SyntheticTokenDataset
 
-    Merak.init(pp=1, tp=1, dp=o.gpus)
+    comm = comm or o.comm
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        Merak.init(pp=1, tp=1, dp=o.gpus)
     torch.manual_seed(0)
     cfg = bert_config(o.model, hidden_dropout_prob=o.dropout, attention_probs_dropout_prob=0.0)
     model = BertForMaskedLM(cfg)
@@ -119,7 +125,7 @@ def build_ours(o, device):
         per_device_train_batch_size=o.mbs, gradient_accumulation_steps=1, max_steps=10 ** 9,
         learning_rate=1e-4, weight_decay=0.01, max_grad_norm=1.0, lr_scheduler_type="constant",
         logging_steps=0, wall_clock_breakdown=False, report_to="none", activation_checkpointing=False,
-        split_method="layer_split", comm_mode=o.comm, cuda_graph=bool(o.cuda_graph), seed=0,
+        split_method="layer_split", comm_mode=comm, cuda_graph=bool(o.cuda_graph), seed=0,
         overlap_dp_reduce=bool(o.dp_overlap))
     ds = SyntheticTokenDataset(cfg.vocab_size, o.seq, 1 << 20, task="mlm", seed=0)
     trainer = Merak.MerakTrainer(model, args, train_dataset=ds)
@@ -153,6 +159,21 @@ def run_ours(o):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    check = None
+    if o.check:
+        # the same five steps from the same seed through both communication back ends
+        curves = {}
+        for comm in dict.fromkeys([o.comm, "nccl"]):
+            cfg, trainer, engine = build_ours(o, device, comm=comm)
+            it = iter(make_batches(cfg, o, 5, device, pinned=False))
+            curves[comm] = [float(engine.train_batch(it)) for _ in range(5)]
+            del trainer, engine, it
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        a, b = curves[o.comm], curves["nccl"]
+        worst = max(abs(x - y) / max(1.0, abs(y)) for x, y in zip(a, b))
+        check = {"steps": 5, "losses": a, "losses_nccl": b, "max_rel_diff": worst, "tolerance": 2e-3}
+        assert worst < 2e-3, "loss curves differ between comm=%s and comm=nccl: %s vs %s" % (o.comm, a, b)
     cfg, trainer, engine = build_ours(o, device)
     rank = dist.get_rank()
     world = dist.get_world_size()
@@ -170,10 +191,12 @@ def run_ours(o):
         torch.cuda.synchronize()
 
     def timed(data_iter, read_loss: bool):
+        loss = None
         for _ in range(o.warmup):
             loss = engine.train_batch(data_iter)
             if read_loss:
                 float(loss)
+        after_warmup = float(loss) if loss is not None else None
         sync_all()
         launches0 = _lib.launch_count()
         sampler = ClockSampler(local)
@@ -194,14 +217,14 @@ def run_ours(o):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         launches = _lib.launch_count() - launches0 + getattr(engine, "graph_replay_launches", 0)
         engine.graph_replay_launches = 0
-        return float(t.item()), clocks, launches, float(last)
+        return float(t.item()), clocks, launches, float(last), after_warmup
 
     # device-timed: batches already on the device
     dev_iter = cycle(make_batches(cfg, o, n_distinct, device, pinned=False))
-    ms_dev, clocks, launches, loss_dev = timed(dev_iter, read_loss=False)
+    ms_dev, clocks, launches, loss_dev, loss_warm = timed(dev_iter, read_loss=False)
     # end to end: pinned host batches copied every step, loss read back every step
     host_batches = make_batches(cfg, o, n_distinct, device, pinned=True)
-    ms_e2e, _, _, loss_e2e = timed(cycle(host_batches), read_loss=True)
+    ms_e2e, _, _, loss_e2e, _ = timed(cycle(host_batches), read_loss=True)
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
 
     tokens = o.mbs * o.seq * world * o.steps
@@ -224,7 +247,8 @@ def run_ours(o):
             "clocks": clocks, "gpu_launches": int(launches),
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / o.steps,
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4},
-            "final_loss": loss_e2e, "device_status_word": status,
+            "loss_after_warmup": loss_warm, "final_loss": loss_e2e, "device_status_word": status,
+            **({"check": check} if check is not None else {}),
         }), flush=True)
     sync_all()
     import merak_b200.initialize as ini

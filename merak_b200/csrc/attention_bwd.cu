@@ -4,19 +4,31 @@
 //
 //   S^T  = K Q^T          P^T  = exp2(S^T * scale - lse)
 //   dP^T = V dO^T         dS^T = P^T o (dP^T - delta) * scale
-//   dV  += P^T dO         dK  += dS^T Q            dQ += dS K     (dQ through fp32 red.add)
+//   dV  += P^T dO         dK  += dS^T Q            dQ += dS K     (dQ partials are added into an fp32 buffer)
 //
 // All five run on the tensor core with TMEM accumulators: S^T, dP^T (consumed by the compute
 // warps one key row per thread), dK and dV (resident for the whole CTA), and a dQ partial that is
-// drained to global memory with vector reductions.  P^T and dS^T are written to shared memory once
+// added to global memory: head dim 64 stages the [128 q][64] tile in shared memory and hands it to
+// the TMA unit as two bulk tensor reductions (whole 128-byte lines per request; a thread holds one
+// row, so direct vector reductions touch 32 different lines per warp instruction), head dim 128
+// has no shared memory left for that and issues the vector reductions.  P^T and dS^T are written to shared memory once
 // and serve as the K-major A operand of dV/dK and as the MN-major A operand of dQ; the Q and dO
 // tiles likewise serve as K-major B of the first two products and MN-major B of dK/dV.
 //
 //   warp 0       TMA producer           warp 1   UMMA issuer
 //   warps 2..9   compute: two warpgroups, each handles 64 of the 128 query columns of every row.
+//
+// Head dim 64 runs as a software pipeline over the query blocks.  A compute thread copies its 64
+// S^T and 64 dP^T values into registers and releases those TMEM columns at once, so the tensor core
+// computes S^T / dP^T of block i+1 while the CUDA cores work on block i; the P^T / dS^T stores of
+// block i wait for the dV / dK / dQ products of block i-1 (which read the same shared memory), and
+// the dQ partial of block i-1 (double buffered in TMEM) is drained while those products of block i
+// run.  Head dim 128 fills all 512 TMEM columns (the dQ partial reuses the S^T columns), so it keeps
+// the plain order: products, element-wise step, products, drain.
 #include "attention.h"
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include <type_traits>
 
 namespace mrk {
 
@@ -51,7 +63,8 @@ struct AttnBwdSmem {
   static constexpr int kDSOff = kPOff + 32768;                   // dS^T
   static constexpr int kStatOff = kDSOff + 32768;                // lse2 / delta, double buffered
   static constexpr int kBarOff = kStatOff + 2 * 2 * 128 * 4;
-  static constexpr int kTotal = kBarOff + 256 + 1024;
+  static constexpr int kDQStageOff = kBarOff + 1024;             // D=64: two [128 q][32] fp32 tiles (one per warpgroup)
+  static constexpr int kTotal = kDQStageOff + (D == 64 ? 2 * 16384 : 0) + 1024;
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -67,12 +80,12 @@ template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tdq, const AttnBwdParams p) {
   using L = AttnBwdSmem<D>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kSCol = 0, kDPCol = 128, kDKCol = 256, kDVCol = 256 + D;
-  constexpr uint32_t kDQCol = (D == 64) ? 384 : 0;   // D=128: the dQ partial reuses the S^T columns
+  constexpr uint32_t kDQCol = (D == 64) ? 384 : 0;   // D=64: two buffers of 64 columns; D=128: reuses the S^T columns
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -84,9 +97,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint64_t* sp_full = qdo_empty + kStages;     // 1
   uint64_t* pds_full = sp_full + 1;            // 1 (256 arrivals)
   uint64_t* dq_full = pds_full + 1;            // 1
-  uint64_t* dq_empty = dq_full + 1;            // 1 (256 arrivals)
-  uint64_t* dkv_full = dq_empty + 1;           // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
+  uint64_t* dq_empty = dq_full + 1;            // 2 (256 arrivals), one per dQ buffer
+  uint64_t* dkv_full = dq_empty + 2;           // 1
+  uint64_t* sdp_free = dkv_full + 1;           // 1 (256 arrivals): S^T and dP^T are in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stat = reinterpret_cast<float*>(smem + L::kStatOff);  // [2 buffers][lse2[128] | delta[128]]
 
@@ -114,13 +128,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     mbar_init(smem_u32(sp_full), 1);
     mbar_init(smem_u32(pds_full), 256);
     mbar_init(smem_u32(dq_full), 1);
-    mbar_init(smem_u32(dq_empty), 256);
+    mbar_init(smem_u32(&dq_empty[0]), 256);
+    mbar_init(smem_u32(&dq_empty[1]), 256);
     mbar_init(smem_u32(dkv_full), 1);
+    mbar_init(smem_u32(sdp_free), 256);
     fence_mbar_init();
     tma_prefetch_desc(&tq);
     tma_prefetch_desc(&tk);
     tma_prefetch_desc(&tv);
     tma_prefetch_desc(&tdo);
+    tma_prefetch_desc(&tdq);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -165,17 +182,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t idesc_dkv = make_idesc_bf16(128, D, 0, 1);
       const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);
       bool ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, p.status);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int it = 0; it < total_iters && ok; ++it) {
-        ok = mbar_wait(smem_u32(&qdo_full[stage]), phase, abort_flag, p.status);
-        if (!ok) break;
-        if (D == 128 && it > 0) {
-          ok = mbar_wait(smem_u32(dq_empty), (it - 1) & 1, abort_flag, p.status);
-          if (!ok) break;
-        }
-        tc_fence_after();
-        const uint32_t qs = smem_u32(smem + L::kStageOff + stage * 2 * L::kTile);
+      // S^T = K Q^T and dP^T = V dO^T of the query block in ring stage `st`
+      auto issue_scores = [&](int st) {
+        const uint32_t qs = smem_u32(smem + L::kStageOff + st * 2 * L::kTile);
         const uint32_t dos = qs + L::kTile;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
@@ -186,29 +195,77 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           umma_bf16_ss(tmem_base + kDPCol, desc_kmajor(v_smem + (k / 4) * 16384, k % 4),
                        desc_kmajor(dos + (k / 4) * 16384, k % 4), idesc_s, k != 0 ? 1u : 0u);
         umma_commit(smem_u32(sp_full));
-        ok = mbar_wait(smem_u32(pds_full), it & 1, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
+      };
+      // dV += P^T dO, dK += dS^T Q (contraction over the 128 queries of the block)
+      auto issue_dkv = [&](int st, int it) {
+        const uint32_t qs = smem_u32(smem + L::kStageOff + st * 2 * L::kTile);
+        const uint32_t dos = qs + L::kTile;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)   // contraction over the 128 queries of this block
+        for (int k = 0; k < 8; ++k)
           umma_bf16_ss(tmem_base + kDVCol, desc_kmajor(p_smem + (k / 4) * 16384, k % 4),
                        desc_mnmajor(dos, k, 128), idesc_dkv, (it | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16_ss(tmem_base + kDKCol, desc_kmajor(ds_smem + (k / 4) * 16384, k % 4),
                        desc_mnmajor(qs, k, 128), idesc_dkv, (it | k) != 0 ? 1u : 0u);
-        if (D == 64 && it > 0) {
-          ok = mbar_wait(smem_u32(dq_empty), (it - 1) & 1, abort_flag, p.status);
+      };
+      // dQ partial = dS K (contraction over the 128 keys of this CTA)
+      auto issue_dq = [&](uint32_t col) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(tmem_base + col, desc_mnmajor(ds_smem, k, 128), desc_mnmajor(k_smem, k, 128),
+                       idesc_dq, k != 0 ? 1u : 0u);
+      };
+      if constexpr (D == 64) {
+        // stage of block `it` is it % 2 (kStages == 2); its full-barrier phase is (it / 2) & 1
+        if (ok) ok = mbar_wait(smem_u32(&qdo_full[0]), 0, abort_flag, p.status);
+        if (ok) {
+          tc_fence_after();
+          issue_scores(0);
+        }
+        for (int it = 0; it < total_iters && ok; ++it) {
+          const int stage = it & 1;
+          if (it + 1 < total_iters) {
+            ok = mbar_wait(smem_u32(&qdo_full[stage ^ 1]), ((it + 1) >> 1) & 1, abort_flag, p.status) &&
+                 mbar_wait(smem_u32(sdp_free), it & 1, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            issue_scores(stage ^ 1);
+          }
+          ok = mbar_wait(smem_u32(pds_full), it & 1, abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
+          issue_dkv(stage, it);
+          if (it >= 2) {   // the drain of the partial that used this dQ buffer two blocks ago
+            ok = mbar_wait(smem_u32(&dq_empty[it & 1]), ((it >> 1) - 1) & 1, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_dq(kDQCol + (it & 1) * 64);
+          umma_commit(smem_u32(&qdo_empty[stage]));
+          umma_commit(smem_u32(dq_full));
         }
-#pragma unroll
-        for (int k = 0; k < 8; ++k)   // contraction over the 128 keys of this CTA
-          umma_bf16_ss(tmem_base + kDQCol, desc_mnmajor(ds_smem, k, 128), desc_mnmajor(k_smem, k, 128),
-                       idesc_dq, k != 0 ? 1u : 0u);
-        umma_commit(smem_u32(&qdo_empty[stage]));
-        umma_commit(smem_u32(dq_full));
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      } else {
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int it = 0; it < total_iters && ok; ++it) {
+          ok = mbar_wait(smem_u32(&qdo_full[stage]), phase, abort_flag, p.status);
+          if (!ok) break;
+          if (it > 0) {   // the dQ partial shares the S^T columns
+            ok = mbar_wait(smem_u32(&dq_empty[0]), (it - 1) & 1, abort_flag, p.status);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          issue_scores(stage);
+          ok = mbar_wait(smem_u32(pds_full), it & 1, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dkv(stage, it);
+          issue_dq(kDQCol);
+          umma_commit(smem_u32(&qdo_empty[stage]));
+          umma_commit(smem_u32(dq_full));
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
       }
       if (ok) umma_commit(smem_u32(dkv_full));
     }
@@ -223,98 +280,184 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int tid_c = threadIdx.x - 64;      // 0..255
     const float kbias = (p.key_bias && key < p.Lk) ? p.key_bias[(long long)b * p.Lk + key] * 1.4426950408889634f : 0.f;
     bool ok = true;
-    for (int it = 0; it < total_iters && ok; ++it) {
+
+    // lse (log2 units) for threads 0..127, delta * scale for threads 128..255, of query block `it`
+    auto load_stat = [&](int it) -> float {
       const int h = hkv * group + it / iters_per_head;
-      const int j = j_begin + it % iters_per_head;
-      const int q0 = j * 128;
-      float* st = stat + (it & 1) * 256;
-      {
-        // stage lse (in log2 units) and delta of this query block
-        const int q = q0 + (tid_c & 127);
-        const long long off = ((long long)b * p.H + h) * p.Lq + q;
-        if (tid_c < 128) st[tid_c] = q < p.Lq ? p.lse[off] * 1.4426950408889634f : INFINITY;
-        else             st[tid_c] = q < p.Lq ? p.delta[off] : 0.f;
+      const int q = (j_begin + it % iters_per_head) * 128 + (tid_c & 127);
+      const long long off = ((long long)b * p.H + h) * p.Lq + q;
+      if (tid_c < 128) return q < p.Lq ? __ldg(p.lse + off) * 1.4426950408889634f : INFINITY;
+      return q < p.Lq ? __ldg(p.delta + off) * p.scale : 0.f;
+    };
+    // P^T and dS^T of 32 query columns (col0 .. col0+31 of the block) of this thread's key row
+    // (`masked` is a compile-time tag: a per-element branch would end the basic block at every
+    // element and leave each exp2 -> multiply -> pack chain exposed at its full latency)
+    auto chunk = [&](auto masked, const uint32_t* s, const uint32_t* dp, const float* st, int col0, int q0,
+                     uint32_t* pk, uint32_t* dsk) {
+#pragma unroll
+      for (int i8 = 0; i8 < 32; i8 += 8) {
+        // the per-query statistics are the same for every lane: 16-byte broadcast loads, 8 columns at a time
+        const float4 l0 = *reinterpret_cast<const float4*>(st + col0 + i8);
+        const float4 l1 = *reinterpret_cast<const float4*>(st + col0 + i8 + 4);
+        const float4 d0 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8);
+        const float4 d1 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8 + 4);
+        const float lse8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float dl8[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          float pv[2], dv_[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = i8 + j + e;
+            const float x = fmaf(__uint_as_float(s[i]), p.scale_log2, kbias - lse8[j + e]);
+            float pe = exp2f(x);
+            if constexpr (decltype(masked)::value) {
+              const int q = q0 + col0 + i;
+              if (key >= p.Lk || (p.causal && key > q + shift)) pe = 0.f;
+            }
+            pv[e] = pe;
+            dv_[e] = pe * fmaf(__uint_as_float(dp[i]), p.scale, -dl8[j + e]);   // delta was staged times scale
+          }
+          pk[(i8 + j) >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dsk[(i8 + j) >> 1] = pack_bf16x2(dv_[0], dv_[1]);
+        }
       }
+    };
+    // 32 columns of P^T / dS^T -> atom (col0/64), 16-byte chunks ((col0%64)/8)..+3 of row r
+    auto store_chunk = [&](int col0, const uint32_t* pk, const uint32_t* dsk) {
+      const uint32_t atom = (uint32_t)(col0 >> 6), ch0 = (uint32_t)((col0 & 63) >> 3);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint32_t off = atom * 16384 + sw128_offset((uint32_t)r, ch0 + q4);
+        *reinterpret_cast<uint4*>(smem + L::kPOff + off) =
+            make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        *reinterpret_cast<uint4*>(smem + L::kDSOff + off) =
+            make_uint4(dsk[4 * q4], dsk[4 * q4 + 1], dsk[4 * q4 + 2], dsk[4 * q4 + 3]);
+      }
+    };
+    // dQ partial of query block `it` (TMEM columns `col`) -> fp32 accumulator in global memory
+    auto drain_dq = [&](int it, uint32_t col) {
+      const int h = hkv * group + it / iters_per_head;
+      const int q = (j_begin + it % iters_per_head) * 128 + r;
+      float* dst = p.dq_acc + (((long long)b * p.Lq + q) * p.H + h) * D + wg * (D / 2);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_off + col + wg * (D / 2) + c * 32, v);
+        tmem_wait_ld();
+        if (q < p.Lq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(dst + c * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                       __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));   // dS already carries the scale
+        }
+      }
+    };
+
+    // head dim 64: dQ partial of query block `it` -> shared memory -> bulk tensor reduction.  Each
+    // warpgroup owns 32 of the 64 columns and one staging tile.
+    uint8_t* dq_stage = smem + L::kDQStageOff + wg * 16384;
+    const bool dq_leader = (tid_c & 127) == 0;
+    auto drain_dq_tma = [&](int it) {
+      const int h = hkv * group + it / iters_per_head;
+      const int q0 = (j_begin + it % iters_per_head) * 128;
+      uint32_t v[32];
+      tmem_ld32(tmem_base + lane_off + kDQCol + (it & 1) * 64 + wg * 32, v);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&dq_empty[it & 1]));
+      if (dq_leader) tma_store_wait_read<0>();      // the previous reduction has read the staging tile
+      named_bar_sync(2 + wg, 128);
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4)
+        *reinterpret_cast<uint4*>(dq_stage + sw128_offset((uint32_t)r, (uint32_t)q4)) =
+            make_uint4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+      fence_proxy_async_smem();
+      named_bar_sync(2 + wg, 128);
+      if (dq_leader) {   // rows past Lq fall outside the tensor map and are dropped
+        tma_reduce_add_4d(&tdq, smem_u32(dq_stage), wg * 32, h, q0, b);
+        tma_store_commit();
+      }
+    };
+
+    float stat_next = total_iters > 0 ? load_stat(0) : 0.f;
+    for (int it = 0; it < total_iters && ok; ++it) {
+      const int q0 = (j_begin + it % iters_per_head) * 128;
+      float* st = stat + (it & 1) * 256;
+      st[tid_c] = stat_next;
+      if (it + 1 < total_iters) stat_next = load_stat(it + 1);   // in flight during this block's work
       compute_bar_sync();
       ok = mbar_wait(smem_u32(sp_full), it & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = (key >= p.Lk) || (p.causal && (k0 + 127 > q0 + shift));
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = wg * 64 + c * 32;
-        uint32_t s[32], dp[32];
-        tmem_ld32(tmem_base + lane_off + kSCol + col0, s);
-        tmem_ld32(tmem_base + lane_off + kDPCol + col0, dp);
+      if constexpr (D == 64) {
+        // two halves of 32 columns: the second half's TMEM loads are in flight while the first half
+        // is stored, and the element-wise step never holds more than 64 inputs in registers
+        const int col0 = wg * 64;
+        uint32_t sa[32], da[32], sb[32], db[32];
+        tmem_ld32(tmem_base + lane_off + kSCol + col0, sa);
+        tmem_ld32(tmem_base + lane_off + kDPCol + col0, da);
         tmem_wait_ld();
         uint32_t pk[16], dsk[16];
-#pragma unroll
-        for (int i8 = 0; i8 < 32; i8 += 8) {
-          // the per-query statistics are the same for every lane: 16-byte broadcast loads, 8 columns at a time
-          const float4 l0 = *reinterpret_cast<const float4*>(st + col0 + i8);
-          const float4 l1 = *reinterpret_cast<const float4*>(st + col0 + i8 + 4);
-          const float4 d0 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8);
-          const float4 d1 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8 + 4);
-          const float lse8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-          const float dl8[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-#pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            float pv[2], dv_[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int i = i8 + j + e;
-              const float x = fmaf(__uint_as_float(s[i]), p.scale_log2, kbias - lse8[j + e]);
-              float pe = exp2f(x);
-              if (need_mask) {
-                const int q = q0 + col0 + i;
-                if (key >= p.Lk || (p.causal && key > q + shift)) pe = 0.f;
-              }
-              pv[e] = pe;
-              dv_[e] = pe * (__uint_as_float(dp[i]) - dl8[j + e]) * p.scale;
-            }
-            pk[(i8 + j) >> 1] = pack_bf16x2(pv[0], pv[1]);
-            dsk[(i8 + j) >> 1] = pack_bf16x2(dv_[0], dv_[1]);
-          }
+        if (need_mask) chunk(std::true_type{}, sa, da, st, col0, q0, pk, dsk);
+        else chunk(std::false_type{}, sa, da, st, col0, q0, pk, dsk);
+        tmem_ld32(tmem_base + lane_off + kSCol + col0 + 32, sb);
+        tmem_ld32(tmem_base + lane_off + kDPCol + col0 + 32, db);
+        if (it > 0) {   // the products of the previous block have read P^T / dS^T; its dQ partial is ready
+          ok = mbar_wait(smem_u32(dq_full), (it - 1) & 1, abort_flag, p.status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) { tmem_wait_ld(); break; }
         }
-        // columns col0..col0+31 -> atom (col0/64), 16-byte chunks ((col0%64)/8)..+3 of row r
-        const uint32_t atom = (uint32_t)(col0 >> 6), ch0 = (uint32_t)((col0 & 63) >> 3);
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t off = atom * 16384 + sw128_offset((uint32_t)r, ch0 + q4);
-          *reinterpret_cast<uint4*>(smem + L::kPOff + off) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-          *reinterpret_cast<uint4*>(smem + L::kDSOff + off) =
-              make_uint4(dsk[4 * q4], dsk[4 * q4 + 1], dsk[4 * q4 + 2], dsk[4 * q4 + 3]);
+        store_chunk(col0, pk, dsk);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(sdp_free));       // the tensor core may overwrite S^T / dP^T now
+        if (need_mask) chunk(std::true_type{}, sb, db, st, col0 + 32, q0, pk, dsk);
+        else chunk(std::false_type{}, sb, db, st, col0 + 32, q0, pk, dsk);
+        store_chunk(col0 + 32, pk, dsk);
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(pds_full));
+        if (it > 0) {
+          tc_fence_after();
+          drain_dq_tma(it - 1);
         }
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(pds_full));
-      // drain the dQ partial of this (key block, query block)
-      ok = mbar_wait(smem_u32(dq_full), it & 1, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        const int q = q0 + r;
-        float* dst = p.dq_acc + (((long long)b * p.Lq + q) * p.H + h) * D + wg * (D / 2);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + lane_off + kDQCol + wg * (D / 2) + c * 32, v);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = wg * 64 + c * 32;
+          uint32_t s[32], dp[32];
+          tmem_ld32(tmem_base + lane_off + kSCol + col0, s);
+          tmem_ld32(tmem_base + lane_off + kDPCol + col0, dp);
           tmem_wait_ld();
-          if (q < p.Lq) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              red_add_v4(dst + c * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
-                         __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));   // dS already carries the scale
-          }
+          uint32_t pk[16], dsk[16];
+          if (need_mask) chunk(std::true_type{}, s, dp, st, col0, q0, pk, dsk);
+          else chunk(std::false_type{}, s, dp, st, col0, q0, pk, dsk);
+          store_chunk(col0, pk, dsk);
         }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(pds_full));
+        ok = mbar_wait(smem_u32(dq_full), it & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        drain_dq(it, kDQCol);
+        tc_fence_before();
+        mbar_arrive(smem_u32(&dq_empty[0]));
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(dq_empty));
     }
+    if (D == 64 && total_iters > 0 && ok) {   // the last block's dQ partial
+      ok = mbar_wait(smem_u32(dq_full), (total_iters - 1) & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        drain_dq_tma(total_iters - 1);
+      }
+    }
+    if (D == 64 && dq_leader) tma_store_wait_read<0>();   // shared memory stays valid until the last reduction has read it
     // dK, dV of this key block
     if (total_iters > 0 && ok) {
       ok = mbar_wait(smem_u32(dkv_full), 0, abort_flag, p.status);
@@ -425,7 +568,7 @@ __global__ void attn_bwd_dq_cast_kernel(const float* __restrict__ acc, __nv_bflo
 
 template <int D>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                      const AttnBwdParams& p, cudaStream_t stream) {
+                      const CUtensorMap& tdq, const AttnBwdParams& p, cudaStream_t stream) {
   using L = AttnBwdSmem<D>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -435,7 +578,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     configured[dev & 63] = true;
   }
   dim3 grid((p.Lk + 127) / 128, p.Hkv, p.B);
-  attn_bwd_kernel<D><<<grid, kBwdThreads, L::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<D><<<grid, kBwdThreads, L::kTotal, stream>>>(tq, tk, tv, tdo, tdq, p);
   MRK_CHECK_LAUNCH();
   return 0;
 }
@@ -460,6 +603,13 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
   if ((rc = make_bshd_tmap(&tk, k, D, Lk, Hkv, B, sk[0], sk[1], sk[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tv, v, D, Lk, Hkv, B, sv[0], sv[1], sv[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tdo, dout, D, Lq, H, B, sdo[0], sdo[1], sdo[2], 128))) return rc;
+  CUtensorMap tdq;   // the fp32 dQ accumulator [B, Lq, H, D]: boxes of 128 queries x 32 columns of one head
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)Lq, (uint64_t)B};
+    const uint64_t strides[3] = {(uint64_t)D, (uint64_t)H * D, (uint64_t)Lq * H * D};
+    const uint32_t box[4] = {32, 1, 128, 1};
+    if ((rc = make_tmap_4d(&tdq, dq_acc, 4, dims, strides, box, 3))) return rc;
+  }
   const long long rows = (long long)B * Lq * H;
   {
     const int warps_per_block = 8;
@@ -485,7 +635,7 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "attention backward: status word unavailable");
-  rc = (D == 64) ? launch_bwd<64>(tq, tk, tv, tdo, p, s) : launch_bwd<128>(tq, tk, tv, tdo, p, s);
+  rc = (D == 64) ? launch_bwd<64>(tq, tk, tv, tdo, tdq, p, s) : launch_bwd<128>(tq, tk, tv, tdo, tdq, p, s);
   if (rc) return rc;
   {
     const long long total_vec = rows * (D / 8);
