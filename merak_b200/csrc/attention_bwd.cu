@@ -61,10 +61,10 @@ struct AttnBwdSmem {
   static constexpr int kStageOff = 2 * kTile;                    // [Q_j | dO_j] per stage
   static constexpr int kPOff = kStageOff + kStages * 2 * kTile;  // P^T   [128 kv][128 q] bf16
   static constexpr int kDSOff = kPOff + 32768;                   // dS^T
-  static constexpr int kStatOff = kDSOff + 32768;                // lse2 / delta, double buffered
-  static constexpr int kBarOff = kStatOff + 2 * 2 * 128 * 4;
-  static constexpr int kDQStageOff = kBarOff + 1024;             // D=64: two [128 q][32] fp32 tiles (one per warpgroup)
-  static constexpr int kTotal = kDQStageOff + (D == 64 ? 2 * 16384 : 0) + 1024;
+  static constexpr int kStatOff = kDSOff + 32768;                // per compute warp: 2 x (lse2[64] | delta[64])
+  static constexpr int kBarOff = kStatOff + 8 * 2 * 128 * 4;
+  static constexpr int kDQStageOff = kBarOff + 1024;             // D=64: one [32 q][32] fp32 tile per compute warp
+  static constexpr int kTotal = kDQStageOff + (D == 64 ? 8 * 4096 : 0) + 1024;
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -72,15 +72,20 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-__device__ __forceinline__ void compute_bar_sync() {
-  asm volatile("bar.sync 1, 256;" ::: "memory");
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src_smem, int32_t c0, int32_t c1,
+                                             int32_t c2, int32_t c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(m)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
-                const __grid_constant__ CUtensorMap tdq, const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tdq, const __grid_constant__ CUtensorMap tdk,
+                const __grid_constant__ CUtensorMap tdv, const AttnBwdParams p) {
   using L = AttnBwdSmem<D>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -102,7 +107,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint64_t* sdp_free = dkv_full + 1;           // 1 (256 arrivals): S^T and dP^T are in registers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stat = reinterpret_cast<float*>(smem + L::kStatOff);  // [2 buffers][lse2[128] | delta[128]]
+  float* stat = reinterpret_cast<float*>(smem + L::kStatOff);  // [8 warps][2 buffers][lse2[64] | delta * scale[64]]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_blk = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -138,6 +143,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     tma_prefetch_desc(&tv);
     tma_prefetch_desc(&tdo);
     tma_prefetch_desc(&tdq);
+    tma_prefetch_desc(&tdk);
+    tma_prefetch_desc(&tdv);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -281,15 +288,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const float kbias = (p.key_bias && key < p.Lk) ? p.key_bias[(long long)b * p.Lk + key] * 1.4426950408889634f : 0.f;
     bool ok = true;
 
-    // lse (log2 units) for threads 0..127, delta * scale for threads 128..255, of query block `it`
-    auto load_stat = [&](int it) -> float {
+    // Every warp stages the statistics of its own 64 query columns (no barrier between warps):
+    // lane l fetches lse (log2 units) and delta * scale of columns l and l + 32 of the warp's half.
+    struct Stat { float lse0, lse1, dl0, dl1; };
+    auto load_stat = [&](int it) -> Stat {
       const int h = hkv * group + it / iters_per_head;
-      const int q = (j_begin + it % iters_per_head) * 128 + (tid_c & 127);
+      const int q = (j_begin + it % iters_per_head) * 128 + wg * 64 + lane;
       const long long off = ((long long)b * p.H + h) * p.Lq + q;
-      if (tid_c < 128) return q < p.Lq ? __ldg(p.lse + off) * 1.4426950408889634f : INFINITY;
-      return q < p.Lq ? __ldg(p.delta + off) * p.scale : 0.f;
+      Stat v;
+      v.lse0 = q < p.Lq ? __ldg(p.lse + off) * 1.4426950408889634f : INFINITY;
+      v.lse1 = q + 32 < p.Lq ? __ldg(p.lse + off + 32) * 1.4426950408889634f : INFINITY;
+      v.dl0 = q < p.Lq ? __ldg(p.delta + off) * p.scale : 0.f;
+      v.dl1 = q + 32 < p.Lq ? __ldg(p.delta + off + 32) * p.scale : 0.f;
+      return v;
     };
-    // P^T and dS^T of 32 query columns (col0 .. col0+31 of the block) of this thread's key row
+    // P^T and dS^T of 32 query columns (col0 .. col0+31 of the block) of this thread's key row;
+    // `st` points at the 32 lse values of these columns, the delta values follow 64 floats later
     // (`masked` is a compile-time tag: a per-element branch would end the basic block at every
     // element and leave each exp2 -> multiply -> pack chain exposed at its full latency)
     auto chunk = [&](auto masked, const uint32_t* s, const uint32_t* dp, const float* st, int col0, int q0,
@@ -297,10 +311,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
       for (int i8 = 0; i8 < 32; i8 += 8) {
         // the per-query statistics are the same for every lane: 16-byte broadcast loads, 8 columns at a time
-        const float4 l0 = *reinterpret_cast<const float4*>(st + col0 + i8);
-        const float4 l1 = *reinterpret_cast<const float4*>(st + col0 + i8 + 4);
-        const float4 d0 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8);
-        const float4 d1 = *reinterpret_cast<const float4*>(st + 128 + col0 + i8 + 4);
+        const float4 l0 = *reinterpret_cast<const float4*>(st + i8);
+        const float4 l1 = *reinterpret_cast<const float4*>(st + i8 + 4);
+        const float4 d0 = *reinterpret_cast<const float4*>(st + 64 + i8);
+        const float4 d1 = *reinterpret_cast<const float4*>(st + 64 + i8 + 4);
         const float lse8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
         const float dl8[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
@@ -355,9 +369,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     };
 
     // head dim 64: dQ partial of query block `it` -> shared memory -> bulk tensor reduction.  Each
-    // warpgroup owns 32 of the 64 columns and one staging tile.
-    uint8_t* dq_stage = smem + L::kDQStageOff + wg * 16384;
-    const bool dq_leader = (tid_c & 127) == 0;
+    // warp owns 32 query rows x 32 columns and a staging tile of its own, so the warps never wait
+    // for one another.
+    uint8_t* dq_stage = smem + L::kDQStageOff + cw * 4096;
+    const bool dq_leader = lane == 0;
     auto drain_dq_tma = [&](int it) {
       const int h = hkv * group + it / iters_per_head;
       const int q0 = (j_begin + it % iters_per_head) * 128;
@@ -367,26 +382,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(smem_u32(&dq_empty[it & 1]));
       if (dq_leader) tma_store_wait_read<0>();      // the previous reduction has read the staging tile
-      named_bar_sync(2 + wg, 128);
+      __syncwarp();
 #pragma unroll
       for (int q4 = 0; q4 < 8; ++q4)
-        *reinterpret_cast<uint4*>(dq_stage + sw128_offset((uint32_t)r, (uint32_t)q4)) =
+        *reinterpret_cast<uint4*>(dq_stage + sw128_offset((uint32_t)lane, (uint32_t)q4)) =
             make_uint4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
       fence_proxy_async_smem();
-      named_bar_sync(2 + wg, 128);
+      __syncwarp();
       if (dq_leader) {   // rows past Lq fall outside the tensor map and are dropped
-        tma_reduce_add_4d(&tdq, smem_u32(dq_stage), wg * 32, h, q0, b);
+        tma_reduce_add_4d(&tdq, smem_u32(dq_stage), wg * 32, h, q0 + quad * 32, b);
         tma_store_commit();
       }
     };
 
-    float stat_next = total_iters > 0 ? load_stat(0) : 0.f;
+    Stat stat_next = total_iters > 0 ? load_stat(0) : Stat{0.f, 0.f, 0.f, 0.f};
+    float* stat_w = stat + cw * 256;
     for (int it = 0; it < total_iters && ok; ++it) {
       const int q0 = (j_begin + it % iters_per_head) * 128;
-      float* st = stat + (it & 1) * 256;
-      st[tid_c] = stat_next;
+      float* st = stat_w + (it & 1) * 128;
+      st[lane] = stat_next.lse0;
+      st[32 + lane] = stat_next.lse1;
+      st[64 + lane] = stat_next.dl0;
+      st[96 + lane] = stat_next.dl1;
       if (it + 1 < total_iters) stat_next = load_stat(it + 1);   // in flight during this block's work
-      compute_bar_sync();
+      __syncwarp();
       ok = mbar_wait(smem_u32(sp_full), it & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -414,8 +433,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(smem_u32(sdp_free));       // the tensor core may overwrite S^T / dP^T now
-        if (need_mask) chunk(std::true_type{}, sb, db, st, col0 + 32, q0, pk, dsk);
-        else chunk(std::false_type{}, sb, db, st, col0 + 32, q0, pk, dsk);
+        if (need_mask) chunk(std::true_type{}, sb, db, st + 32, col0 + 32, q0, pk, dsk);
+        else chunk(std::false_type{}, sb, db, st + 32, col0 + 32, q0, pk, dsk);
         store_chunk(col0 + 32, pk, dsk);
         tc_fence_before();
         fence_proxy_async_smem();
@@ -433,8 +452,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           tmem_ld32(tmem_base + lane_off + kDPCol + col0, dp);
           tmem_wait_ld();
           uint32_t pk[16], dsk[16];
-          if (need_mask) chunk(std::true_type{}, s, dp, st, col0, q0, pk, dsk);
-          else chunk(std::false_type{}, s, dp, st, col0, q0, pk, dsk);
+          if (need_mask) chunk(std::true_type{}, s, dp, st + c * 32, col0, q0, pk, dsk);
+          else chunk(std::false_type{}, s, dp, st + c * 32, col0, q0, pk, dsk);
           store_chunk(col0, pk, dsk);
         }
         tc_fence_before();
@@ -464,9 +483,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
+      // dK and dV leave through shared memory (the P^T / dS^T tiles are free now) as bulk tensor
+      // stores: a thread holds one key row, so direct stores would touch 32 lines per instruction.
+      // Tile (tensor, 64-column half) is [128 keys][64] bf16 in the 128-byte swizzle; rows past Lk
+      // fall outside the tensor map and are dropped.
       tc_fence_after();
-      __nv_bfloat16* dk_dst = p.dk + (long long)b * p.dk_sb + (long long)key * p.dk_ss + (long long)hkv * p.dk_sh + wg * (D / 2);
-      __nv_bfloat16* dv_dst = p.dv + (long long)b * p.dv_sb + (long long)key * p.dv_ss + (long long)hkv * p.dv_sh + wg * (D / 2);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t a[32], v[32];
@@ -478,24 +499,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < 32; ++i) { a[i] = 0u; v[i] = 0u; }
         }
-        if (key < p.Lk) {
+        const int col = wg * (D / 2) + c * 32;            // first of these 32 columns
+        uint8_t* tile_k = smem + L::kPOff + (col >> 6) * 16384;
+        uint8_t* tile_v = smem + L::kPOff + (D / 64) * 16384 + (col >> 6) * 16384;
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 wk, wv;
-            // dS^T was already multiplied by the softmax scale
-            wk.x = pack_bf16x2(__uint_as_float(a[8 * q4]), __uint_as_float(a[8 * q4 + 1]));
-            wk.y = pack_bf16x2(__uint_as_float(a[8 * q4 + 2]), __uint_as_float(a[8 * q4 + 3]));
-            wk.z = pack_bf16x2(__uint_as_float(a[8 * q4 + 4]), __uint_as_float(a[8 * q4 + 5]));
-            wk.w = pack_bf16x2(__uint_as_float(a[8 * q4 + 6]), __uint_as_float(a[8 * q4 + 7]));
-            wv.x = pack_bf16x2(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
-            wv.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
-            wv.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
-            wv.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
-            reinterpret_cast<uint4*>(dk_dst + c * 32)[q4] = wk;
-            reinterpret_cast<uint4*>(dv_dst + c * 32)[q4] = wv;
-          }
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 wk, wv;
+          // dS^T was already multiplied by the softmax scale
+          wk.x = pack_bf16x2(__uint_as_float(a[8 * q4]), __uint_as_float(a[8 * q4 + 1]));
+          wk.y = pack_bf16x2(__uint_as_float(a[8 * q4 + 2]), __uint_as_float(a[8 * q4 + 3]));
+          wk.z = pack_bf16x2(__uint_as_float(a[8 * q4 + 4]), __uint_as_float(a[8 * q4 + 5]));
+          wk.w = pack_bf16x2(__uint_as_float(a[8 * q4 + 6]), __uint_as_float(a[8 * q4 + 7]));
+          wv.x = pack_bf16x2(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
+          wv.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+          wv.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+          wv.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+          const uint32_t off = sw128_offset((uint32_t)r, (uint32_t)(((col & 63) >> 3) + q4));
+          *reinterpret_cast<uint4*>(tile_k + off) = wk;
+          *reinterpret_cast<uint4*>(tile_v + off) = wv;
         }
       }
+      fence_proxy_async_smem();
+    }
+    // every compute thread reaches this barrier, whatever happened above
+    named_bar_sync(1, 256);
+    if (tid_c == 0 && !*abort_flag) {
+#pragma unroll
+      for (int a = 0; a < D / 64; ++a) {
+        tma_store_4d(&tdk, smem_u32(smem + L::kPOff + a * 16384), a * 64, k0, hkv, b);
+        tma_store_4d(&tdv, smem_u32(smem + L::kPOff + (D / 64) * 16384 + a * 16384), a * 64, k0, hkv, b);
+      }
+      tma_store_commit();
+      tma_store_wait_read<0>();
     }
   }
 
@@ -568,7 +603,8 @@ __global__ void attn_bwd_dq_cast_kernel(const float* __restrict__ acc, __nv_bflo
 
 template <int D>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                      const CUtensorMap& tdq, const AttnBwdParams& p, cudaStream_t stream) {
+                      const CUtensorMap& tdq, const CUtensorMap& tdk, const CUtensorMap& tdv, const AttnBwdParams& p,
+                      cudaStream_t stream) {
   using L = AttnBwdSmem<D>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -578,7 +614,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     configured[dev & 63] = true;
   }
   dim3 grid((p.Lk + 127) / 128, p.Hkv, p.B);
-  attn_bwd_kernel<D><<<grid, kBwdThreads, L::kTotal, stream>>>(tq, tk, tv, tdo, tdq, p);
+  attn_bwd_kernel<D><<<grid, kBwdThreads, L::kTotal, stream>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   MRK_CHECK_LAUNCH();
   return 0;
 }
@@ -603,13 +639,16 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
   if ((rc = make_bshd_tmap(&tk, k, D, Lk, Hkv, B, sk[0], sk[1], sk[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tv, v, D, Lk, Hkv, B, sv[0], sv[1], sv[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tdo, dout, D, Lq, H, B, sdo[0], sdo[1], sdo[2], 128))) return rc;
-  CUtensorMap tdq;   // the fp32 dQ accumulator [B, Lq, H, D]: boxes of 128 queries x 32 columns of one head
+  CUtensorMap tdq;   // the fp32 dQ accumulator [B, Lq, H, D]: boxes of 32 queries x 32 columns of one head
   {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)Lq, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)D, (uint64_t)H * D, (uint64_t)Lq * H * D};
-    const uint32_t box[4] = {32, 1, 128, 1};
+    const uint32_t box[4] = {32, 1, 32, 1};
     if ((rc = make_tmap_4d(&tdq, dq_acc, 4, dims, strides, box, 3))) return rc;
   }
+  CUtensorMap tdk, tdv;
+  if ((rc = make_bshd_tmap(&tdk, dk, D, Lk, Hkv, B, sdk[0], sdk[1], sdk[2], 128))) return rc;
+  if ((rc = make_bshd_tmap(&tdv, dv, D, Lk, Hkv, B, sdv[0], sdv[1], sdv[2], 128))) return rc;
   const long long rows = (long long)B * Lq * H;
   {
     const int warps_per_block = 8;
@@ -635,7 +674,8 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "attention backward: status word unavailable");
-  rc = (D == 64) ? launch_bwd<64>(tq, tk, tv, tdo, tdq, p, s) : launch_bwd<128>(tq, tk, tv, tdo, tdq, p, s);
+  rc = (D == 64) ? launch_bwd<64>(tq, tk, tv, tdo, tdq, tdk, tdv, p, s)
+                 : launch_bwd<128>(tq, tk, tv, tdo, tdq, tdk, tdv, p, s);
   if (rc) return rc;
   {
     const long long total_vec = rows * (D / 8);

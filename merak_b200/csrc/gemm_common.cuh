@@ -303,16 +303,24 @@ __device__ __noinline__ void epilogue_tile_t(const GemmParams& p, long long row,
                       ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                       ((reinterpret_cast<uintptr_t>(p.aux_in) & 15) == 0) &&
                       ((reinterpret_cast<uintptr_t>(p.aux_out) & 15) == 0);
+// Two chunks of 32 columns per TMEM round trip: a load that queues behind the tensor core's own
+// accumulator traffic takes about a thousand cycles, and one chunk at a time that latency was most
+// of the epilogue.
+const int nchunks = min(ncols / 32, (p.N - col_base + 31) / 32);     // uniform across the warp
 #pragma unroll 1
-for (int c = 0; c < ncols / 32; ++c) {
-  const int col0 = col_base + c * 32;
-  if (col0 >= p.N) break;  // uniform across the warp
-  uint32_t r[32];
-  tmem_ld32(t_row + c * 32, r);
+for (int c2 = 0; c2 < nchunks; c2 += 2) {
+  uint32_t r2[2][32];
+  tmem_ld32(t_row + c2 * 32, r2[0]);
+  tmem_ld32(t_row + min(c2 + 1, nchunks - 1) * 32, r2[1]);      // (an odd tail re-reads its own chunk)
   tmem_wait_ld();
+#pragma unroll
+for (int h = 0; h < 2; ++h) {
+  const int c = c2 + h;
+  if (c >= nchunks) continue;
+  const int col0 = col_base + c * 32;
   float v[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[h][j]) * p.alpha;
   const bool full = (col0 + 32 <= p.N);
   if (p.bias != nullptr && first_split) {
     const bool bias_vec = full && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
@@ -504,6 +512,7 @@ for (int c = 0; c < ncols / 32; ++c) {
       }
     }
   }
+}
 }
 }
 

@@ -20,13 +20,20 @@ namespace mrk {
 
 constexpr int kPairBlockM = 256;      // rows per cluster tile (128 per CTA)
 constexpr int kPairBlockN = 256;
-constexpr int kPairBlockK = 64;
+constexpr int kPairBlockK = 64;       // one k-block: the 64-element swizzle atom
 constexpr int kPairThreads = 320;     // TMA warp, UMMA warp, 8 epilogue warps
-constexpr int kPairStages = 5;
-constexpr int kPairABytes = 128 * kPairBlockK * 2;            // this CTA's rows of A
-constexpr int kPairBBytes = (kPairBlockN / 2) * kPairBlockK * 2;  // this CTA's half of B
-constexpr int kPairStageBytes = kPairABytes + kPairBBytes;    // 32 KB
-constexpr int kPairStagingBytes = 2 * 32768;   // epilogue staging: two 128 x 128 bf16 blocks (TMA-store source)
+// A ring stage holds kPairGroup consecutive k-blocks and has ONE full and ONE empty barrier: the UMMA
+// thread waits once and commits once per eight UMMAs.  Measured on B200 with 256x256x16 UMMAs back to
+// back: no commit 128 cycles per UMMA, one commit per four UMMAs 138-166 (the more code around the
+// commit, the worse), one per eight 128.
+constexpr int kPairGroup = 2;
+constexpr int kPairStages = 3;
+constexpr int kPairABytes = 128 * kPairBlockK * 2;            // this CTA's rows of A, one k-block
+constexpr int kPairBBytes = (kPairBlockN / 2) * kPairBlockK * 2;  // this CTA's half of B, one k-block
+constexpr int kPairSubBytes = kPairABytes + kPairBBytes;      // 32 KB per k-block
+constexpr int kPairStageBytes = kPairGroup * kPairSubBytes;   // 64 KB
+// epilogue staging: one 128-row x 64-column bf16 box (TMA-store source) per column half
+constexpr int kPairStagingBytes = 2 * 16384;
 constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes + 1024 + 1024;
 
 // mode 1, store thread: the partial product of sub-tile `u` is complete in this rank's buffer.
@@ -269,7 +276,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();          // 0 = leader
-  const uint32_t peer = cta ^ 1u;
   const bool leader = cta == 0;
   const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
   const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
@@ -344,27 +350,30 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           ok = comm_wait_rows(p, m0, 128, abort_flag);
           if (!ok) break;
         }
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; kb += kPairGroup) {
+          const int nsub = min(kPairGroup, kb_end - kb);
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, p.status);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full_bar[stage]);
-          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
-          const uint32_t sb = sa + kPairABytes;
-          if (leader) mbar_arrive_expect_tx(fb, 2 * kPairStageBytes);   // bytes of both CTAs
-          const int k0 = kb * kPairBlockK;
-          if (!a_mn) {
-            tma_load_2d_pair(sa, &tma_a, fb, k0, m0);
-          } else {
+          if (leader) mbar_arrive_expect_tx(fb, (uint32_t)(nsub * 2 * kPairSubBytes));   // bytes of both CTAs
+          for (int sub = 0; sub < nsub; ++sub) {
+            const uint32_t sa = smem_u32(smem + stage * kPairStageBytes + sub * kPairSubBytes);
+            const uint32_t sb = sa + kPairABytes;
+            const int k0 = (kb + sub) * kPairBlockK;
+            if (!a_mn) {
+              tma_load_2d_pair(sa, &tma_a, fb, k0, m0);
+            } else {
 #pragma unroll
-            for (int atom = 0; atom < 2; ++atom)
-              tma_load_2d_pair(sa + atom * (kPairBlockK * 128), &tma_a, fb, m0 + atom * 64, k0);
-          }
-          if (!b_mn) {
-            tma_load_2d_pair(sb, &tma_b, fb, k0, n0);
-          } else {
+              for (int atom = 0; atom < 2; ++atom)
+                tma_load_2d_pair(sa + atom * (kPairBlockK * 128), &tma_a, fb, m0 + atom * 64, k0);
+            }
+            if (!b_mn) {
+              tma_load_2d_pair(sb, &tma_b, fb, k0, n0);
+            } else {
 #pragma unroll
-            for (int atom = 0; atom < 2; ++atom)
-              tma_load_2d_pair(sb + atom * (kPairBlockK * 128), &tma_b, fb, n0 + atom * 64, k0);
+              for (int atom = 0; atom < 2; ++atom)
+                tma_load_2d_pair(sb + atom * (kPairBlockK * 128), &tma_b, fb, n0 + atom * 64, k0);
+            }
           }
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
@@ -397,26 +406,27 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         const uint32_t d_tmem = tmem_base + acc * kPairBlockN;
         const int kb_begin = (unit % p.num_splits) * p.kb_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; kb += kPairGroup) {
+          const int nsub = min(kPairGroup, kb_end - kb);
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
-          const uint32_t sb = sa + kPairABytes;
+          for (int sub = 0; sub < nsub; ++sub) {
+            const uint32_t sa = smem_u32(smem + stage * kPairStageBytes + sub * kPairSubBytes);
+            const uint32_t sb = sa + kPairABytes;
 #pragma unroll
-          for (int k = 0; k < kPairBlockK / 16; ++k) {
-            const uint64_t da = a_mn ? desc_mnmajor(sa, k, kPairBlockK) : desc_kmajor(sa, k);
-            const uint64_t db = b_mn ? desc_mnmajor(sb, k, kPairBlockK) : desc_kmajor(sb, k);
-            umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+            for (int k = 0; k < kPairBlockK / 16; ++k) {
+              const uint64_t da = a_mn ? desc_mnmajor(sa, k, kPairBlockK) : desc_kmajor(sa, k);
+              const uint64_t db = b_mn ? desc_mnmajor(sb, k, kPairBlockK) : desc_kmajor(sb, k);
+              umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb != kb_begin || sub != 0 || k != 0) ? 1u : 0u);
+            }
           }
           // release this stage in both CTAs once the UMMAs above have read it
-          umma_commit_pair(smem_u32(&empty_bar[stage]));
-          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), peer));
+          umma_commit_pair_both(smem_u32(&empty_bar[stage]));
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) {
-          umma_commit_pair(smem_u32(&tmem_full_bar[acc]));
-          umma_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[acc]), peer));
+          umma_commit_pair_both(smem_u32(&tmem_full_bar[acc]));
         }
       }
     }
@@ -426,12 +436,29 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     const int row_in_tile = quad * 32 + lane;
     // two warps share a TMEM lane quadrant: warps 2..5 take the left half of the columns, 6..9 the right
     const int half = (warp - 2) >> 2;
-    uint8_t* stage = staging + half * 32768;
+    uint8_t* stage = staging + half * 16384;        // one 128 x 64 bf16 box, reused by the two 64-column passes
     const bool store_thread = (warp == 2 + half * 4) && lane == 0;     // issues this half's TMA stores
-    bool staged_before = false;
+    bool box_busy = false;     // a TMA store that reads the box may still be in flight
     int iter = 0;
     bool ok = true;
     int pending_flag = -1, pending_owner = 0;     // mode 1: sub-tile whose stores are in flight (store thread)
+    // before the box is overwritten: its last store must have read it (128 threads of this half)
+    auto box_acquire = [&]() {
+      if (box_busy) {
+        if (store_thread) tma_store_wait_read<0>();
+        named_bar_sync(1 + half, 128);
+      }
+    };
+    // after the box is written: one thread hands it to the TMA unit
+    auto box_store = [&](const CUtensorMap* map, int col, long long row0) {
+      fence_proxy_async_smem();
+      named_bar_sync(1 + half, 128);
+      if (store_thread) {
+        if (row0 < p.M) tma_store_2d(map, smem_u32(stage), col, (int32_t)row0);
+        tma_store_commit();
+      }
+      box_busy = true;
+    };
     for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++iter) {
       int m_blk, n_blk;
       tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
@@ -452,58 +479,43 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       // staged output for this block? (uniform over the four warps of the half)
       const bool staged = p.tma_store && !split_k && col_half < p.N &&
                           (col_half + kPairBlockN / 2 <= p.N || (p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr));
-      if (staged_before) {       // the previous block's TMA stores must have read the staging buffer
-        if (store_thread) {
-          if (rs) {              // ... and, under a fused reduce-scatter, have landed: tell the owner of the rows
-            tma_store_wait<0>();
-            if (pending_flag >= 0) rs_publish(p, pending_owner, pending_flag);
-            pending_flag = -1;
-          } else {
-            tma_store_wait_read<0>();
-          }
-        }
-        named_bar_sync(1 + half, 128);
+      if (rs && store_thread && pending_flag >= 0) {
+        // fused reduce-scatter: the previous sub-tile's stores have landed; tell the owner of the rows
+        tma_store_wait<0>();
+        rs_publish(p, pending_owner, pending_flag);
+        pending_flag = -1;
       }
-      const bool two_pass = staged && p.tma_store_aux && p.aux_out != nullptr;
-      if (two_pass) {
-        // pre-activation side output first: stage, store, and wait until the buffer can be reused
-        epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k,
-                      first_split, stage, row_in_tile, 1);
-        fence_proxy_async_smem();
-        named_bar_sync(1 + half, 128);
-        if (store_thread) {
-          if (row0 < p.M) {
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-              if (col_half + b * 64 < p.N)
-                tma_store_2d(&tma_aux, smem_u32(stage + b * 16384), col_half + b * 64, (int32_t)row0);
-          }
-          tma_store_commit();
-          tma_store_wait_read<0>();
-        }
-        named_bar_sync(1 + half, 128);
-      }
-      epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k, first_split,
-                    staged ? stage : nullptr, row_in_tile, two_pass ? 2 : 0);
-      tc_fence_before();
-      __syncwarp();            // every lane's TMEM reads are complete: one (possibly remote) arrival per warp
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));   // TMEM is free
+      auto release_tmem = [&]() {
+        tc_fence_before();
+        __syncwarp();            // every lane's TMEM reads are complete: one (possibly remote) arrival per warp
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));   // TMEM is free
+      };
       if (staged) {
-        fence_proxy_async_smem();
-        named_bar_sync(1 + half, 128);
-        if (store_thread && row0 < p.M) {
-#pragma unroll
-          for (int b = 0; b < 2; ++b)
-            if (col_half + b * 64 < p.N)
-              tma_store_2d(&tma_c, smem_u32(stage + b * 16384), col_half + b * 64, (int32_t)row0);
-          tma_store_commit();
-          if (rs && col_half < p.N) {
-            pending_flag = ((m_blk * p.num_n_blocks + n_blk) * 2 + (int)cta) * 2 + half;
-            pending_owner = (int)((row0 / p.comm.seg_rows) % p.comm.n);
+        const bool two_pass = p.tma_store_aux && p.aux_out != nullptr;
+        const int npass = (col_half + 64 < p.N) ? 2 : 1;        // 64-column passes with anything to write
+        for (int b = 0; b < npass; ++b) {
+          const int col_b = col_half + b * 64;
+          const uint32_t t_b = t_row + half * (kPairBlockN / 2) + b * 64;
+          if (two_pass) {
+            // the pre-activation side output of these columns first, through the same box
+            box_acquire();
+            epilogue_tile(p, row, row_ok, t_b, col_b, 64, split_k, first_split, stage, row_in_tile, 1);
+            box_store(&tma_aux, col_b, row0);
           }
+          box_acquire();
+          epilogue_tile(p, row, row_ok, t_b, col_b, 64, split_k, first_split, stage, row_in_tile, two_pass ? 2 : 0);
+          if (b == npass - 1) release_tmem();
+          box_store(&tma_c, col_b, row0);
         }
+        if (rs && store_thread && row0 < p.M) {
+          pending_flag = ((m_blk * p.num_n_blocks + n_blk) * 2 + (int)cta) * 2 + half;
+          pending_owner = (int)((row0 / p.comm.seg_rows) % p.comm.n);
+        }
+      } else {
+        epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k,
+                      first_split, nullptr, row_in_tile, 0);
+        release_tmem();
       }
-      staged_before = staged;
     }
     if (store_thread) {
       if (rs) {

@@ -3,7 +3,7 @@
 
     python tools/profile_cases.py <case> [--iters N]
 
-Cases: gemm, gemm_gelu, gemm_k1024, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce,
+Cases: gemm, gemm_gelu, gemm_k1024, gemm_table, wgrad, attn_fwd, attn_bwd, norm, adamw, dp_step, ag_gemm, tp_reduce,
 cross_entropy, rope, swiglu, embedding, colsum, moe_push.
 Each prints the CUDA-event time per launch and the achieved TFLOP/s or GB/s.  The multi-rank
 kernels run with all ranks' buffers on this one GPU and the cross-rank barriers pre-satisfied, so
@@ -60,6 +60,46 @@ def main():
         act = G.ACT_GELU_ERF if o.case == "gemm_gelu" else G.ACT_NONE
         ms = _time(lambda: G.gemm(a, b, bias=bias, act=act, want_preact=o.case == "gemm_gelu"), it)
         print("%s %dx%dx%d: %.3f ms  %.1f TFLOP/s" % (o.case, M, N, K, ms, 2.0 * M * N * K / ms / 1e9))
+    elif o.case == "gemm_table":
+        # forward / data-gradient / weight-gradient GEMMs of the model configurations, against torch.matmul
+        # (cuBLAS) on the same box: median of 20 launches each, L2 flushed between launches
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+        def med(fn, n=20):
+            for _ in range(5):
+                fn()
+            ts = []
+            for _ in range(n):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return sorted(ts)[n // 2]
+
+        T = 16384                      # tokens per micro-batch
+        shapes = [("BERT-large qkv", T, 3072, 1024), ("BERT-large out/ffn2-dgrad", T, 1024, 1024),
+                  ("BERT-large ffn1", T, 4096, 1024), ("BERT-large ffn2", T, 1024, 4096),
+                  ("GPT-2 1.5B tp2 qkv", T, 2400, 1600), ("GPT-2 1.5B tp2 ffn1", T, 3200, 1600),
+                  ("GPT-2 1.5B tp2 proj", T, 1600, 800), ("GPT-2 1.5B tp2 ffn2", T, 1600, 3200),
+                  ("Llama-7B tp4 qkv", T, 3072, 4096), ("Llama-7B tp4 gate/up", T, 2752, 4096),
+                  ("Llama-7B tp4 o", T, 4096, 1024), ("Llama-7B tp4 down", T, 4096, 2752),
+                  ("square", 8192, 8192, 8192)]
+        print("| GEMM | M x N x K | fprop ours / cuBLAS (ms) | ratio | wgrad ours / cuBLAS (ms) | ratio |")
+        print("|---|---|---|---|---|---|")
+        for name, M, N, K in shapes:
+            a = torch.randn(M, K, device=dev, dtype=bf)
+            w = torch.randn(N, K, device=dev, dtype=bf) * 0.02
+            dy = torch.randn(M, N, device=dev, dtype=bf)
+            dw = torch.zeros(N, K, device=dev)
+            t_f = med(lambda: G.gemm(a, w))
+            c_f = med(lambda: torch.matmul(a, w.t()))
+            t_w = med(lambda: G.gemm(dy, a, a_mn=True, b_mn=True, out=dw, accumulate=True))
+            c_w = med(lambda: torch.matmul(dy.t(), a))           # bf16 output, no accumulation: a lower bound
+            print("| %s | %d x %d x %d | %.4f / %.4f | %.2f | %.4f / %.4f | %.2f |"
+                  % (name, M, N, K, t_f, c_f, t_f / c_f, t_w, c_w, t_w / c_w), flush=True)
     elif o.case == "wgrad":
         M, N, K = 16384, 4096, 1024           # dW[N,K] += dY[M,N]^T X[M,K]
         dy = torch.randn(M, N, device=dev, dtype=bf)
