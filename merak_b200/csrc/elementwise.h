@@ -33,6 +33,9 @@ int mrk_rope(const void* x, void* y, const float* cosb, const float* sinb, const
              int inverse, void* stream);
 int mrk_swiglu_fwd(const void* gu, void* out, long long M, int F, long long ld, void* stream);
 int mrk_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long M, int F, long long ld, void* stream);
+int mrk_act_fwd(const void* x, void* y, long long n, int act, void* stream);
+int mrk_act_bwd(const void* d, const void* h, void* out, float* colsum_out, long long M, int N, long long ld, int act,
+                void* stream);
 int mrk_colsum(const void* x, float* out, long long M, int N, long long ld, void* stream);
 // Next-token sampling (csrc/sampling.cu): temperature / top-k (1..1024) / top-p / draw for a batch of rows.
 int mrk_sample_topk_topp(const void* logits, int is_bf16, long long rows, int V, long long row_stride, int top_k,

@@ -3,6 +3,7 @@
 #pragma once
 #include "gemm_tcgen05.h"
 #include "sm100_ptx.cuh"
+#include "activations.cuh"
 #include "symm.cuh"
 
 namespace mrk {
@@ -70,8 +71,9 @@ struct GemmParams {
   unsigned* status;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int num_splits, kb_per_split;   // split-K: work unit = (tile, split); partial sums meet in fp32 red.add
-  int tma_store;                  // the kernel may write C through shared memory + TMA stores (bf16, no accumulate)
+  int tma_store;                  // C leaves through shared memory + the TMA unit: 1 = bf16 stores (no accumulate), 2 = fp32 stores or adds
   int tma_store_aux;              // ... and the pre-activation side output too (second tensor map)
+  int tma_aux_in;                 // aux_in blocks can be brought in with TMA loads (third tensor map)
   GemmComm comm;
 };
 
@@ -204,74 +206,6 @@ __device__ __forceinline__ void comm_gather_role(const GemmParams& p, uint8_t* s
     for (int s = 0; s < num_seg; ++s) atomicAdd(c.seg_flags + s, 1u);
 }
 
-// erf-GELU pieces from one exponential: with e = exp(-x^2/2), the normal pdf is e/sqrt(2 pi) and
-// erf(|x|/sqrt 2) = 1 - poly(t) * e, t = 1/(1 + p |x|/sqrt 2) (Abramowitz-Stegun 7.1.26, |error| < 1.5e-7).
-// About 20 instructions per element instead of the ~60 of erff + expf, which matters because the
-// epilogue warps evaluate it for every output element.
-__device__ __forceinline__ void gelu_erf_parts(float x, float& cdf, float& pdf) {
-  const float ax = fabsf(x) * 0.7071067811865476f;
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
-  const float e = __expf(-ax * ax);
-  float poly = fmaf(t, 1.061405429f, -1.453152027f);
-  poly = fmaf(t, poly, 1.421413741f);
-  poly = fmaf(t, poly, -0.284496736f);
-  poly = fmaf(t, poly, 0.254829592f);
-  const float erf_abs = fmaf(-poly * t, e, 1.0f);
-  cdf = 0.5f * (1.0f + copysignf(erf_abs, x));
-  pdf = 0.3989422804014327f * e;
-}
-__device__ __forceinline__ float gelu_erf(float x) {
-  float cdf, pdf;
-  gelu_erf_parts(x, cdf, pdf);
-  return x * cdf;
-}
-__device__ __forceinline__ float gelu_erf_grad(float x) {
-  float cdf, pdf;
-  gelu_erf_parts(x, cdf, pdf);
-  return fmaf(x, pdf, cdf);
-}
-__device__ __forceinline__ float fast_tanh(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + fast_tanh(u));
-}
-__device__ __forceinline__ float gelu_tanh_grad(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = fast_tanh(u);
-  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
-  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
-}
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
-__device__ __forceinline__ float silu_grad(float x) {
-  const float s = 1.0f / (1.0f + __expf(-x));
-  return s * (1.0f + x * (1.0f - s));
-}
-
-template <int act>
-__device__ __forceinline__ float apply_act(float v) {
-  switch (act) {
-    case MRK_ACT_GELU_ERF: return gelu_erf(v);
-    case MRK_ACT_GELU_TANH: return gelu_tanh(v);
-    case MRK_ACT_RELU: return v > 0.f ? v : 0.f;
-    case MRK_ACT_SILU: return silu(v);
-    default: return v;
-  }
-}
-template <int act>
-__device__ __forceinline__ float apply_act_grad(float x) {
-  switch (act) {
-    case MRK_ACT_GELU_ERF: return gelu_erf_grad(x);
-    case MRK_ACT_GELU_TANH: return gelu_tanh_grad(x);
-    case MRK_ACT_RELU: return x > 0.f ? 1.f : 0.f;
-    case MRK_ACT_SILU: return silu_grad(x);
-    default: return 1.f;
-  }
-}
-
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
   // Grouped raster: 8 row-blocks share their B panel in L2 before the next group starts.
   constexpr int kGroup = 8;
@@ -361,7 +295,10 @@ for (int h = 0; h < 2; ++h) {
   if (stage != nullptr) {
     // shared-memory staged output: side tensors are only present on full-width blocks here.
     // pass 1 stages the pre-activation side output alone, pass 2 the main output without it; pass 0
-    // does the main output and writes a side output, if any, directly.
+    // does the main output and writes a side output, if any, directly; pass 3 is pass 0 with an
+    // fp32 box of 32 columns (weight gradients).  Pass 8: like pass 0, and the caller has brought the
+    // aux_in block into the box with a TMA load (a thread owns a row, so loading it from global memory
+    // touches 32 lines per instruction); the result overwrites it in place.
     if (pass == 1) {
       uint8_t* box = stage + (c >> 1) * 16384;
 #pragma unroll
@@ -373,7 +310,7 @@ for (int h = 0; h < 2; ++h) {
       }
       continue;
     }
-    if (pass == 0 && p.aux_out != nullptr && row_ok) {
+    if ((pass == 0 || pass == 3 || pass == 8) && p.aux_out != nullptr && row_ok) {
       uint4* dst = reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col0);
 #pragma unroll
       for (int q = 0; q < 4; ++q)
@@ -384,11 +321,13 @@ for (int h = 0; h < 2; ++h) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = apply_act<kAct>(v[j]);
     }
-    if (kAux != MRK_AUX_NONE && row_ok) {
+    if (kAux != MRK_AUX_NONE && (row_ok || pass == 8)) {
       const uint4* src = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col0);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint4 a = __ldg(src + q);
+        const uint4 a = pass == 8 ? *reinterpret_cast<const uint4*>(stage + (c >> 1) * 16384 +
+                                                                    sw128_offset((uint32_t)r_in_tile, (uint32_t)((c & 1) * 4 + q)))
+                                  : __ldg(src + q);
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -402,6 +341,14 @@ for (int h = 0; h < 2; ++h) {
           }
         }
       }
+    }
+    if (pass == 3) {
+      // fp32 box: these 32 columns are one 128-byte row; the caller stores it or adds it into the output
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(stage + sw128_offset((uint32_t)r_in_tile, (uint32_t)q)) =
+            make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      continue;
     }
     uint8_t* box = stage + (c >> 1) * 16384;
 #pragma unroll

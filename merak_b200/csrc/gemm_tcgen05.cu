@@ -258,7 +258,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, c
 }
 
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& taux,
-                     GemmParams& p, cudaStream_t stream);
+                     const CUtensorMap& tauxin, GemmParams& p, cudaStream_t stream);
 
 }  // namespace mrk
 
@@ -298,6 +298,7 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
   memset(&p.comm, 0, sizeof(p.comm));
   p.tma_store = 0;
   p.tma_store_aux = 0;
+  p.tma_aux_in = 0;
   if (comm != nullptr) p.comm = *comm;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
@@ -318,13 +319,27 @@ static int gemm_entry(const void* A, const void* B, void* C, int M, int N, int K
       if (rc) return rc;
       p.tma_store = 1;
     }
+    if ((flags & MRK_GEMM_OUT_F32) && (ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+      // fp32 outputs (weight gradients): boxes of 128 rows x 32 columns, stored or added by the TMA unit
+      rc = make_tmap_2d(&tc, C, 4, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 128, 3);
+      if (rc) return rc;
+      p.tma_store = 2;
+    }
     CUtensorMap taux = ta;
     if (p.tma_store && aux_out != nullptr && (ld_aux_out % 8) == 0 && (reinterpret_cast<uintptr_t>(aux_out) & 15) == 0) {
       rc = make_tmap_2d(&taux, aux_out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ld_aux_out, 64, 128, 3);
       if (rc) return rc;
       p.tma_store_aux = 1;
     }
-    return launch_gemm_pair(ta, tb, tc, taux, p, s);
+    CUtensorMap tauxin = ta;
+    p.tma_aux_in = 0;
+    if (p.tma_store == 1 && aux_mode != MRK_AUX_NONE && (ld_aux_in % 8) == 0 &&
+        (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0) {
+      rc = make_tmap_2d(&tauxin, aux_in, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ld_aux_in, 64, 128, 3);
+      if (rc) return rc;
+      p.tma_aux_in = 1;
+    }
+    return launch_gemm_pair(ta, tb, tc, taux, tauxin, p, s);
   }
   if (bn == 256) return launch<256>(ta, tb, p, s);
   if (bn == 128) return launch<128>(ta, tb, p, s);

@@ -257,7 +257,7 @@ __device__ __forceinline__ void rs_reducer_role(const GemmParams& p, uint8_t* sm
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_aux,
-                      const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tma_auxin, const GemmParams p) {
   constexpr uint32_t kTmemCols = 512;   // two 256-column accumulator buffers
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -270,6 +270,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;                     // used in the even CTA only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* aux_full = reinterpret_cast<uint64_t*>(bar_base + 128);    // per column half: aux_in block has landed
   uint64_t* pull_full = reinterpret_cast<uint64_t*>(bar_base + 256);   // mode 1, reduce phase (8 slots at most)
   uint64_t* pull_empty = pull_full + 8;
   volatile int* slot_piece = reinterpret_cast<volatile int*>(bar_base + 512);
@@ -306,7 +307,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       mbar_init(smem_u32(&pull_full[s]), 1);
       mbar_init(smem_u32(&pull_empty[s]), 256);
     }
+    mbar_init(smem_u32(&aux_full[0]), 1);
+    mbar_init(smem_u32(&aux_full[1]), 1);
     fence_mbar_init();
+    if (p.tma_aux_in) tma_prefetch_desc(&tma_auxin);
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (p.tma_store) tma_prefetch_desc(&tma_c);
@@ -439,18 +443,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     uint8_t* stage = staging + half * 16384;        // one 128 x 64 bf16 box, reused by the two 64-column passes
     const bool store_thread = (warp == 2 + half * 4) && lane == 0;     // issues this half's TMA stores
     bool box_busy = false;     // a TMA store that reads the box may still be in flight
+    uint32_t aux_phase = 0;    // parity of this half's aux_in barrier
     int iter = 0;
     bool ok = true;
     int pending_flag = -1, pending_owner = 0;     // mode 1: sub-tile whose stores are in flight (store thread)
     // before the box is overwritten: its last store must have read it (128 threads of this half)
-    auto box_acquire = [&]() {
+    auto box_acquire = [&]() __attribute__((always_inline)) {
       if (box_busy) {
         if (store_thread) tma_store_wait_read<0>();
         named_bar_sync(1 + half, 128);
       }
     };
     // after the box is written: one thread hands it to the TMA unit
-    auto box_store = [&](const CUtensorMap* map, int col, long long row0) {
+    auto box_store = [&](const CUtensorMap* map, int col, long long row0) __attribute__((always_inline)) {
       fence_proxy_async_smem();
       named_bar_sync(1 + half, 128);
       if (store_thread) {
@@ -467,25 +472,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       const bool first_split = (unit % p.num_splits) == 0;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
-      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
       const long long row0 = (long long)m_blk * kPairBlockM + (long long)cta * 128;
       const long long row = row0 + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kPairBlockN;
       const int col_half = n_blk * kPairBlockN + half * (kPairBlockN / 2);
       // staged output for this block? (uniform over the four warps of the half)
-      const bool staged = p.tma_store && !split_k && col_half < p.N &&
+      const bool staged32 = p.tma_store == 2 && col_half < p.N;     // fp32 output: boxes of 32 columns
+      const bool staged = p.tma_store == 1 && !split_k && col_half < p.N &&
                           (col_half + kPairBlockN / 2 <= p.N || (p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr));
+      // aux_in (residual, or the saved pre-activation of a backward GEMM) comes into the box by TMA
+      const bool aux_tma = staged && p.tma_aux_in && p.aux_mode != MRK_AUX_NONE &&
+                           !(p.tma_store_aux && p.aux_out != nullptr);
+      auto aux_fetch = [&](int col) __attribute__((always_inline)) {        // the box is free: start the load of its aux_in block
+        if (store_thread) {
+          mbar_arrive_expect_tx(smem_u32(&aux_full[half]), 16384u);
+          tma_load_2d(smem_u32(stage), &tma_auxin, smem_u32(&aux_full[half]), col, (int32_t)row0);
+        }
+      };
+      if (aux_tma) {      // the first block's load overlaps the wait for the accumulator
+        box_acquire();
+        aux_fetch(col_half);
+      }
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
       if (rs && store_thread && pending_flag >= 0) {
         // fused reduce-scatter: the previous sub-tile's stores have landed; tell the owner of the rows
         tma_store_wait<0>();
         rs_publish(p, pending_owner, pending_flag);
         pending_flag = -1;
       }
-      auto release_tmem = [&]() {
+      auto release_tmem = [&]() __attribute__((always_inline)) {
         tc_fence_before();
         __syncwarp();            // every lane's TMEM reads are complete: one (possibly remote) arrival per warp
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));   // TMEM is free
@@ -502,14 +521,48 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             epilogue_tile(p, row, row_ok, t_b, col_b, 64, split_k, first_split, stage, row_in_tile, 1);
             box_store(&tma_aux, col_b, row0);
           }
-          box_acquire();
-          epilogue_tile(p, row, row_ok, t_b, col_b, 64, split_k, first_split, stage, row_in_tile, two_pass ? 2 : 0);
+          if (aux_tma) {
+            if (b > 0) {
+              box_acquire();
+              aux_fetch(col_b);
+            }
+            ok = mbar_wait(smem_u32(&aux_full[half]), aux_phase, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            aux_phase ^= 1u;
+            if (!ok) break;
+          } else {
+            box_acquire();
+          }
+          epilogue_tile(p, row, row_ok, t_b, col_b, 64, split_k, first_split, stage, row_in_tile,
+                        aux_tma ? 8 : (two_pass ? 2 : 0));
           if (b == npass - 1) release_tmem();
           box_store(&tma_c, col_b, row0);
         }
         if (rs && store_thread && row0 < p.M) {
           pending_flag = ((m_blk * p.num_n_blocks + n_blk) * 2 + (int)cta) * 2 + half;
           pending_owner = (int)((row0 / p.comm.seg_rows) % p.comm.n);
+        }
+      } else if (staged32) {
+        // fp32 output through the same box, 32 columns (one 128-byte row per output row) at a time: a plain
+        // store, or an element-wise add when the GEMM accumulates into its output or splits K
+        const bool add = split_k || (p.flags & MRK_GEMM_ACCUMULATE) != 0;
+        const int npass = min(4, (p.N - col_half + 31) / 32);
+        for (int b = 0; b < npass; ++b) {
+          const int col_b = col_half + b * 32;
+          box_acquire();
+          epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2) + b * 32, col_b, 32, split_k, first_split,
+                        stage, row_in_tile, 3);
+          if (b == npass - 1) release_tmem();
+          fence_proxy_async_smem();
+          named_bar_sync(1 + half, 128);
+          if (store_thread) {
+            if (row0 < p.M) {
+              if (add) tma_reduce_add_2d(&tma_c, smem_u32(stage), col_b, (int32_t)row0);
+              else tma_store_2d(&tma_c, smem_u32(stage), col_b, (int32_t)row0);
+            }
+            tma_store_commit();
+          }
+          box_busy = true;
         }
       } else {
         epilogue_tile(p, row, row_ok, t_row + half * (kPairBlockN / 2), col_half, kPairBlockN / 2, split_k,
@@ -542,7 +595,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 }
 
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& taux,
-                     GemmParams& p, cudaStream_t stream) {
+                     const CUtensorMap& tauxin, GemmParams& p, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   MRK_CUDA_OK(cudaGetDevice(&dev));
@@ -559,12 +612,19 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   p.num_splits = 1;
   const bool can_split = (p.flags & MRK_GEMM_OUT_F32) && (p.flags & MRK_GEMM_ACCUMULATE) &&
                          p.act == MRK_ACT_NONE && p.aux_mode == MRK_AUX_NONE && p.aux_out == nullptr;
-  if (can_split && tiles * 2 <= max_clusters && p.num_k_blocks >= 16) {
-    int want = max_clusters / tiles;
+  if (can_split && p.num_k_blocks >= 16) {
+    // Weight gradients have few output tiles and a long K: pick the number of K ranges whose units fill
+    // whole rounds of the clusters best.  Cost of `s` ranges, in k-blocks: rounds x (k-blocks per unit + a
+    // fixed charge per unit for pipeline fill and the extra pass over the output).
     const int max_by_k = p.num_k_blocks / 8;
-    if (want > max_by_k) want = max_by_k;
-    if (want > 32) want = 32;
-    if (want > 1) p.num_splits = want;
+    long long best_cost = 0;
+    for (int sp = 1; sp <= 32 && sp <= max_by_k; ++sp) {
+      const int kb = (p.num_k_blocks + sp - 1) / sp;
+      const int nsp = (p.num_k_blocks + kb - 1) / kb;
+      const long long rounds = ((long long)tiles * nsp + max_clusters - 1) / max_clusters;
+      const long long cost = rounds * (kb + 6);
+      if (sp == 1 || cost < best_cost) { best_cost = cost; p.num_splits = nsp; }
+    }
   }
   p.kb_per_split = (p.num_k_blocks + p.num_splits - 1) / p.num_splits;
   p.num_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
@@ -582,7 +642,7 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   if (p.comm.mode != 0 && p.comm.perm)
     p.comm.perm = (p.comm.seg_rows % kPairBlockM == 0 && p.num_m_blocks % p.comm.n == 0 && p.M % kPairBlockM == 0) ? 1 : 0;
   if (p.comm.mode == 1) {
-    MRK_REQUIRE(p.tma_store && p.num_splits == 1, "gemm_rs: the partial product must leave through TMA stores");
+    MRK_REQUIRE(p.tma_store == 1 && p.num_splits == 1, "gemm_rs: the partial product must leave through TMA stores");
     MRK_REQUIRE(p.comm.units_total == p.num_m_blocks * p.num_n_blocks * 4, "gemm_rs: flag array does not match the tiling");
     MRK_REQUIRE(p.comm.rs_queue != nullptr, "gemm_rs: no work queue");
     // compute clusters + reducer clusters, all resident at once (the reducers must run from the start)
@@ -607,9 +667,10 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (p.num_splits > 1) p.tma_store = 0;
+  if (p.num_splits > 1 && p.tma_store == 1) p.tma_store = 0;
   if (!p.tma_store) p.tma_store_aux = 0;
-  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, tc, taux, p));
+  if (p.tma_store != 1) p.tma_aux_in = 0;
+  MRK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel, ta, tb, tc, taux, tauxin, p));
   count_launch();
   return 0;
 }

@@ -72,6 +72,8 @@ def _declare(lib):
     sig("mrk_embedding_bwd", c_int, P, P, P, c_ll, c_int, c_int, c_int, c_int, P)
     sig("mrk_rope", c_int, P, P, P, P, P, c_ll, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, P)
     sig("mrk_swiglu_fwd", c_int, P, P, c_ll, c_int, c_ll, P)
+    sig("mrk_act_fwd", c_int, P, P, c_ll, c_int, P)
+    sig("mrk_act_bwd", c_int, P, P, P, P, c_ll, c_int, c_ll, c_int, P)
     sig("mrk_swiglu_bwd", c_int, P, P, P, c_ll, c_int, c_ll, P)
     sig("mrk_colsum", c_int, P, P, c_ll, c_int, c_ll, P)
     sig("mrk_dropout", c_int, P, P, c_ll, c_float, P, c_ull, P)

@@ -33,6 +33,40 @@ def colsum(x2: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor
 
 
 # ---------------------------------------------------------------------------------------------
+# activation between the two GEMMs of an MLP
+# ---------------------------------------------------------------------------------------------
+def _act_kernel_ok(*ts) -> bool:
+    return all(t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) == ts[0].stride(0)
+               and t.stride(0) % 8 == 0 and t.shape[1] % 8 == 0 and t.data_ptr() % 16 == 0 for t in ts)
+
+
+def act_forward(act: int, h: torch.Tensor) -> torch.Tensor:
+    """``act(h)`` for a 2-D bf16 tensor (one pass at memory speed)."""
+    from . import gemm as G
+    if not _lib.use_kernels(h) or not _act_kernel_ok(h) or not h.is_contiguous():
+        return G.act_forward(act, h.float()).to(h.dtype)
+    out = torch.empty_like(h)
+    _lib.check(_lib.kernels().mrk_act_fwd(h.data_ptr(), out.data_ptr(), h.numel(), act, _lib.stream_ptr()), "mrk_act_fwd")
+    return out
+
+
+def act_backward(act: int, d: torch.Tensor, h: torch.Tensor, colsum_out: Optional[torch.Tensor] = None):
+    """``d * act'(h)`` written over ``d`` (2-D bf16).  With ``colsum_out`` (fp32 ``[N]``) the column sums of the
+    result are added into it in the same pass: the bias gradient of the GEMM that produced ``h``."""
+    from . import gemm as G
+    if not _lib.use_kernels(d, h) or not _act_kernel_ok(d, h):
+        out = (d.float() * G.act_grad(act, h)).to(d.dtype)
+        if colsum_out is not None:
+            colsum_out.add_(out.float().sum(0))
+        return out
+    M, N = d.shape
+    _lib.check(_lib.kernels().mrk_act_bwd(d.data_ptr(), h.data_ptr(), d.data_ptr(),
+                                          colsum_out.data_ptr() if colsum_out is not None else None, M, N, d.stride(0),
+                                          act, _lib.stream_ptr()), "mrk_act_bwd")
+    return d
+
+
+# ---------------------------------------------------------------------------------------------
 # embedding (sum of up to three lookups, vocab-parallel aware)
 # ---------------------------------------------------------------------------------------------
 class _Embedding(torch.autograd.Function):

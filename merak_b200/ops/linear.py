@@ -1,9 +1,11 @@
 """Linear layers on the tcgen05 GEMM with hand-written backward passes.
 
 * ``linear(x, weight, bias, residual)``: ``y = x W^T + b (+ residual)``.
-* ``mlp(x, w1, b1, w2, b2, act, residual)``: ``act(x W1^T + b1) W2^T + b2 (+ residual)`` with the
-  activation applied in the first GEMM's epilogue and its derivative applied in the epilogue of
-  the backward data-gradient GEMM, so no elementwise kernel runs between the four GEMMs.
+* ``mlp(x, w1, b1, w2, b2, act, residual)``: ``act(x W1^T + b1) W2^T + b2 (+ residual)``.  The
+  activation is one memory-speed pass between the GEMMs, and in the backward pass one pass applies
+  its derivative and sums the bias gradient of the first GEMM.  (The GEMM can apply both in its
+  epilogue, ``FUSE_ACT_IN_GEMM``; at K = 1024 that made the epilogue warps the bottleneck:
+  0.218 + 0.196 ms fused against 0.116 + 0.045 and 0.103 + 0.06 ms for 16384 x 4096 x 1024.)
 
 Weight gradients are produced by transposed-operand GEMMs straight from the row-major
 activations (no transposes are materialised).  When a parameter carries an fp32 ``main_grad``
@@ -20,8 +22,11 @@ import torch.nn.functional as F
 
 from . import _lib, flop_counter
 from . import gemm as G
-from .elementwise import colsum
+from .elementwise import act_backward, act_forward, colsum
 from .norm import _param_grad
+
+
+FUSE_ACT_IN_GEMM = False
 
 
 def _as2d(x, K):
@@ -117,7 +122,11 @@ class _MLP(torch.autograd.Function):
         N = w2.shape[0]
         x2 = _as2d(x, K)
         r2 = _as2d(residual, N) if residual is not None else None
-        a, h = G.gemm(x2, w1, bias=b1, act=act, want_preact=True)
+        if FUSE_ACT_IN_GEMM or act == G.ACT_NONE:
+            a, h = G.gemm(x2, w1, bias=b1, act=act, want_preact=True)
+        else:
+            h, _ = G.gemm(x2, w1, bias=b1)
+            a = act_forward(act, h)
         y, _ = G.gemm(a, w2, bias=b2, aux_in=r2, aux_mode=G.AUX_ADD if r2 is not None else G.AUX_NONE)
         ctx.save_for_backward(x2, w1, b1, w2, b2, h, a)
         ctx.act, ctx.in_shape, ctx.has_res = act, x.shape, residual is not None
@@ -135,7 +144,14 @@ class _MLP(torch.autograd.Function):
             return dx_extra, None, None, None, None, None, None, None
         dy2 = _as2d(dy, N)
         # dh = (dy W2) * act'(h): derivative applied in the GEMM epilogue
-        dh, _ = G.gemm(dy2, w2, b_mn=True, act=ctx.act, aux_in=h, aux_mode=G.AUX_DACT)
+        db1_done = False
+        if FUSE_ACT_IN_GEMM or ctx.act == G.ACT_NONE:
+            dh, _ = G.gemm(dy2, w2, b_mn=True, act=ctx.act, aux_in=h, aux_mode=G.AUX_DACT)
+        else:
+            dh, _ = G.gemm(dy2, w2, b_mn=True)
+            mg1 = getattr(b1, "main_grad", None) if (b1 is not None and b1.requires_grad) else None
+            dh = act_backward(ctx.act, dh, h, mg1.view(-1) if mg1 is not None else None)
+            db1_done = mg1 is not None
         dw2 = _weight_grad(dy2, a, w2) if w2.requires_grad else None
         db2 = _bias_grad(dy2, b2)
         dx = None
@@ -144,7 +160,7 @@ class _MLP(torch.autograd.Function):
             dx2, _ = G.gemm(dh, w1, b_mn=True, aux_in=e2, aux_mode=G.AUX_ADD if e2 is not None else G.AUX_NONE)
             dx = dx2.view(ctx.in_shape)
         dw1 = _weight_grad(dh, x2, w1) if w1.requires_grad else None
-        db1 = _bias_grad(dh, b1)
+        db1 = None if db1_done else _bias_grad(dh, b1)
         return dx, dw1, db1, dw2, db2, None, (dy if ctx.has_res else None), None
 
 

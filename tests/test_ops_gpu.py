@@ -196,6 +196,32 @@ def test_linear_and_mlp_autograd():
     _lib.assert_status_ok("linear")
 
 
+@pytest.mark.parametrize("act", ["gelu_erf", "gelu_tanh", "relu", "silu"])
+@pytest.mark.parametrize("M,N", [(1000, 4096), (37, 264)])
+def test_activation_passes_between_the_mlp_gemms(act, M, N):
+    """act(h) and d * act'(h) with the bias-gradient column sums in the same pass, against fp32 PyTorch."""
+    from merak_b200.ops.elementwise import act_backward, act_forward
+    code = {"gelu_erf": G.ACT_GELU_ERF, "gelu_tanh": G.ACT_GELU_TANH, "relu": G.ACT_RELU, "silu": G.ACT_SILU}[act]
+    torch.manual_seed(0)
+    h = (torch.randn(M, N, device="cuda") * 2.5).bfloat16()
+    d = torch.randn(M, N, device="cuda").bfloat16()
+    hr = h.float().requires_grad_()
+    yr = G.act_forward(code, hr)
+    yr.backward(d.float())
+    y = act_forward(code, h)
+    torch.testing.assert_close(y.float(), yr.detach(), rtol=1e-2, atol=2e-3)
+    acc = torch.ones(N, device="cuda")
+    dh = act_backward(code, d.clone(), h, acc)
+    torch.testing.assert_close(dh.float(), hr.grad, rtol=1e-2, atol=3e-3)
+    torch.testing.assert_close(acc, 1.0 + dh.float().sum(0), rtol=1e-3, atol=1e-2)
+    # the tails of the erf polynomial: exact zero / identity far from the origin
+    far = torch.tensor([[-30.0, -6.0, 6.0, 30.0] * 2], device="cuda").bfloat16()
+    if act == "gelu_erf":
+        torch.testing.assert_close(act_forward(code, far).float(), F.gelu(far.float()), rtol=1e-2, atol=1e-3)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok("activation")
+
+
 @pytest.mark.parametrize("M,N,pitch", [(1000, 4096, 4096), (777, 30522, 30528), (513, 250, 256), (64, 30, 30)])
 def test_colsum_vector_and_ragged(M, N, pitch):
     """Column sums (bias gradients): 16-byte path for full and ragged widths with a padded pitch, scalar
