@@ -289,6 +289,199 @@ norm_bwd_kernel(const NormBwdParams p) {
   }
 }
 
+// -------------------------------------------------------------------------------------------------
+// One warp per row, for hidden sizes up to 1024 that are multiples of 256.  A lane holds V = H / 256
+// vectors of 8 values; sums are warp shuffles, so no warp ever waits for another one (the block-wide
+// kernels above spend most of a row at their barriers: 0.59 and 0.27 of the copy bandwidth at
+// H = 1024).  Same arithmetic and the same dropout counters as the block-wide kernels.
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+
+template <int V>
+__global__ void __launch_bounds__(128) norm_fwd_warp_kernel(const NormFwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_id = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const long long n_warps = (long long)gridDim.x * 4;
+  const bool drop = p.rng != nullptr && p.p_drop > 0.f;
+  const float keep_scale = drop ? 1.f / (1.f - p.p_drop) : 1.f;
+  unsigned long long seed = 0, offset = 0;
+  if (drop) { seed = p.rng[0]; offset = p.rng[1]; }
+  const float inv_h = 1.f / (float)p.H;
+  // gamma / beta of this lane's columns stay in registers for all rows
+  float g[V][8], bb[V][8];
+#pragma unroll
+  for (int it = 0; it < V; ++it) {
+    load8p(p.gamma, (lane + 32 * it) * 8, p.params_f32, g[it]);
+    if (p.beta) load8p(p.beta, (lane + 32 * it) * 8, p.params_f32, bb[it]);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bb[it][i] = 0.f;
+    }
+  }
+  for (long long row = warp_id; row < p.M; row += n_warps) {
+    uint4 rx[V], rr[V];
+#pragma unroll
+    for (int it = 0; it < V; ++it) {
+      rx[it] = __ldg(reinterpret_cast<const uint4*>(p.x + row * p.H + (lane + 32 * it) * 8));
+      if (p.residual) rr[it] = __ldg(reinterpret_cast<const uint4*>(p.residual + row * p.H + (lane + 32 * it) * 8));
+    }
+    float v[V][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < V; ++it) {
+      const int vi = lane + 32 * it;
+      const uint32_t w[4] = {rx[it].x, rx[it].y, rx[it].z, rx[it].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 t = unpack_bf16x2(w[i]); v[it][2 * i] = t.x; v[it][2 * i + 1] = t.y; }
+      if (drop) {
+        const unsigned long long e = (unsigned long long)row * p.H + (unsigned long long)vi * 8;
+        float r[8];
+        philox_uniform8(seed, offset + p.call_id, e, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[it][i] = r[i] < p.p_drop ? 0.f : v[it][i] * keep_scale;
+      }
+      if (p.residual) {
+        const uint32_t q[4] = {rr[it].x, rr[it].y, rr[it].z, rr[it].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = unpack_bf16x2(q[i]); v[it][2 * i] += t.x; v[it][2 * i + 1] += t.y; }
+      }
+      if (p.z) {
+        store8(p.z + row * p.H + vi * 8, v[it]);
+        // statistics are taken on the rounded values the backward pass will read
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[it][i] = __bfloat162float(__float2bfloat16(v[it][i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += p.rms ? v[it][i] * v[it][i] : v[it][i];
+    }
+    float mean = 0.f, rstd;
+    if (p.rms) {
+      rstd = rsqrtf(warp_sum(sum) * inv_h + p.eps);
+    } else {
+      mean = warp_sum(sum) * inv_h;
+      float sq = 0.f;
+#pragma unroll
+      for (int it = 0; it < V; ++it)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float d = v[it][i] - mean; sq += d * d; }
+      rstd = rsqrtf(warp_sum(sq) * inv_h + p.eps);
+    }
+    if (lane == 0) {
+      if (p.mean) p.mean[row] = mean;
+      if (p.rstd) p.rstd[row] = rstd;
+    }
+#pragma unroll
+    for (int it = 0; it < V; ++it) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = fmaf((v[it][i] - mean) * rstd, g[it][i], bb[it][i]);
+      store8(p.y + row * p.H + (lane + 32 * it) * 8, o);
+    }
+  }
+}
+
+template <int V>
+__global__ void __launch_bounds__(128) norm_bwd_warp_kernel(const NormBwdParams p) {
+  __shared__ float red[4][2][V * 256 + 8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warp_id = (long long)blockIdx.x * 4 + warp;
+  const long long n_warps = (long long)gridDim.x * 4;
+  const bool drop = p.rng != nullptr && p.p_drop > 0.f && p.dx != nullptr;
+  const float keep_scale = drop ? 1.f / (1.f - p.p_drop) : 1.f;
+  unsigned long long seed = 0, offset = 0;
+  if (drop) { seed = p.rng[0]; offset = p.rng[1]; }
+  const float inv_h = 1.f / (float)p.H;
+  float g[V][8], dg[V][8], db[V][8];
+#pragma unroll
+  for (int it = 0; it < V; ++it) {
+    load8p(p.gamma, (lane + 32 * it) * 8, p.params_f32, g[it]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dg[it][i] = 0.f; db[it][i] = 0.f; }
+  }
+  for (long long row = warp_id; row < p.M; row += n_warps) {
+    uint4 rdy[V], rz[V], rex[V];
+#pragma unroll
+    for (int it = 0; it < V; ++it) {
+      const long long off = row * p.H + (lane + 32 * it) * 8;
+      rdy[it] = __ldg(reinterpret_cast<const uint4*>(p.dy + off));
+      rz[it] = __ldg(reinterpret_cast<const uint4*>(p.z + off));
+      if (p.dz_extra) rex[it] = __ldg(reinterpret_cast<const uint4*>(p.dz_extra + off));
+    }
+    const float mean = p.mean ? p.mean[row] : 0.f;
+    const float rstd = p.rstd[row];
+    float xh[V][8], dxh[V][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < V; ++it) {
+      const uint32_t wd[4] = {rdy[it].x, rdy[it].y, rdy[it].z, rdy[it].w};
+      const uint32_t wz[4] = {rz[it].x, rz[it].y, rz[it].z, rz[it].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 d = unpack_bf16x2(wd[i]), z = unpack_bf16x2(wz[i]);
+        const float dyv[2] = {d.x, d.y}, zv[2] = {z.x, z.y};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int k = 2 * i + e;
+          xh[it][k] = (zv[e] - mean) * rstd;
+          dxh[it][k] = dyv[e] * g[it][k];
+          dg[it][k] += dyv[e] * xh[it][k];
+          db[it][k] += dyv[e];
+          s1 += dxh[it][k];
+          s2 += dxh[it][k] * xh[it][k];
+        }
+      }
+    }
+    s1 = p.rms ? 0.f : warp_sum(s1) * inv_h;
+    s2 = warp_sum(s2) * inv_h;
+#pragma unroll
+    for (int it = 0; it < V; ++it) {
+      const int vi = lane + 32 * it;
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = rstd * (dxh[it][i] - s1 - xh[it][i] * s2);
+      if (p.dz_extra) {
+        const uint32_t we[4] = {rex[it].x, rex[it].y, rex[it].z, rex[it].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = unpack_bf16x2(we[i]); o[2 * i] += t.x; o[2 * i + 1] += t.y; }
+      }
+      if (p.dres) store8(p.dres + row * p.H + vi * 8, o);
+      if (p.dx && p.dx != p.dres) {
+        if (drop) {
+          const unsigned long long e = (unsigned long long)row * p.H + (unsigned long long)vi * 8;
+          float r[8];
+          philox_uniform8(seed, offset + p.call_id, e, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = r[i] < p.p_drop ? 0.f : o[i] * keep_scale;
+        }
+        store8(p.dx + row * p.H + vi * 8, o);
+      }
+    }
+  }
+  // the four warps of the block add up their partial sums in shared memory, then the block adds
+  // them into one of kNormSlots accumulator rows (see norm_bwd_kernel)
+#pragma unroll
+  for (int it = 0; it < V; ++it)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      red[warp][0][(lane + 32 * it) * 8 + i] = dg[it][i];
+      red[warp][1][(lane + 32 * it) * 8 + i] = db[it][i];
+    }
+  __syncthreads();
+  float* pg = p.partial + (long long)(blockIdx.x % kNormSlots) * 2 * p.H;
+  for (int c = threadIdx.x * 4; c < 2 * p.H; c += 128 * 4) {
+    const int which = c / p.H, col = c % p.H;       // H is a multiple of 256: a group of 4 never straddles
+    float t[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      t[k] = red[0][which][col + k] + red[1][which][col + k] + red[2][which][col + k] + red[3][which][col + k];
+    red_add_f4(pg + which * p.H + col, t[0], t[1], t[2], t[3]);
+  }
+}
+
 __global__ void __launch_bounds__(256)
 norm_bwd_reduce_kernel(float* __restrict__ partial, int blocks, int H, float* __restrict__ dgamma,
                        float* __restrict__ dbeta) {
@@ -317,6 +510,20 @@ norm_bwd_reduce_kernel(float* __restrict__ partial, int blocks, int H, float* __
 
 using namespace mrk;
 
+// Grid of the warp-per-row kernels: every block resident at once (blocks of 128 threads, no dynamic
+// shared memory), or fewer when there is less work.  The occupancy query runs once per kernel.
+template <auto kernel>
+static unsigned resident_grid(long long want) {
+  static int per_sm = 0;          // one instance per kernel
+  if (per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 128, 0) != cudaSuccess || n < 1) n = 1;
+    per_sm = n;
+  }
+  const long long cap = (long long)sm_count() * per_sm;
+  return (unsigned)(want < cap ? want : cap);
+}
+
 template <int T, int V>
 static void launch_norm_fwd(const NormFwdParams& p, unsigned grid, cudaStream_t s) {
   norm_fwd_kernel<T, V><<<grid, T, 0, s>>>(p);
@@ -335,6 +542,18 @@ MRK_API int mrk_norm_fwd(const void* x, const void* residual, const void* gamma,
                   (__nv_bfloat16*)z, mean, rstd, (const unsigned long long*)rng, call_id, p_drop, eps, M, H, rms,
                   params_f32};
   cudaStream_t s = (cudaStream_t)stream;
+  if (H <= 1024 && H % 256 == 0) {
+    // one warp per row; as many blocks of four warps as are resident at once
+    const long long want = (M + 3) / 4;
+    switch (H / 256) {
+      case 1: norm_fwd_warp_kernel<1><<<resident_grid<norm_fwd_warp_kernel<1>>(want), 128, 0, s>>>(p); break;
+      case 2: norm_fwd_warp_kernel<2><<<resident_grid<norm_fwd_warp_kernel<2>>(want), 128, 0, s>>>(p); break;
+      case 3: norm_fwd_warp_kernel<3><<<resident_grid<norm_fwd_warp_kernel<3>>(want), 128, 0, s>>>(p); break;
+      default: norm_fwd_warp_kernel<4><<<resident_grid<norm_fwd_warp_kernel<4>>(want), 128, 0, s>>>(p); break;
+    }
+    MRK_CHECK_LAUNCH();
+    return 0;
+  }
   const long long cap = (long long)sm_count() * 32;
   const unsigned grid = (unsigned)(M < cap ? M : cap);
   if (H <= 1024) launch_norm_fwd<128, 1>(p, grid, s);
@@ -343,6 +562,26 @@ MRK_API int mrk_norm_fwd(const void* x, const void* residual, const void* gamma,
   else launch_norm_fwd<256, 4>(p, grid, s);
   MRK_CHECK_LAUNCH();
   return 0;
+}
+
+// The kernel that walks the rows (both entry points use the same one, so their results are identical).
+static void launch_norm_bwd_main(const NormBwdParams& p, cudaStream_t s) {
+  const long long M = p.M;
+  const int H = p.H;
+  const long long cap = (long long)sm_count() * 8;
+  const unsigned grid = (unsigned)(M < cap ? M : cap);
+  if (H <= 1024 && H % 256 == 0) {
+    const long long want = (M + 3) / 4;
+    switch (H / 256) {
+      case 1: norm_bwd_warp_kernel<1><<<resident_grid<norm_bwd_warp_kernel<1>>(want), 128, 0, s>>>(p); break;
+      case 2: norm_bwd_warp_kernel<2><<<resident_grid<norm_bwd_warp_kernel<2>>(want), 128, 0, s>>>(p); break;
+      case 3: norm_bwd_warp_kernel<3><<<resident_grid<norm_bwd_warp_kernel<3>>(want), 128, 0, s>>>(p); break;
+      default: norm_bwd_warp_kernel<4><<<resident_grid<norm_bwd_warp_kernel<4>>(want), 128, 0, s>>>(p); break;
+    }
+  } else if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
+  else if (H <= 2048) launch_norm_bwd<128, 2>(p, grid, s);
+  else if (H <= 4096) launch_norm_bwd<256, 2>(p, grid, s);
+  else launch_norm_bwd<256, 4>(p, grid, s);
 }
 
 // Number of workspace rows (each 2*H floats) mrk_norm_bwd may use.
@@ -359,12 +598,7 @@ MRK_API int mrk_norm_bwd(const void* dy, const void* z, const void* dz_extra, co
                   rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, workspace,
                   (const unsigned long long*)rng, call_id, p_drop, M, H, rms, params_f32};
   cudaStream_t s = (cudaStream_t)stream;
-  const long long cap = (long long)sm_count() * 8;
-  const unsigned grid = (unsigned)(M < cap ? M : cap);
-  if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
-  else if (H <= 2048) launch_norm_bwd<128, 2>(p, grid, s);
-  else if (H <= 4096) launch_norm_bwd<256, 2>(p, grid, s);
-  else launch_norm_bwd<256, 4>(p, grid, s);
+  launch_norm_bwd_main(p, s);
   MRK_CHECK_LAUNCH();
   dim3 rgrid((H + 31) / 32, 2);
   norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(workspace, kNormSlots, H, dgamma, dbeta);
@@ -421,15 +655,12 @@ MRK_API int mrk_norm_bwd_noalloc(const void* dy, const void* z, const void* dz_e
                   rstd, (__nv_bfloat16*)dres, (__nv_bfloat16*)dx, dgamma, dbeta, scratch,
                   nullptr, 0ull, 0.f, M, H, rms, params_f32};
   cudaStream_t s = (cudaStream_t)stream;
-  const long long cap = (long long)sm_count() * 8;
-  const unsigned grid = (unsigned)(M < cap ? M : cap);
   // Blocks add their partial sums into the kNormSlots accumulator rows; the reduction kernel sums
   // the rows and clears them, so a completed call leaves the array zero.  A call whose second
   // launch failed would leave partial sums behind, so the rows are also cleared up front (a
   // memset on the caller's stream; it allocates nothing).
   MRK_CUDA_OK(cudaMemsetAsync(scratch, 0, sizeof(float) * kNormSlots * 2 * kNoAllocMaxH, s));
-  if (H <= 1024) launch_norm_bwd<128, 1>(p, grid, s);
-  else launch_norm_bwd<128, 2>(p, grid, s);
+  launch_norm_bwd_main(p, s);
   MRK_CHECK_LAUNCH();
   dim3 rgrid((H + 31) / 32, 2);
   norm_bwd_reduce_kernel<<<rgrid, 256, 0, s>>>(scratch, kNormSlots, H, dgamma, dbeta);
