@@ -287,7 +287,13 @@ def run_reference(o, small=None):
 def main():
     o = parse()
     if o.impl == "reference":
-        run_reference(o)
+        # BENCH_REFERENCE_SMALL=1 shrinks the model so that the arm's plumbing can be exercised on a CPU box
+        # in a test; the printed config then says "small test shape" and the number means nothing
+        small = None
+        if os.environ.get("BENCH_REFERENCE_SMALL") == "1":
+            small = dict(vocab=512, hidden=64, layers=2, heads=4, ff=128)
+            o.mbs, o.seq = 2, 32
+        run_reference(o, small=small)
         return
     run_ours(o)
 

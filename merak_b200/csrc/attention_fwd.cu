@@ -66,7 +66,8 @@ __device__ __forceinline__ bool named_bar_any_nonzero(uint32_t bar_id, float v) 
 template <int D, int NT>
 __global__ void __launch_bounds__(AttnFwdSmem<D, NT>::kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                const __grid_constant__ CUtensorMap tv, const AttnFwdParams p) {
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap to,
+                const AttnFwdParams p) {
   using L = AttnFwdSmem<D, NT>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = 512;
@@ -121,6 +122,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     tma_prefetch_desc(&tq);
     tma_prefetch_desc(&tk);
     tma_prefetch_desc(&tv);
+    tma_prefetch_desc(&to);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -223,7 +225,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 }
 
 template <int D, int NT>
-static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                       const AttnFwdParams& p, cudaStream_t stream) {
   using L = AttnFwdSmem<D, NT>;
   static bool configured[64] = {false};
@@ -234,7 +236,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     configured[dev & 63] = true;
   }
   dim3 grid((p.Lq + 128 * NT - 1) / (128 * NT), p.H, p.B);
-  attn_fwd_kernel<D, NT><<<grid, L::kThreads, L::kTotal, stream>>>(tq, tk, tv, p);
+  attn_fwd_kernel<D, NT><<<grid, L::kThreads, L::kTotal, stream>>>(tq, tk, tv, to, p);
   MRK_CHECK_LAUNCH();
   return 0;
 }
@@ -267,6 +269,8 @@ MRK_API int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out,
   if ((rc = make_bshd_tmap(&tq, q, D, Lq, H, B, q_sb, q_ss, q_sh, 128))) return rc;
   if ((rc = make_bshd_tmap(&tk, k, D, Lk, Hkv, B, k_sb, k_ss, k_sh, 128))) return rc;
   if ((rc = make_bshd_tmap(&tv, v, D, Lk, Hkv, B, v_sb, v_ss, v_sh, 128))) return rc;
+  CUtensorMap to;
+  if ((rc = make_bshd_tmap(&to, out, D, Lq, H, B, o_sb, o_ss, o_sh, 128))) return rc;
   AttnFwdParams p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.o_sb = o_sb; p.o_ss = o_ss; p.o_sh = o_sh;
@@ -277,6 +281,6 @@ MRK_API int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out,
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "attention: status word unavailable");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 64) return Lq > 128 ? launch_fwd<64, 2>(tq, tk, tv, p, s) : launch_fwd<64, 1>(tq, tk, tv, p, s);
-  return launch_fwd<128, 1>(tq, tk, tv, p, s);
+  if (D == 64) return Lq > 128 ? launch_fwd<64, 2>(tq, tk, tv, to, p, s) : launch_fwd<64, 1>(tq, tk, tv, to, p, s);
+  return launch_fwd<128, 1>(tq, tk, tv, to, p, s);
 }

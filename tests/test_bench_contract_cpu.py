@@ -9,8 +9,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_reference_arm_reports_unavailable_or_runs():
+    # the model is shrunk on this CPU box (BERT-large would take minutes per step); the arm is otherwise the same
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1",
-                          "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=300)
+                          "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, BENCH_REFERENCE_SMALL="1"))
     assert res.returncode == 0, res.stderr[-2000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     out = json.loads(line)
