@@ -12,6 +12,17 @@ int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out, float* 
                  long long v_sb, long long v_ss, long long v_sh,
                  long long o_sb, long long o_ss, long long o_sh,
                  int causal, float scale, void* stream);
+// The same with dropout on the probabilities (attention_dropout.cuh): `rng` points at [seed, offset]
+// (two 64-bit words on the device), `call_id` distinguishes the attention calls of a step; the
+// backward call must get the same three values.
+int mrk_attn_fwd_drop(const void* q, const void* k, const void* v, void* out, float* lse,
+                      const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                      long long q_sb, long long q_ss, long long q_sh,
+                      long long k_sb, long long k_ss, long long k_sh,
+                      long long v_sb, long long v_ss, long long v_sh,
+                      long long o_sb, long long o_ss, long long o_sh,
+                      int causal, float scale, float p_drop, const void* rng, unsigned long long call_id,
+                      void* stream);
 #ifdef __cplusplus
 }
 #endif
@@ -24,6 +35,11 @@ int mrk_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
                  const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
                  const long long* strides, int causal, float scale, void* stream);
+int mrk_attn_bwd_drop(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                      const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                      const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                      const long long* strides, int causal, float scale, float p_drop, const void* rng,
+                      unsigned long long call_id, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -28,6 +28,7 @@
 #include "attention.h"
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "attention_dropout.cuh"
 #include <type_traits>
 
 namespace mrk {
@@ -49,6 +50,9 @@ struct AttnBwdParams {
   int B, H, Hkv, Lq, Lk;
   int causal;
   float scale, scale_log2;
+  float p_drop;                    // dropout on the probabilities (0 = off): same arguments as the forward call
+  const unsigned long long* rng;
+  unsigned long long call_id;
   unsigned* status;
 };
 
@@ -61,8 +65,8 @@ struct AttnBwdSmem {
   static constexpr int kStageOff = 2 * kTile;                    // [Q_j | dO_j] per stage
   static constexpr int kPOff = kStageOff + kStages * 2 * kTile;  // P^T   [128 kv][128 q] bf16
   static constexpr int kDSOff = kPOff + 32768;                   // dS^T
-  static constexpr int kStatOff = kDSOff + 32768;                // per compute warp: 2 x (lse2[64] | delta[64])
-  static constexpr int kBarOff = kStatOff + 8 * 2 * 128 * 4;
+  static constexpr int kStatOff = kDSOff + 32768;                // per compute warp: 2 x (lse2[64] | delta[64] | row key[64])
+  static constexpr int kBarOff = kStatOff + 8 * 2 * 192 * 4;
   static constexpr int kDQStageOff = kBarOff + 1024;             // D=64: one [32 q][32] fp32 tile per compute warp
   static constexpr int kTotal = kDQStageOff + (D == 64 ? 8 * 4096 : 0) + 1024;
 };
@@ -100,7 +104,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint64_t* sdp_free = dkv_full + 1;           // 1 (256 arrivals): S^T and dP^T are in registers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stat = reinterpret_cast<float*>(smem + L::kStatOff);  // [8 warps][2 buffers][lse2[64] | delta * scale[64]]
+  float* stat = reinterpret_cast<float*>(smem + L::kStatOff);  // [8 warps][2 buffers][lse2[64] | delta * scale[64] | dropout row key[64]]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_blk = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -283,7 +287,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
     // Every warp stages the statistics of its own 64 query columns (no barrier between warps):
     // lane l fetches lse (log2 units) and delta * scale of columns l and l + 32 of the warp's half.
-    struct Stat { float lse0, lse1, dl0, dl1; };
+    const bool drop = p.p_drop > 0.f;
+    const float keep_scale = drop ? 1.f / (1.f - p.p_drop) : 1.f;
+    const uint32_t drop_thresh = attn_drop_thresh(p.p_drop);
+    const uint32_t drop_base = drop ? attn_drop_base(p.rng[0], p.rng[1] + p.call_id) : 0u;
+    struct Stat { float lse0, lse1, dl0, dl1; uint32_t rk0, rk1; };
     auto load_stat = [&](int it) -> Stat {
       const int h = hkv * group + it / iters_per_head;
       const int q = (j_begin + it % iters_per_head) * 128 + wg * 64 + lane;
@@ -293,10 +301,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       v.lse1 = q + 32 < p.Lq ? __ldg(p.lse + off + 32) * 1.4426950408889634f : INFINITY;
       v.dl0 = q < p.Lq ? __ldg(p.delta + off) * p.scale : 0.f;
       v.dl1 = q + 32 < p.Lq ? __ldg(p.delta + off + 32) * p.scale : 0.f;
+      v.rk0 = drop ? attn_drop_rowkey(drop_base, (uint32_t)(b * p.H + h), (uint32_t)q) : 0u;
+      v.rk1 = drop ? attn_drop_rowkey(drop_base, (uint32_t)(b * p.H + h), (uint32_t)(q + 32)) : 0u;
       return v;
     };
     // P^T and dS^T of 32 query columns (col0 .. col0+31 of the block) of this thread's key row;
-    // `st` points at the 32 lse values of these columns, the delta values follow 64 floats later
+    // `st` points at the 32 lse values of these columns, the delta values follow 64 floats later and
+    // the dropout row keys 128 floats later
     // (`masked` is a compile-time tag: a per-element branch would end the basic block at every
     // element and leave each exp2 -> multiply -> pack chain exposed at its full latency)
     auto chunk = [&](auto masked, const uint32_t* s, const uint32_t* dp, const float* st, int col0, int q0,
@@ -318,12 +329,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
             const int i = i8 + j + e;
             const float x = fmaf(__uint_as_float(s[i]), p.scale_log2, kbias - lse8[j + e]);
             float pe = exp2f(x);
+            float mt = 1.f;        // dropout mask times 1 / (1 - p)
             if constexpr (decltype(masked)::value) {
               const int q = q0 + col0 + i;
               if (key >= p.Lk || (p.causal && key > q + shift)) pe = 0.f;
+              if (drop)
+                mt = attn_drop_keep(reinterpret_cast<const uint32_t*>(st)[128 + i], (uint32_t)key, drop_thresh) ? keep_scale : 0.f;
             }
-            pv[e] = pe;
-            dv_[e] = pe * fmaf(__uint_as_float(dp[i]), p.scale, -dl8[j + e]);   // delta was staged times scale
+            pv[e] = pe * mt;       // the dV product sees the dropped probabilities
+            dv_[e] = pe * fmaf(__uint_as_float(dp[i]) * mt, p.scale, -dl8[j + e]);   // delta was staged times scale
           }
           pk[(i8 + j) >> 1] = pack_bf16x2(pv[0], pv[1]);
           dsk[(i8 + j) >> 1] = pack_bf16x2(dv_[0], dv_[1]);
@@ -388,22 +402,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
     };
 
-    Stat stat_next = total_iters > 0 ? load_stat(0) : Stat{0.f, 0.f, 0.f, 0.f};
-    float* stat_w = stat + cw * 256;
+    Stat stat_next = total_iters > 0 ? load_stat(0) : Stat{0.f, 0.f, 0.f, 0.f, 0u, 0u};
+    float* stat_w = stat + cw * 384;
     for (int it = 0; it < total_iters && ok; ++it) {
       const int q0 = (j_begin + it % iters_per_head) * 128;
-      float* st = stat_w + (it & 1) * 128;
+      float* st = stat_w + (it & 1) * 192;
       st[lane] = stat_next.lse0;
       st[32 + lane] = stat_next.lse1;
       st[64 + lane] = stat_next.dl0;
       st[96 + lane] = stat_next.dl1;
+      reinterpret_cast<uint32_t*>(st)[128 + lane] = stat_next.rk0;
+      reinterpret_cast<uint32_t*>(st)[160 + lane] = stat_next.rk1;
       if (it + 1 < total_iters) stat_next = load_stat(it + 1);   // in flight during this block's work
       __syncwarp();
       ok = mbar_wait(smem_u32(sp_full), it & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool need_mask = (key >= p.Lk) || (p.causal && (k0 + 127 > q0 + shift));
+      const bool need_mask = (key >= p.Lk) || (p.causal && (k0 + 127 > q0 + shift)) || drop;
       if constexpr (D == 64) {
         // two halves of 32 columns: the second half's TMEM loads are in flight while the first half
         // is stored, and the element-wise step never holds more than 64 inputs in registers
@@ -616,11 +632,13 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 using namespace mrk;
 
-MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                         const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
-                         const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
-                         const long long* strides /* q,k,v,o,do,dq,dk,dv: (sb,ss,sh) each = 24 values */,
-                         int causal, float scale, void* stream) {
+MRK_API int mrk_attn_bwd_drop(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                              const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                              const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                              const long long* strides /* q,k,v,o,do,dq,dk,dv: (sb,ss,sh) each = 24 values */,
+                              int causal, float scale, float p_drop, const void* rng, unsigned long long call_id,
+                              void* stream) {
+  MRK_REQUIRE(p_drop >= 0.f && p_drop < 1.f && (p_drop == 0.f || rng != nullptr), "attention backward: bad dropout arguments");
   MRK_REQUIRE(D == 64 || D == 128, "attention backward: head dim %d not supported (64 or 128)", D);
   MRK_REQUIRE(B > 0 && H > 0 && Hkv > 0 && Lq > 0 && Lk > 0 && H % Hkv == 0, "attention backward: bad sizes");
   const long long* sq = strides, *sk = strides + 3, *sv = strides + 6, *so = strides + 9, *sdo = strides + 12,
@@ -665,6 +683,7 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
   p.key_bias = key_bias;
   p.B = B; p.H = H; p.Hkv = Hkv; p.Lq = Lq; p.Lk = Lk; p.causal = causal;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.p_drop = p_drop; p.rng = reinterpret_cast<const unsigned long long*>(rng); p.call_id = call_id;
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "attention backward: status word unavailable");
   rc = (D == 64) ? launch_bwd<64>(tq, tk, tv, tdo, tdq, tdk, tdv, p, s)
@@ -678,4 +697,12 @@ MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void
     MRK_CHECK_LAUNCH();
   }
   return 0;
+}
+
+MRK_API int mrk_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                         const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                         const long long* strides, int causal, float scale, void* stream) {
+  return mrk_attn_bwd_drop(q, k, v, o, dout, lse, delta, dq_acc, dq, dk, dv, key_bias, B, H, Hkv, Lq, Lk, D, strides,
+                           causal, scale, 0.f, nullptr, 0ull, stream);
 }

@@ -21,6 +21,7 @@
 #include "attention.h"
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "attention_dropout.cuh"
 
 namespace mrk {
 
@@ -34,6 +35,9 @@ struct AttnFwdParams {
   int B, H, Hkv, Lq, Lk;
   int causal;
   float scale_log2;             // softmax scale * log2(e)
+  float p_drop;                 // dropout on the probabilities (0 = off)
+  const unsigned long long* rng;   // [seed, offset] on the device when p_drop > 0
+  unsigned long long call_id;
   unsigned* status;
 };
 
@@ -253,13 +257,15 @@ int make_bshd_tmap(CUtensorMap* out, const void* base, int D, int L, int H, int 
 
 using namespace mrk;
 
-MRK_API int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
-                         const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
-                         long long q_sb, long long q_ss, long long q_sh,
-                         long long k_sb, long long k_ss, long long k_sh,
-                         long long v_sb, long long v_ss, long long v_sh,
-                         long long o_sb, long long o_ss, long long o_sh,
-                         int causal, float scale, void* stream) {
+MRK_API int mrk_attn_fwd_drop(const void* q, const void* k, const void* v, void* out, float* lse,
+                              const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                              long long q_sb, long long q_ss, long long q_sh,
+                              long long k_sb, long long k_ss, long long k_sh,
+                              long long v_sb, long long v_ss, long long v_sh,
+                              long long o_sb, long long o_ss, long long o_sh,
+                              int causal, float scale, float p_drop, const void* rng, unsigned long long call_id,
+                              void* stream) {
+  MRK_REQUIRE(p_drop >= 0.f && p_drop < 1.f && (p_drop == 0.f || rng != nullptr), "attention: bad dropout arguments");
   MRK_REQUIRE(D == 64 || D == 128, "attention: head dim %d not supported (64 or 128)", D);
   MRK_REQUIRE(B > 0 && H > 0 && Hkv > 0 && Lq > 0 && Lk > 0 && H % Hkv == 0, "attention: bad sizes");
   MRK_REQUIRE((o_ss % 8) == 0 && (o_sh % 8) == 0 && (o_sb % 8) == 0 && ((uintptr_t)out & 15) == 0,
@@ -278,9 +284,23 @@ MRK_API int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out,
   p.B = B; p.H = H; p.Hkv = Hkv; p.Lq = Lq; p.Lk = Lk;
   p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.p_drop = p_drop;
+  p.rng = reinterpret_cast<const unsigned long long*>(rng);
+  p.call_id = call_id;
   p.status = status_word_device();
   MRK_REQUIRE(p.status != nullptr, "attention: status word unavailable");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 64) return Lq > 128 ? launch_fwd<64, 2>(tq, tk, tv, to, p, s) : launch_fwd<64, 1>(tq, tk, tv, to, p, s);
   return launch_fwd<128, 1>(tq, tk, tv, to, p, s);
+}
+
+MRK_API int mrk_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                         const float* key_bias, int B, int H, int Hkv, int Lq, int Lk, int D,
+                         long long q_sb, long long q_ss, long long q_sh,
+                         long long k_sb, long long k_ss, long long k_sh,
+                         long long v_sb, long long v_ss, long long v_sh,
+                         long long o_sb, long long o_ss, long long o_sh,
+                         int causal, float scale, void* stream) {
+  return mrk_attn_fwd_drop(q, k, v, out, lse, key_bias, B, H, Hkv, Lq, Lk, D, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh,
+                           v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, causal, scale, 0.f, nullptr, 0ull, stream);
 }

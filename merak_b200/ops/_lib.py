@@ -59,6 +59,8 @@ def _declare(lib):
     P = c_void_p
     sig("mrk_attn_fwd", c_int, *([P] * 6 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, P]))
     sig("mrk_attn_bwd", c_int, *([P] * 12 + [c_int] * 6 + [P, c_int, c_float, P]))
+    sig("mrk_attn_fwd_drop", c_int, *([P] * 6 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, c_float, P, c_ull, P]))
+    sig("mrk_attn_bwd_drop", c_int, *([P] * 12 + [c_int] * 6 + [P, c_int, c_float, c_float, P, c_ull, P]))
     sig("mrk_norm_fwd", c_int, P, P, P, P, P, P, P, P, P, c_ull, c_float, c_float, c_ll, c_int, c_int, c_int, P)
     sig("mrk_norm_bwd", c_int, P, P, P, P, P, P, P, P, P, P, P, P, c_ull, c_float, c_ll, c_int, c_int, c_int, P)
     sig("mrk_norm_bwd_workspace_rows", c_int)

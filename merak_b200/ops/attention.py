@@ -19,6 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib, flop_counter
+from .rng import dropout_state
 
 def _declare():
     _lib.kernels()
@@ -43,11 +44,36 @@ def attention_reference(q, k, v, key_bias=None, causal=False, scale=None):
     return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
 
 
+def _mix32(x: torch.Tensor) -> torch.Tensor:
+    m = 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    x = (x * 0x85EBCA6B) & m
+    x = x ^ (x >> 13)
+    x = (x * 0xC2B2AE35) & m
+    return x ^ (x >> 16)
+
+
+def dropout_keep_mask(seed: int, stream: int, B: int, H: int, Lq: int, Lk: int, p: float, device) -> torch.Tensor:
+    """The keep mask ``[B, H, Lq, Lk]`` (bool) the flash kernels use for dropout probability ``p`` and generator
+    state ``(seed, stream = offset + call id)``: the same stateless hash as ``csrc/attention_dropout.cuh``,
+    evaluated with int64 tensors.  For tests and for reproducing a run's masks."""
+    m = 0xFFFFFFFF
+    t = lambda v: torch.tensor(int(v) & m, dtype=torch.int64, device=device)
+    base = _mix32(t(seed) ^ _mix32((t(seed >> 32) + 0x9E3779B9) & m)
+                  ^ _mix32(((t(stream) * 0x9E3779B1) + t(stream >> 32)) & m))
+    bh = torch.arange(B * H, dtype=torch.int64, device=device).view(B, H, 1, 1)
+    q = torch.arange(Lq, dtype=torch.int64, device=device).view(1, 1, Lq, 1)
+    k = torch.arange(Lk, dtype=torch.int64, device=device).view(1, 1, 1, Lk)
+    rowkey = _mix32((_mix32(base ^ ((bh * 0x85EBCA6B) & m)) + q * 0xC2B2AE35) & m)
+    thresh = min(int(float(torch.tensor(p, dtype=torch.float32).item()) * 4294967296.0), m)
+    return _mix32(rowkey ^ ((k * 0x9E3779B1) & m)) >= thresh
+
+
 def attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p):
     """Attention with dropout on the probabilities (the eager ``matmul -> softmax -> dropout -> matmul``
-    of the reference's models).  The flash kernels have no dropout, so this is PyTorch's
-    ``scaled_dot_product_attention`` (announced once through ``note_library_fallback`` on CUDA); tensors are
-    ``[B, L, H, D]`` as everywhere in this module."""
+    of the reference's models) for the cases the flash kernels do not take (CPU, dtypes other than bf16, head
+    dims other than 64 / 128): PyTorch's ``scaled_dot_product_attention``, announced once through
+    ``note_library_fallback`` on CUDA; tensors are ``[B, L, H, D]`` as everywhere in this module."""
     _lib.note_library_fallback("attention with dropout on the probabilities", q)
     B, Lq, H, D = q.shape
     Hkv = k.shape[2]
@@ -75,10 +101,18 @@ def _tma_ok(t) -> bool:
                                                                   for s in _strides3(t)))
 
 
+def _dropout_args(dropout_p: float, device):
+    """(generator state tensor or None, call id) of one attention call; the backward pass reuses both."""
+    if dropout_p <= 0.0:
+        return None, 0
+    st = dropout_state()
+    return st.tensor(device), st.next_call_id()
+
+
 class _FlashAttention(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, q, k, v, key_bias, causal, scale):
+    def forward(ctx, q, k, v, key_bias, causal, scale, dropout_p=0.0):
         _declare()
         B, Lq, H, D = q.shape
         Lk, Hkv = k.shape[1], k.shape[2]
@@ -86,18 +120,19 @@ class _FlashAttention(torch.autograd.Function):
         out = torch.empty((B, Lq, H, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
         kb = key_bias.float().contiguous() if key_bias is not None else None
-        rc = _lib.kernels().mrk_attn_fwd(
+        rng, call_id = _dropout_args(dropout_p, q.device)
+        rc = _lib.kernels().mrk_attn_fwd_drop(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(kb),
             B, H, Hkv, Lq, Lk, D, *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
-            int(causal), float(scale), _lib.stream_ptr())
+            int(causal), float(scale), float(dropout_p), _lib.ptr(rng), call_id, _lib.stream_ptr())
         _lib.check(rc, "mrk_attn_fwd")
-        ctx.save_for_backward(q, k, v, out, lse, kb)
-        ctx.causal, ctx.scale = causal, scale
+        ctx.save_for_backward(q, k, v, out, lse, kb, rng)
+        ctx.causal, ctx.scale, ctx.drop = causal, scale, (float(dropout_p), call_id)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, lse, kb = ctx.saved_tensors
+        q, k, v, out, lse, kb, rng = ctx.saved_tensors
         B, Lq, H, D = q.shape
         Lk, Hkv = k.shape[1], k.shape[2]
         if not _tma_ok(dout):
@@ -111,13 +146,13 @@ class _FlashAttention(torch.autograd.Function):
         for t in (q, k, v, out, dout, dq, dk, dv):
             strides.extend(_strides3(t))
         arr = (ctypes.c_longlong * 24)(*strides)
-        rc = _lib.kernels().mrk_attn_bwd(
+        rc = _lib.kernels().mrk_attn_bwd_drop(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
             delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(kb),
             B, H, Hkv, Lq, Lk, D, ctypes.cast(arr, ctypes.c_void_p), int(ctx.causal), float(ctx.scale),
-            _lib.stream_ptr())
+            ctx.drop[0], _lib.ptr(rng), ctx.drop[1], _lib.stream_ptr())
         _lib.check(rc, "mrk_attn_bwd")
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 class _FlashAttentionPacked(torch.autograd.Function):
@@ -126,7 +161,7 @@ class _FlashAttentionPacked(torch.autograd.Function):
     tensor, so no per-slice gradient tensors are materialised and summed."""
 
     @staticmethod
-    def forward(ctx, qkv, hq, hkv, key_bias, causal, scale):
+    def forward(ctx, qkv, hq, hkv, key_bias, causal, scale, dropout_p=0.0):
         if not _tma_ok(qkv):
             qkv = qkv.contiguous()
         B, L, _, D = qkv.shape
@@ -134,19 +169,20 @@ class _FlashAttentionPacked(torch.autograd.Function):
         out = torch.empty((B, L, hq, D), dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty((B, hq, L), dtype=torch.float32, device=qkv.device)
         kb = key_bias.float().contiguous() if key_bias is not None else None
-        rc = _lib.kernels().mrk_attn_fwd(
+        rng, call_id = _dropout_args(dropout_p, qkv.device)
+        rc = _lib.kernels().mrk_attn_fwd_drop(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(kb),
             B, hq, hkv, L, L, D, *_strides3(q), *_strides3(k), *_strides3(v), *_strides3(out),
-            int(causal), float(scale), _lib.stream_ptr())
+            int(causal), float(scale), float(dropout_p), _lib.ptr(rng), call_id, _lib.stream_ptr())
         _lib.check(rc, "mrk_attn_fwd")
-        ctx.save_for_backward(qkv, out, lse, kb)
-        ctx.meta = (hq, hkv, causal, scale)
+        ctx.save_for_backward(qkv, out, lse, kb, rng)
+        ctx.meta = (hq, hkv, causal, scale, float(dropout_p), call_id)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, out, lse, kb = ctx.saved_tensors
-        hq, hkv, causal, scale = ctx.meta
+        qkv, out, lse, kb, rng = ctx.saved_tensors
+        hq, hkv, causal, scale, p_drop, call_id = ctx.meta
         B, L, _, D = qkv.shape
         if not _tma_ok(dout):
             dout = dout.contiguous()
@@ -159,12 +195,13 @@ class _FlashAttentionPacked(torch.autograd.Function):
         for t in (q, k, v, out, dout, dq, dk, dv):
             strides.extend(_strides3(t))
         arr = (ctypes.c_longlong * 24)(*strides)
-        rc = _lib.kernels().mrk_attn_bwd(
+        rc = _lib.kernels().mrk_attn_bwd_drop(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
             delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(kb),
-            B, hq, hkv, L, L, D, ctypes.cast(arr, ctypes.c_void_p), int(causal), float(scale), _lib.stream_ptr())
+            B, hq, hkv, L, L, D, ctypes.cast(arr, ctypes.c_void_p), int(causal), float(scale), p_drop, _lib.ptr(rng),
+            call_id, _lib.stream_ptr())
         _lib.check(rc, "mrk_attn_bwd")
-        return dqkv, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None
 
 
 def flash_attention_packed(qkv: torch.Tensor, num_q_heads: int, num_kv_heads: int,
@@ -174,18 +211,16 @@ def flash_attention_packed(qkv: torch.Tensor, num_q_heads: int, num_kv_heads: in
     ``dropout_p`` > 0 (pass it in training mode only) drops attention probabilities."""
     D = qkv.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if dropout_p > 0.0:
-        q, k, v = (qkv[:, :, :num_q_heads], qkv[:, :, num_q_heads:num_q_heads + num_kv_heads],
-                   qkv[:, :, num_q_heads + num_kv_heads:])
-        return attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p)
     if not _lib.use_kernels(qkv) or qkv.dtype != torch.bfloat16 or D not in (64, 128):
-        _lib.note_library_fallback("attention", qkv)
         q, k, v = (qkv[:, :, :num_q_heads], qkv[:, :, num_q_heads:num_q_heads + num_kv_heads],
                    qkv[:, :, num_q_heads + num_kv_heads:])
+        if dropout_p > 0.0:
+            return attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p)
+        _lib.note_library_fallback("attention", qkv)
         return attention_reference(q, k, v, key_bias, causal, scale)
     if flop_counter.enabled():
         flop_counter.add(4 * qkv.shape[0] * num_q_heads * qkv.shape[1] * qkv.shape[1] * D // (2 if causal else 1))
-    return _FlashAttentionPacked.apply(qkv, num_q_heads, num_kv_heads, key_bias, causal, scale)
+    return _FlashAttentionPacked.apply(qkv, num_q_heads, num_kv_heads, key_bias, causal, scale, float(dropout_p))
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
@@ -198,12 +233,12 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     """
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if dropout_p > 0.0:
-        return attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p)
-    if not _lib.use_kernels(q, k, v):
+    if not _lib.use_kernels(q, k, v) or q.dtype != torch.bfloat16 or D not in (64, 128):
+        if dropout_p > 0.0:
+            return attention_with_dropout(q, k, v, key_bias, causal, scale, dropout_p)
+        if _lib.use_kernels(q, k, v):
+            _lib.note_library_fallback("attention", q)
         return attention_reference(q, k, v, key_bias, causal, scale)
     if flop_counter.enabled():
         flop_counter.add(4 * q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1] * D // (2 if causal else 1))
-    assert q.dtype == torch.bfloat16, "tcgen05 attention takes bf16"
-    assert D in (64, 128), "head_dim must be 64 or 128 on the sm_100a path"
-    return _FlashAttention.apply(q, k, v, key_bias, causal, scale)
+    return _FlashAttention.apply(q, k, v, key_bias, causal, scale, float(dropout_p))
