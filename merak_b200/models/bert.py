@@ -8,7 +8,7 @@ headline example (examples/bert_pretraining/run_bert.py:61-117) and of its BERT 
 ``query/key/value`` so checkpoints interchange.
 
 Per layer: fused QKV GEMM -> flash attention (bidirectional, optional key-padding bias) ->
-output GEMM -> fused dropout+residual+LayerNorm -> MLP (GELU in the GEMM epilogue) -> fused
+output GEMM -> fused dropout+residual+LayerNorm -> MLP (GEMM, GELU pass, GEMM) -> fused
 dropout+residual+LayerNorm.
 """
 from __future__ import annotations

@@ -1,6 +1,6 @@
 """GPT-2 decoder with Hugging Face parameter names (``transformer.h.{i}.attn.c_attn`` ...), built
 on the framework's kernels: fused QKV GEMM -> flash attention -> projection GEMM with residual
-epilogue, fused residual+LayerNorm, MLP with the GELU applied in the GEMM epilogue.
+epilogue, fused residual+LayerNorm, MLP (GEMM, activation pass at memory speed, GEMM).
 
 The module tree and names follow ``transformers``' ``GPT2LMHeadModel`` so the reference's GPT-2
 feature dict (Merak/core/tensor_parallel/mp_mapping.py:21-29: c_attn/c_fc column-parallel,
