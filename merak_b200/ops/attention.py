@@ -106,7 +106,9 @@ def _dropout_args(dropout_p: float, device):
     if dropout_p <= 0.0:
         return None, 0
     st = dropout_state()
-    return st.tensor(device), st.next_call_id()
+    # heads are what tensor parallelism shards: the rank-dependent generator, so that two ranks' local head
+    # 0 do not share a mask (with one rank per replica the two generators coincide)
+    return st.tensor(device, sharded=True), st.next_call_id()
 
 
 class _FlashAttention(torch.autograd.Function):

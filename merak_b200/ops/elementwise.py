@@ -262,5 +262,5 @@ def dropout(x: torch.Tensor, p: float, training: bool = True) -> torch.Tensor:
     if p <= 0.0 or not training:
         return x
     if not _lib.use_kernels(x) or x.dtype != torch.bfloat16 or x.numel() % 8 != 0:
-        return F.dropout(x, p, True)
+        return dropout_state().host_dropout(x, p)
     return _Dropout.apply(x, p)

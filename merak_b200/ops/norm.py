@@ -19,7 +19,7 @@ from .rng import dropout_state
 def norm_reference(x, residual, weight, bias, eps, rms, p_drop=0.0, training=True):
     z = x.float()
     if p_drop > 0.0 and training:
-        z = F.dropout(z, p_drop, True)
+        z = dropout_state().host_dropout(z, p_drop)
     if residual is not None:
         z = z + residual.float()
     z = z.to(x.dtype)

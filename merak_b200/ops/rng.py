@@ -78,6 +78,37 @@ class DropoutState:
         finally:
             self.default_kind = prev
 
+    # --- masks for the PyTorch fallback paths ---------------------------------------------------
+    def host_keep_mask(self, shape, p: float, device, sharded: bool | None = None) -> torch.Tensor:
+        """Boolean keep mask for tensors the kernels do not take (CPU, dtypes other than bf16).  Like the
+        kernels' masks it is a pure function of (seed of the chosen generator, offset + call id, element
+        index), so it does not depend on how much any torch generator was used before, agrees on every rank
+        that shares the seed, and a recomputed forward pass regenerates it from the restored call id."""
+        kind = self.default_kind if sharded is None else ("sharded" if sharded else "replicated")
+        seed, stream = int(self.seeds[kind]), self._offset() + self.next_call_id()
+        m = 0xFFFFFFFF
+
+        def mix(x):
+            x = x ^ (x >> 16)
+            x = (x * 0x85EBCA6B) & m
+            x = x ^ (x >> 13)
+            x = (x * 0xC2B2AE35) & m
+            return x ^ (x >> 16)
+
+        t = lambda v: torch.tensor(int(v) & m, dtype=torch.int64, device=device)
+        base = mix(t(seed) ^ mix((t(seed >> 32) + 0x9E3779B9) & m) ^ mix(((t(stream) * 0x9E3779B1) + t(stream >> 32)) & m))
+        n = 1
+        for d in shape:
+            n *= int(d)
+        idx = torch.arange(n, dtype=torch.int64, device=device)
+        bits = mix((mix(base ^ (idx & m)) + (idx >> 32) * 0xC2B2AE35) & m)
+        thresh = min(int(float(p) * 4294967296.0), m)
+        return (bits >= thresh).view(tuple(shape))
+
+    def host_dropout(self, x: torch.Tensor, p: float, sharded: bool | None = None) -> torch.Tensor:
+        keep = self.host_keep_mask(x.shape, p, x.device, sharded)
+        return x * keep.to(x.dtype) * (1.0 / (1.0 - p))
+
     # --- call numbering -------------------------------------------------------------------------
     def next_call_id(self) -> int:
         self.call_id += 1

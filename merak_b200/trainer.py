@@ -224,6 +224,11 @@ class MerakTrainer:
                                      optimizer_factory=(lambda p: self.create_optimizer(p)) if self._wants_custom_optimizer() else None,
                                      lr_scheduler_factory=self.create_lr_scheduler)
         self.optimizer, self.lr_scheduler = self.engine.optimizer, self.engine.lr_scheduler
+        # Tracing, sharding and the tensor-parallel rebuild have drawn from the default generators since the
+        # seeds were set, and not the same amount on every rank (a rank builds the layers of its own stage,
+        # rank 0 writes caches).  Training starts from the seeded state again, so that ranks of one
+        # tensor-parallel group draw the same dropout masks for the activations they all hold.
+        model_parallel_manual_seed(a.seed)
         return self.engine
 
     def _wants_custom_optimizer(self) -> bool:

@@ -55,8 +55,15 @@ def main():
     ap.add_argument("--dp_bucket", type=int, default=8 << 20)
     ap.add_argument("--inject_overflow", type=int, default=-1, help="step whose gradients get an inf written in")
     ap.add_argument("--user_opt", default="", help="sgd | adamw: a torch.optim optimizer built by the trainer hook")
+    ap.add_argument("--dropout", type=float, default=0.0, help="hidden, embedding and attention dropout of the model")
+    ap.add_argument("--attn_dropout", type=float, default=-1.0, help="attention dropout alone (default: --dropout)")
+    ap.add_argument("--check_replicated", type=int, default=0,
+                    help="after training: parameters that are not tensor-parallel must be bit-identical on every "
+                         "rank of the tensor-parallel group")
     ap.add_argument("--out", required=True)
     o = ap.parse_args()
+    if o.attn_dropout < 0:
+        o.attn_dropout = o.dropout
 
     Merak.init(o.pp, o.tp, o.dp, sp=o.sp, ep=o.ep, backend="gloo" if o.device == "cpu" else "nccl")
     torch.manual_seed(1234)
@@ -66,12 +73,12 @@ def main():
     build_ctx.__enter__()
     if o.model == "gpt2":
         over = dict(n_head=o.n_head, n_embd=32 * o.n_head) if o.n_head else {}
-        model = GPT2LMHeadModel(gpt2_config("gpt2-tiny", vocab_size=V, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
-                                            **over))
+        model = GPT2LMHeadModel(gpt2_config("gpt2-tiny", vocab_size=V, resid_pdrop=o.dropout, embd_pdrop=o.dropout,
+                                            attn_pdrop=o.attn_dropout, **over))
         task = "causal"
     elif o.model == "bert":
-        model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=0.0,
-                                            attention_probs_dropout_prob=0.0))
+        model = BertForMaskedLM(bert_config("bert-tiny", vocab_size=V, hidden_dropout_prob=o.dropout,
+                                            attention_probs_dropout_prob=o.attn_dropout))
         task = "mlm"
     elif o.model == "moe":
         from merak_b200.models.moe import DeepseekV2ForCausalLM, deepseek_v2_config
@@ -122,6 +129,18 @@ def main():
             scales.append(engine.loss_scaler.cur_scale)
             skipped.append(bool(torch.equal(before, engine.flat.model)))
         trainer.params.step()
+    if o.check_replicated:
+        from merak_b200.parallel import mpu
+        group = mpu.get_model_parallel_group()
+        n = torch.distributed.get_world_size(group)
+        for name, prm in engine.module.named_parameters():
+            if getattr(prm, "model_parallel", False):
+                continue
+            mine = prm.detach().float().contiguous()
+            every = [torch.empty_like(mine) for _ in range(n)]
+            torch.distributed.all_gather(every, mine, group=group)
+            for r, other in enumerate(every):
+                assert torch.equal(other, every[0]), "replicated parameter %s differs on tensor-parallel rank %d" % (name, r)
     if o.save_dir:
         trainer.save_checkpoint()
     if torch.distributed.get_rank() == 0:

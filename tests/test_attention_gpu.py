@@ -110,7 +110,7 @@ def test_attention_probability_dropout_against_the_same_mask(case):
         kb = torch.zeros(B, Lk, device="cuda")
         kb[:, Lk - Lk // 3:] = -30000.0
     out = flash_attention(q, k, v, key_bias=kb, causal=causal, dropout_p=p)
-    seed, offset = (int(x) for x in st.tensor(q.device).tolist())
+    seed, offset = (int(x) for x in st.tensor(q.device, sharded=True).tolist())
     call_id = st.get_call_id()
     dout = torch.randn_like(out)
     out.backward(dout)

@@ -198,6 +198,18 @@ def _run(tmp, name, world, extra):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("model", ["gpt2", "bert"])
+def test_tp2_dropout_keeps_replicated_parameters_identical(tmp_path, model):
+    """Tensor parallelism with dropout switched on (hidden, embedding, attention probabilities): activations
+    every rank holds get the same mask on every rank, so parameters that are not sharded (norms, row-parallel
+    biases, position embeddings) receive identical gradients and stay bit-identical; the script checks that
+    after the last step and fails otherwise."""
+    losses = _run(tmp_path, "tp2_dropout", 2, ["--model", model, "--tp", "2", "--steps", "5", "--gas", "2",
+                                               "--dropout", "0.1", "--check_replicated", "1"])
+    assert all(l == l for l in losses) and losses[-1] < losses[0] + 0.5
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("model", ["gpt2", "bert"])
 def test_fused_dp_matches_nccl_two_gpus(tmp_path, model):
     base = ["--model", model, "--dp", "2", "--steps", "6", "--gas", "2"]
     ref = _run(tmp_path, "nccl", 2, base + ["--comm", "nccl"])

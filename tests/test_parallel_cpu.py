@@ -148,6 +148,16 @@ def test_pp2_dp2_layer_split_4ranks(tmp_path, baseline):
     assert_close(got, baseline["gpt2"])
 
 
+@pytest.mark.parametrize("model", ["gpt2", "bert"])
+def test_tp2_dropout_keeps_replicated_parameters_identical(tmp_path, model):
+    """Dropout switched on under tensor parallelism: activations every rank holds get the same mask on every
+    rank (the masks are a function of the replicated seed, the step and the call number, not of how much a
+    torch generator was used), so parameters that are not sharded stay bit-identical; the script asserts it."""
+    losses = run_layout(tmp_path, "tp2_dropout_" + model, 2, ["--model", model, "--tp", "2", "--steps", "4", "--gas", "2",
+                                                             "--dropout", "0.1", "--check_replicated", "1"])
+    assert all(l == l for l in losses)
+
+
 def test_ulysses_sp2_matches_single(tmp_path, baseline):
     got = run_layout(tmp_path, "sp2", 2, ["--sp", "2", "--model", "llama"])
     assert_close(got, baseline["llama"])
