@@ -25,21 +25,27 @@ TINY = dict(
 )
 
 
-def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, config_overrides=None):
+def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, config_overrides=None,
+        tiny_overrides=None, loss_fn=None):
     """``tp_lists``: (column-parallel names, row-parallel names) for models without a built-in feature
     dict, the counterpart of the reference scripts' ``set_tp_layer_lists`` calls
-    (examples/models/llama/run_llama.py:60-68)."""
+    (examples/models/llama/run_llama.py:60-68).  ``tiny_overrides``: configuration fields of the ``--tiny 1``
+    shape that are specific to the family (per-stage lists, token ids).  ``loss_fn``: ``model -> loss(outputs,
+    labels)`` for heads whose loss is not a token cross entropy (CTC), the counterpart of the reference scripts'
+    ``get_loss_fn`` overrides (examples/models/wav2vec2/run_wav2vec2.py:72-119)."""
     import inspect
     extra = {"tiny": 0, "seq_length": 128, "dataset_size": 512}
     extra.update(defaults or {})
     args, own = parse(extra)
     Merak.init(**degrees())
-    kw = dict(config_overrides or {})
+    kw = {}
     if own.tiny:
         accepted = set(inspect.signature(config_cls.__init__).parameters)
         probe = config_cls()
         kw.update({k: v for k, v in TINY.items() if k in accepted or hasattr(probe, k)})
+        kw.update(tiny_overrides or {})          # family-specific shapes (per-stage lists and the like)
         own.seq_length = min(own.seq_length, 32)
+    kw.update(config_overrides or {})
     config = config_cls(**kw)
     for name in ("hidden_dropout_prob", "attention_probs_dropout_prob", "dropout", "attention_dropout",
                  "activation_dropout", "resid_pdrop", "embd_pdrop", "attn_pdrop", "dropout_rate", "classifier_dropout"):
@@ -50,6 +56,7 @@ def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, c
         from merak_b200.parallel.tp_transform import set_tp_layer_lists
         set_tp_layer_lists(col_para_list=tp_lists[0], row_para_list=tp_lists[1])
     train = DynamicGenDataset(config, mode=mode, dataset_size=own.dataset_size, seq_length=own.seq_length)
-    trainer = Merak.MerakTrainer(model, args, train_dataset=train)
+    trainer = Merak.MerakTrainer(model, args, train_dataset=train,
+                                 loss_fn=loss_fn(model) if loss_fn is not None else None)
     trainer.train()
     return trainer
