@@ -44,6 +44,7 @@ def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, c
         probe = config_cls()
         kw.update({k: v for k, v in TINY.items() if k in accepted or hasattr(probe, k)})
         kw.update(tiny_overrides or {})          # family-specific shapes (per-stage lists and the like)
+        kw = {k: v for k, v in kw.items() if v is not None}      # None drops a generic field (aliases of list fields)
         own.seq_length = min(own.seq_length, 32)
     kw.update(config_overrides or {})
     config = config_cls(**kw)

@@ -34,7 +34,10 @@ struct GemmComm {
   int mode, n, rank;
   int seg_rows;
   int perm;                    // start the row-block order at this rank's own segments
-  int gemm_ctas;               // mode 2: CTAs [0, gemm_ctas) compute, the others gather
+  int gemm_ctas;               // modes 1, 2: the LAST gemm_ctas CTAs of the grid compute; the ones before them
+                               // gather / reduce.  They come first because blocks are handed to SMs in index
+                               // order: if something else holds SMs, it is compute CTAs that start late (they
+                               // only wait for data), never the CTAs everybody else waits for.
   void* peer[kGemmMaxPeers];   // bf16 shards of A, one per rank
   long long ld_peer;           // row pitch of those (elements)
   void* gathered;              // mode 2: local gathered A, row pitch ld_peer
@@ -130,7 +133,7 @@ __device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t 
 
 __device__ __forceinline__ void comm_gather_role(const GemmParams& p, uint8_t* smem, int smem_bytes) {
   const GemmComm& c = p.comm;
-  const int cta_g = blockIdx.x - c.gemm_ctas;
+  const int cta_g = blockIdx.x;                 // the gather CTAs are the first ones of the grid
   const int worker = threadIdx.x >> 5;
   const int g = cta_g * kGatherWorkers + worker, G = (gridDim.x - c.gemm_ctas) * kGatherWorkers;
   SymmCtrl* mine = reinterpret_cast<SymmCtrl*>(c.ctrl[c.rank]);

@@ -63,8 +63,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
   const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
 
-  // fused all-gather: the CTAs behind the compute CTAs only move the peers' shards of A
-  if (p.comm.mode == 2 && (int)blockIdx.x >= p.comm.gemm_ctas) {
+  // fused all-gather: the CTAs in front of the compute CTAs only move the peers' shards of A
+  const int aux_ctas = p.comm.mode == 2 ? (int)gridDim.x - p.comm.gemm_ctas : 0;
+  if (p.comm.mode == 2 && (int)blockIdx.x < aux_ctas) {
     comm_gather_role(p, smem, L::kTotal - 1024);
     return;
   }
@@ -101,7 +102,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += cta_stride) {
+      for (int unit = (int)blockIdx.x - aux_ctas; unit < num_units && ok; unit += cta_stride) {
         int m_blk, n_blk;
         tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
         m_blk = comm_perm_m(p, m_blk, kBlockM);
@@ -146,7 +147,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += cta_stride, ++iter) {
+      for (int unit = (int)blockIdx.x - aux_ctas; unit < num_units && ok; unit += cta_stride, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, p.status);
@@ -179,7 +180,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int row_in_tile = quad * 32 + lane;
     int iter = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < num_units && ok; unit += cta_stride, ++iter) {
+    for (int unit = (int)blockIdx.x - aux_ctas; unit < num_units && ok; unit += cta_stride, ++iter) {
       int m_blk, n_blk;
       tile_coords(unit / p.num_splits, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
       m_blk = comm_perm_m(p, m_blk, kBlockM);

@@ -231,7 +231,7 @@ __device__ __forceinline__ void rs_pull_consumer(const GemmParams& p, uint8_t* r
   }
 }
 
-// A CTA that only reduces (blockIdx >= comm.gemm_ctas): the whole dynamic shared memory is its ring.
+// A CTA that only reduces (one of the first CTAs of the grid): the whole dynamic shared memory is its ring.
 __device__ __forceinline__ void rs_reducer_role(const GemmParams& p, uint8_t* smem, int ring_bytes, uint8_t* bar_area) {
   uint64_t* pull_full = reinterpret_cast<uint64_t*>(bar_area + 256);
   uint64_t* pull_empty = pull_full + 8;
@@ -281,14 +281,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const bool a_mn = (p.flags & MRK_GEMM_A_MN) != 0;
   const bool b_mn = (p.flags & MRK_GEMM_B_MN) != 0;
 
-  // fused all-gather (GemmComm mode 2): the clusters behind the compute clusters only move the peers'
+  // fused all-gather (GemmComm mode 2): the clusters in front of the compute clusters only move the peers'
   // shards of A; both CTAs of such a cluster leave together, so no cluster barrier is left waiting
-  if (p.comm.mode == 2 && (int)blockIdx.x >= p.comm.gemm_ctas) {
+  const int aux_ctas = p.comm.mode != 0 ? (int)gridDim.x - p.comm.gemm_ctas : 0;   // gather / reduce CTAs come first
+  if (p.comm.mode == 2 && (int)blockIdx.x < aux_ctas) {
     comm_gather_role(p, smem, kPairStages * kPairStageBytes + kPairStagingBytes);
     return;
   }
-  // fused reduce-scatter (mode 1): the clusters behind the compute clusters only reduce
-  if (p.comm.mode == 1 && (int)blockIdx.x >= p.comm.gemm_ctas) {
+  // fused reduce-scatter (mode 1): the clusters in front of the compute clusters only reduce
+  if (p.comm.mode == 1 && (int)blockIdx.x < aux_ctas) {
     rs_reducer_role(p, smem, kPairStages * kPairStageBytes + kPairStagingBytes, bar_base);
     return;
   }
@@ -327,7 +328,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int cluster_id = blockIdx.x >> 1;
+  const int cluster_id = ((int)blockIdx.x - aux_ctas) >> 1;
   const int num_clusters = (p.comm.mode != 0 ? p.comm.gemm_ctas : (int)gridDim.x) >> 1;
   const bool rs = p.comm.mode == 1;
   // reduce-only launches (single-GPU tests of the reduce phase) skip the multiplication
