@@ -133,6 +133,8 @@ class MerakTrainer:
 
         def loss_fn(outputs, labels):
             logits = outputs[0] if isinstance(outputs, (tuple, list)) else outputs
+            if isinstance(logits, dict):          # a model output object that survived tracing as a mapping
+                logits = logits["logits"] if "logits" in logits else next(iter(logits.values()))
             if isinstance(labels, dict):
                 labels = labels.get("labels", next(iter(labels.values())))
             if causal:
