@@ -25,14 +25,28 @@ TINY = dict(
 )
 
 
+class _Mapped:
+    """A dataset whose samples pass through ``fn`` (sample dict -> sample dict)."""
+
+    def __init__(self, base, fn):
+        self.base, self.fn = base, fn
+
+    def __len__(self):
+        return len(self.base)
+
+    def __getitem__(self, i):
+        return self.fn(self.base[i])
+
+
 def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, config_overrides=None,
-        tiny_overrides=None, loss_fn=None):
+        tiny_overrides=None, loss_fn=None, sample_fn=None):
     """``tp_lists``: (column-parallel names, row-parallel names) for models without a built-in feature
     dict, the counterpart of the reference scripts' ``set_tp_layer_lists`` calls
     (examples/models/llama/run_llama.py:60-68).  ``tiny_overrides``: configuration fields of the ``--tiny 1``
     shape that are specific to the family (per-stage lists, token ids).  ``loss_fn``: ``model -> loss(outputs,
     labels)`` for heads whose loss is not a token cross entropy (CTC), the counterpart of the reference scripts'
-    ``get_loss_fn`` overrides (examples/models/wav2vec2/run_wav2vec2.py:72-119)."""
+    ``get_loss_fn`` overrides (examples/models/wav2vec2/run_wav2vec2.py:72-119).  ``sample_fn``: applied to
+    every generated sample (feature layout fixes)."""
     import inspect
     extra = {"tiny": 0, "seq_length": 128, "dataset_size": 512}
     extra.update(defaults or {})
@@ -57,6 +71,8 @@ def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, c
         from merak_b200.parallel.tp_transform import set_tp_layer_lists
         set_tp_layer_lists(col_para_list=tp_lists[0], row_para_list=tp_lists[1])
     train = DynamicGenDataset(config, mode=mode, dataset_size=own.dataset_size, seq_length=own.seq_length)
+    if sample_fn is not None:       # reshape generated samples into what this family's forward expects
+        train = _Mapped(train, sample_fn)
     trainer = Merak.MerakTrainer(model, args, train_dataset=train,
                                  loss_fn=loss_fn(model) if loss_fn is not None else None)
     trainer.train()

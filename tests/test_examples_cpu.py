@@ -25,6 +25,7 @@ COMMON = ["--per_device_train_batch_size", "2", "--gradient_accumulation_steps",
     ("models/convnext/run_convnext.py", ["--tiny", "1", "--dataset_size", "32"]),
     ("models/marianmt/run_marianmt.py", ["--tiny", "1", "--dataset_size", "32"]),
     ("models/wav2vec2/run_wav2vec2.py", ["--tiny", "1", "--dataset_size", "32"]),      # speech input, CTC loss hook
+    ("models/clip/run_clip.py", ["--tiny", "1", "--dataset_size", "32"]),              # two towers, contrastive loss hook
 ])
 def test_example_runs(tmp_path, script, extra):
     cmd = [sys.executable, os.path.join(ROOT, "examples", script), "--output_dir", str(tmp_path)] + extra + COMMON
