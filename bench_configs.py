@@ -41,6 +41,7 @@ def main():
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--gbs", type=int, default=0)
+    ap.add_argument("--dp-overlap", type=int, default=1, help="reduce data-parallel gradients while the backward pass runs")
     for k in ("pp", "tp", "dp", "ep"):
         ap.add_argument("--" + k, type=int, default=0, help="override the layout (smaller boxes)")
     o = ap.parse_args()
@@ -93,7 +94,7 @@ def main():
         gradient_accumulation_steps=gas, max_steps=10 ** 9, learning_rate=1e-4, weight_decay=0.01, max_grad_norm=1.0,
         lr_scheduler_type="constant", logging_steps=0, wall_clock_breakdown=False, report_to="none",
         activation_checkpointing=c["recompute"], zero_stage=c["zero"] or None, megatron_sequence_parallel=c["sp"],
-        split_method="layer_split", comm_mode=o.comm, seed=0)
+        split_method="layer_split", comm_mode=o.comm, seed=0, overlap_dp_reduce=bool(o.dp_overlap))
     ds = SyntheticTokenDataset(cfg.vocab_size, c["seq"], 1 << 16, task="causal", seed=1)
     trainer = Merak.MerakTrainer(model, args, train_dataset=ds)
     engine = trainer.init_engine()
@@ -104,8 +105,11 @@ def main():
         dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(o.warmup):
+    for i in range(o.warmup):
         engine.train_batch(data_iter)
+        if rank == 0 and os.environ.get("BENCH_PROGRESS") == "1":
+            torch.cuda.synchronize()
+            print("warm-up step %d done" % i, file=sys.stderr, flush=True)
     sync_all()
     sampler = ClockSampler(local)
     sampler.start()
