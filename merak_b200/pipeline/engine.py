@@ -855,13 +855,17 @@ class PipelineEngine:
         self._ov = None
         if getattr(self, "fused_dp", None) is None or not getattr(self.args, "overlap_dp_reduce", True):
             return
-        if mpu.get_expert_parallel_world_size() > 1 and \
-                any(getattr(p, "expert_parallel", False) for p in self.module.parameters()):
+        expert_parallel = mpu.get_expert_parallel_world_size() > 1 and \
+            any(getattr(p, "expert_parallel", False) for p in self.module.parameters())
+        if expert_parallel or mpu.get_model_parallel_world_size() > 1 or mpu.get_sequence_parallel_world_size() > 1 \
+                or self.num_stages > 1:
             # The backward pass of an expert-parallel layer runs all-to-all kernels that wait for their peers.
             # With the gradient pushes of this overlap issued between them, the 27-layer DeepSeek-V2-Lite shape
             # on 4 GPUs stopped making progress (every rank in a bounded wait); without them it runs.  Until
-            # that interaction is understood, such models reduce after the backward pass.  (The same on every
-            # rank: the test reads the model and the topology only.)
+            # that interaction is understood, the overlap is used where it was measured: pure data
+            # parallelism, whose backward pass waits for no peer.  Tensor-, sequence- and pipeline-parallel
+            # backward passes also contain kernels or collectives that wait for peers, so they reduce after
+            # the backward pass.  (The same on every rank: the test reads the model and the topology only.)
             return
         layers = self.module.local_layers
         offset_of = {id(p): o for p, o in zip(self.flat.params, self.flat.offsets)}
