@@ -39,18 +39,21 @@ class _Mapped:
 
 
 def run(config_cls, model_cls, mode="text_only", tp_lists=None, defaults=None, config_overrides=None,
-        tiny_overrides=None, loss_fn=None, sample_fn=None):
+        tiny_overrides=None, loss_fn=None, sample_fn=None, num_layers=None):
     """``tp_lists``: (column-parallel names, row-parallel names) for models without a built-in feature
     dict, the counterpart of the reference scripts' ``set_tp_layer_lists`` calls
     (examples/models/llama/run_llama.py:60-68).  ``tiny_overrides``: configuration fields of the ``--tiny 1``
     shape that are specific to the family (per-stage lists, token ids).  ``loss_fn``: ``model -> loss(outputs,
     labels)`` for heads whose loss is not a token cross entropy (CTC), the counterpart of the reference scripts'
     ``get_loss_fn`` overrides (examples/models/wav2vec2/run_wav2vec2.py:72-119).  ``sample_fn``: applied to
-    every generated sample (feature layout fixes)."""
+    every generated sample (feature layout fixes).  ``num_layers``: the depth the partitioner should assume when
+    the configuration does not state it as one number."""
     import inspect
     extra = {"tiny": 0, "seq_length": 128, "dataset_size": 512}
     extra.update(defaults or {})
     args, own = parse(extra)
+    if num_layers is not None and getattr(args, "num_layers", None) is None:
+        args.num_layers = num_layers       # for configurations whose depth is not one integer field
     Merak.init(**degrees())
     kw = {}
     if own.tiny:
