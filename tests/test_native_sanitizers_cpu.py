@@ -2,8 +2,8 @@
 partitioner (``csrc/autopipe.cpp``) is compiled with ``-fsanitize=address,undefined`` into a small
 driver that replays the recorded cost vectors plus randomised and degenerate ones; any
 out-of-bounds access, leak or undefined operation aborts the driver.  (Device code has no such
-tool on this machine; its checks are the small / odd-shape tests against CPU references and the
-bounds-checking build of ``tests/test_bounds_check_gpu.py``.)"""
+tool on this machine; its checks are the small / odd-shape tests against CPU references, the bounded
+waits that report through a status word, and the two-rank skewed-arrival test.)"""
 import os
 import shutil
 import subprocess
