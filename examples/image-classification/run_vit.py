@@ -75,6 +75,11 @@ def collate(features):
             "labels": torch.stack([torch.as_tensor(f["labels"]) for f in features])}
 
 
+def accuracy(p):
+    """Top-1 accuracy of one evaluation step (``p.predictions``: logits, ``p.label_ids``: classes)."""
+    return {"accuracy": (p.predictions.argmax(dim=-1) == p.label_ids).float().mean().item()}
+
+
 def main():
     args, own = parse({"image_size": 224, "hidden_size": 768, "layers": 12, "heads": 12, "num_labels": 1000,
                        "dataset_size": 2048})
@@ -88,8 +93,10 @@ def main():
     args.input_names = ["pixel_values"]
     args.return_logits = True
     trainer = Merak.MerakTrainer(model, args, train_dataset=train, eval_dataset=evald, data_collator=collate,
-                                 leaf_modules=(ViTLayer,), loss_fn=lambda out, labels: F.cross_entropy(out.float(), labels))
+                                 leaf_modules=(ViTLayer,), compute_metrics=accuracy,
+                                 loss_fn=lambda out, labels: F.cross_entropy(out.float(), labels))
     trainer.train()
+    trainer.evaluation()          # logs "eval loss: ..., accuracy: ..." (also after every epoch with --do_eval true)
 
 
 if __name__ == "__main__":

@@ -37,6 +37,10 @@ def convert_to_sequential(model: nn.Module, args, dummy_inputs: Optional[Dict[st
     shards, input_to_shard = shard_model(gm, args.split_method, args.shard_count, model_type,
                                          args.custom_split_points)
     shards[0].dummy_inputs = dummy_inputs
+    # an exported graph that could not keep the batch size symbolic (or was exported for several pipeline
+    # stages, between which only tensors travel) accepts only the batch size of its dummy inputs
+    static = getattr(gm, "exported_dynamic_batch", True) is False and bool(dummy_inputs)
+    shards[0].static_batch_size = int(next(iter(dummy_inputs.values())).shape[0]) if static else None
     if cache is not None:
         os.makedirs(os.path.dirname(cache), exist_ok=True)
         torch.save((shards, input_to_shard), cache)

@@ -269,13 +269,16 @@ class PipelineEngine:
 
     def eval_batch(self, data_iter: Iterator, compute_loss: bool = True, reduce_output: Optional[str] = "avg",
                    num_micro_batches: Optional[int] = None, batch_fn: Optional[Callable] = None):
-        """Forward-only pass over ``num_micro_batches`` micro-batches.  Returns the averaged loss, or
-        the list of last-stage outputs when ``compute_loss=False`` / ``return_logits`` is set."""
+        """Forward-only pass over ``num_micro_batches`` micro-batches.  Returns the averaged loss; the
+        list of last-stage outputs with ``compute_loss=False``; and with ``args.return_logits`` the triple
+        ``(loss, logits, labels)`` whose lists hold one entry per micro-batch on the last stage and are
+        empty elsewhere (reference: Merak/core/merak_engine.py:1271-1360)."""
         self.module.eval()
         self.data_iter = data_iter if batch_fn is None else (batch_fn(b) for b in data_iter)
         n = num_micro_batches or self.micro_batches
         self.total_loss = None
         self._eval_outputs: List[torch.Tensor] = []
+        self._eval_labels: List = []
         self._compute_loss = compute_loss
         sched = S.InferenceSchedule(n, self.num_stages, self.stage_id)
         if sched.num_pipe_buffers() != self.num_buffers:
@@ -290,11 +293,12 @@ class PipelineEngine:
         self.micro_batches = mb_saved
         self._meta_sent, self._recv_act_meta = saved
         self._compute_loss = True
-        if not compute_loss or self.args.return_logits:
+        if not compute_loss:
             return self._eval_outputs
-        if reduce_output is None:
-            return self.total_loss
-        return self._aggregate_total_loss(n)
+        loss = self.total_loss if reduce_output is None else self._aggregate_total_loss(n)
+        if self.args.return_logits:
+            return loss, self._eval_outputs, self._eval_labels
+        return loss
 
     # ------------------------------------------------------------------------------------------
     # CUDA-graph path (single pipeline stage): forward + backward of a micro-batch is captured once
@@ -456,6 +460,8 @@ class PipelineEngine:
         if self.is_last:
             if not getattr(self, "_compute_loss", True) or (not self._training_pass and self.args.return_logits):
                 self._eval_outputs.append(out.detach() if isinstance(out, torch.Tensor) else out)
+                if getattr(self, "_compute_loss", True):
+                    self._eval_labels.append(self.buf_labels[buf])
                 if not getattr(self, "_compute_loss", True):
                     if self.wall_clock_breakdown:
                         self.timers("forward").stop()

@@ -84,6 +84,7 @@ class PipelineModule(nn.Module):
         else:
             _, self.all_layers, self.input_to_shard = convert_to_sequential(model, args, dummy_inputs, leaf_modules)
         self.num_layers_total = len(self.all_layers)
+        self.static_batch_size = getattr(self.all_layers[0], "static_batch_size", None) if self.all_layers else None
         self.param_counts = [sum(p.numel() for p in l.parameters()) for l in self.all_layers]
         self.parts = self._partition()
         self.local_start, self.local_stop = self.parts[self.stage_id], self.parts[self.stage_id + 1]

@@ -4,7 +4,9 @@ Builds the pipeline module (trace -> shard -> stage assignment -> tensor-paralle
 loaders (data-parallel sharded sampler), the optimizer / scheduler / loss, and drives
 ``PipelineEngine.train_batch``.  The hooks of the reference are kept overridable:
 ``create_dataloader``, ``create_optimizer``, ``create_lr_scheduler``, ``get_loss_fn``,
-``prepare_data``; so are ``evaluation``, ``save_checkpoint`` and ``load_checkpoint``.
+``prepare_data``; so are ``evaluation``, ``save_checkpoint`` and ``load_checkpoint``.  With
+``args.return_logits`` and a ``compute_metrics`` callable the evaluation also reports metrics of the
+logits (accuracy and the like), averaged over the data-parallel group.
 """
 from __future__ import annotations
 
@@ -24,7 +26,7 @@ from .ops.cross_entropy import softmax_cross_entropy
 from .parallel import mpu
 from .pipeline.engine import PipelineEngine
 from .pipeline.module import PipelineModule
-from .printer import log_dist, logger
+from .printer import AccMetric, log_dist, logger
 from .recompute import checkpoint, model_parallel_manual_seed
 from .utils.trainer_utils import BaseParams, MegatronPretrainingRandomSampler, RepeatingLoader, WorkerInitObj
 
@@ -88,7 +90,7 @@ class MerakTrainer:
     def __init__(self, model: nn.Module, args: Optional[MerakArguments] = None, train_dataset: Optional[Dataset] = None,
                  eval_dataset: Optional[Dataset] = None, data_collator: Optional[Callable] = None,
                  leaf_modules: Iterable[type] = (), optimizers=(None, None), loss_fn: Optional[Callable] = None,
-                 tokenizer=None, **kwargs):
+                 tokenizer=None, compute_metrics: Optional[Callable] = None, **kwargs):
         if not mpu.is_initialized():
             initialize.init(1, 1, 1)
         self.args = args or MerakArguments()
@@ -112,6 +114,9 @@ class MerakTrainer:
         self.params = BaseParams(self.args, mpu.get_data_parallel_world_size())
         self.summary_writer = None
         self._user_loss_fn = loss_fn
+        # ``compute_metrics(EvalPrediction) -> {name: value}`` on the evaluation logits (needs ``return_logits``)
+        self.compute_metrics = compute_metrics
+        self.eval_metrics: Dict[str, float] = {}
         self.loss_fn = self.get_loss_fn()
         self.engine: Optional[PipelineEngine] = None
         self.pipe_model: Optional[PipelineModule] = None
@@ -289,22 +294,69 @@ class MerakTrainer:
             return None
         engine = self.init_engine()
         if self.eval_dataloader is None:
-            self.eval_dataloader = self.create_dataloader(self.eval_dataset, self.args.per_device_eval_batch_size, False)
+            bs = self.args.per_device_eval_batch_size
+            static = getattr(self.pipe_model, "static_batch_size", None)
+            if static and bs != static:
+                log_dist("the traced graph has the micro-batch size %d built in: evaluating with it instead of %d"
+                         % (static, bs), ranks=[0])
+                bs = static
+            self.eval_dataloader = self.create_dataloader(self.eval_dataset, bs, False)
         it = self._batch_iter(self.eval_dataloader)
         n_steps = max(1, len(self.eval_dataloader) // engine.micro_batches)
         if max_batches:
             n_steps = min(n_steps, max_batches)
         total = 0.0
+        metrics = AccMetric()
         for _ in range(n_steps):
-            total += float(engine.eval_batch(it))
+            out = engine.eval_batch(it)
+            if self.args.return_logits:
+                # (loss, logits, labels); the lists are filled on the last pipeline stage only
+                out, logits, labels = out
+                if self.compute_metrics is not None and logits:
+                    self._update_metrics(metrics, logits, labels)
+            total += float(out)
         loss = total / n_steps
+        self.eval_metrics = self._gather_metrics(metrics) if self.compute_metrics is not None else {}
         w = self._writer()
         if w is not None:
             w.add_scalar("Eval/loss", loss, self.params.global_steps)
-        log_dist("eval loss: %.4f" % loss, ranks=[0])
+            for name, value in self.eval_metrics.items():
+                w.add_scalar("Eval/%s" % name, value, self.params.global_steps)
+        extra = "".join(", %s: %.4f" % kv for kv in sorted(self.eval_metrics.items()))
+        log_dist("eval loss: %.4f%s" % (loss, extra), ranks=[0])
         if dist.is_initialized():
             dist.barrier()
         return loss
+
+    def _update_metrics(self, metrics: "AccMetric", logits, labels):
+        """Feeds one evaluation step's last-stage outputs to ``compute_metrics`` (the reference's
+        examples/lora/run_vit.py:243-268 does this in a trainer subclass)."""
+        from types import SimpleNamespace
+
+        def first(x):
+            while isinstance(x, (tuple, list, dict)):
+                x = (x["labels"] if "labels" in x else next(iter(x.values()))) if isinstance(x, dict) else x[0]
+            return x
+        preds = torch.cat([first(t).float().cpu() for t in logits])
+        refs = torch.cat([first(t).cpu() for t in labels])
+        for name, value in self.compute_metrics(SimpleNamespace(predictions=preds, label_ids=refs)).items():
+            metrics.update(name, float(value), int(refs.shape[0]))
+
+    def _gather_metrics(self, metrics: "AccMetric") -> Dict[str, float]:
+        """Sample-weighted means over the data-parallel group of what the last pipeline stage measured,
+        handed to every rank (rank 0 writes the log)."""
+        local = {k: (m.total, m.count) for k, m in metrics.metrics.items()}
+        if not dist.is_initialized() or dist.get_world_size() == 1:
+            return {k: t / max(1, c) for k, (t, c) in local.items()}
+        gathered = [None] * dist.get_world_size()
+        dist.all_gather_object(gathered, local)
+        sums: Dict[str, list] = {}
+        for part in gathered:
+            for k, (t, c) in part.items():
+                acc = sums.setdefault(k, [0.0, 0])
+                acc[0] += t
+                acc[1] += c
+        return {k: t / max(1, c) for k, (t, c) in sums.items()}
 
     # ------------------------------------------------------------------------------------------
     def save_checkpoint(self, best_model: bool = False, loss: Optional[float] = None):

@@ -33,3 +33,21 @@ def test_example_runs(tmp_path, script, extra):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stderr[-3000:]
     assert "steps: 2 loss:" in (res.stdout + res.stderr)
+
+
+def test_lora_vit_example_reports_accuracy(tmp_path):
+    """LoRA on a traced Hugging Face ViT over two pipeline stages; the evaluation reports the accuracy
+    of the last stage's logits through ``compute_metrics`` (with the batch size the graph was traced for)."""
+    import re
+    port = 29000 + (os.getpid() + 17) % 1000
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "examples", "lora", "run_vit.py"), "--output_dir",
+           str(tmp_path), "--tiny", "1", "--dataset_size", "32", "--do_eval", "true"] + COMMON
+    env = dict(os.environ, MERAK_QUIET="1", OMP_NUM_THREADS="2", PP="2")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-3000:]
+    m = re.search(r"eval loss: ([0-9.]+), accuracy: ([0-9.]+)", out)
+    assert m, out[-2000:]
+    assert 0.0 <= float(m.group(2)) <= 1.0
+    assert "trainable parameters on this stage: 2048 of" in out      # only the adapters of this stage's layer train
