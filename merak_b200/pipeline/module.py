@@ -25,7 +25,7 @@ from ..fx.convert import convert_to_sequential
 from ..parallel import mpu
 from ..parallel.tp_transform import apply_tensor_parallel
 from ..recompute import checkpoint, get_rng_tracker, pre_checkpoint
-from .partition import partition_balanced, partition_layers
+from .partition import LayerPartition, partition_balanced
 
 
 def stage_aware_ratios(r0: float, stages: int) -> List[float]:
@@ -97,31 +97,7 @@ class PipelineModule(nn.Module):
 
     # ------------------------------------------------------------------------------------------
     def _partition(self) -> List[int]:
-        a = self.args
-        kw = {}
-        if a.partition_method == "parameters":
-            kw["param_counts"] = self.param_counts
-        elif a.partition_method == "custom":
-            kw["custom"] = a.custom_partition
-        elif a.partition_method == "autopipe":
-            # per-shard forward MFLOPs from the profiler (backward = 3x), like the reference's
-            # autopipe path; parameter counts stand in when the model cannot be run here (meta weights)
-            fwd = None
-            dummy = getattr(self.all_layers[0], "dummy_inputs", None)
-            if dummy is not None:
-                try:
-                    from ..fx.split import run_shards
-                    from .profiler import profile_layer_costs
-                    fwd = profile_layer_costs(self.all_layers, lambda: run_shards(self.all_layers, dummy))
-                except Exception:
-                    fwd = None
-            if fwd is None:
-                fwd = [max(1, c // 1000) for c in self.param_counts]
-            kw["fwd_costs"], kw["bwd_costs"] = fwd, [3 * f for f in fwd]
-        parts = partition_layers(a.partition_method, self.num_layers_total, self.num_stages, **kw)
-        if any(parts[i] == parts[i + 1] for i in range(self.num_stages)) and self.num_layers_total >= self.num_stages:
-            parts = partition_layers("uniform", self.num_layers_total, self.num_stages)
-        return parts
+        return LayerPartition(self.args, self.all_layers, self.num_stages, self.param_counts).partition()
 
     def stage_owner(self, layer_idx: int) -> int:
         for s in range(self.num_stages):

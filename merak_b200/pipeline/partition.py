@@ -134,3 +134,59 @@ def partition_layers(method: str, num_layers: int, num_stages: int, param_counts
         starts = autopipe_partition(fwd_costs, bwd_costs, num_stages)
         return starts + [num_layers]
     raise ValueError("unknown partition_method %r" % method)
+
+
+class LayerPartition:
+    """The partition methods as an object over one shard list, the form the pipeline module uses
+    (Merak/core/pipeline/layers_partition.py:29-163): ``uniform()``, ``uniform_floor()``,
+    ``parameters()``, ``custom_layer_idx()`` and ``autopipe()`` each return the stage boundaries;
+    ``partition()`` dispatches on ``args.partition_method`` and falls back to ``uniform`` when a
+    method would leave a stage without shards."""
+
+    def __init__(self, args, layers: Sequence, num_stages: int, param_counts: Sequence[int] = ()):
+        self.args, self.layers, self.num_stages = args, list(layers), int(num_stages)
+        self.param_counts = list(param_counts) or self._count_layer_params()
+
+    def _count_layer_params(self) -> List[int]:
+        return [sum(p.numel() for p in l.parameters()) if l is not None else 0 for l in self.layers]
+
+    def uniform(self) -> List[int]:
+        return partition_layers("uniform", len(self.layers), self.num_stages)
+
+    def uniform_floor(self) -> List[int]:
+        return partition_layers("uniform_floor", len(self.layers), self.num_stages)
+
+    def parameters(self) -> List[int]:
+        return partition_layers("parameters", len(self.layers), self.num_stages, param_counts=self.param_counts)
+
+    def custom_layer_idx(self) -> List[int]:
+        return partition_layers("custom", len(self.layers), self.num_stages, custom=self.args.custom_partition)
+
+    def layer_costs(self) -> List[int]:
+        """Per-shard forward cost for ``autopipe``: MFLOPs from the profiler when the shards can be run
+        on their dummy inputs; parameter counts stand in when they cannot (meta weights)."""
+        dummy = getattr(self.layers[0], "dummy_inputs", None) if self.layers else None
+        if dummy is not None:
+            try:
+                from ..fx.split import run_shards
+                from .profiler import profile_layer_costs
+                return profile_layer_costs(self.layers, lambda: run_shards(self.layers, dummy))
+            except Exception:
+                pass
+        return [max(1, c // 1000) for c in self.param_counts]
+
+    def autopipe(self) -> List[int]:
+        fwd = self.layer_costs()          # the backward pass is taken as three forward passes, as in the reference
+        return partition_layers("autopipe", len(self.layers), self.num_stages, fwd_costs=fwd,
+                                bwd_costs=[3 * f for f in fwd])
+
+    def partition(self, method: str = None) -> List[int]:
+        method = (method or self.args.partition_method).lower()
+        table = {"uniform": self.uniform, "uniform_floor": self.uniform_floor, "parameters": self.parameters,
+                 "custom": self.custom_layer_idx, "autopipe": self.autopipe}
+        if method not in table:
+            raise ValueError("unknown partition_method %r" % method)
+        parts = table[method]()
+        if any(parts[i] == parts[i + 1] for i in range(self.num_stages)) and len(self.layers) >= self.num_stages:
+            parts = self.uniform()
+        return parts

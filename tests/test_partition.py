@@ -75,3 +75,27 @@ def test_partition_layers_dispatch():
     assert P.partition_layers("autopipe", 24, 4, fwd_costs=[1000] * 24, bwd_costs=[3000] * 24) == [0, 6, 12, 18, 24]
     with pytest.raises(ValueError):
         P.partition_layers("custom", 10, 3, custom=[0, 8, 4])
+
+
+def test_layer_partition_object_methods():
+    """``LayerPartition`` gives the five methods over one shard list and falls back to ``uniform`` when a
+    method would leave a stage empty (Merak/core/pipeline/layers_partition.py:29-163)."""
+    from types import SimpleNamespace
+
+    import torch.nn as nn
+
+    from merak_b200.pipeline.partition import LayerPartition
+    layers = [nn.Linear(4, 4 * (1 + (i == 0) * 7)) for i in range(6)]          # the first shard is 8 x the others
+    args = SimpleNamespace(partition_method="parameters", custom_partition=[0, 1, 6])
+    lp = LayerPartition(args, layers, num_stages=2)
+    assert lp.param_counts == [sum(p.numel() for p in l.parameters()) for l in layers]
+    assert lp.uniform() == [0, 3, 6] and lp.uniform_floor() == [0, 3, 6]
+    assert lp.parameters() == [0, 1, 6] == lp.partition()                     # balanced by parameter count
+    assert lp.custom_layer_idx() == [0, 1, 6]
+    auto = lp.autopipe()                                                      # costs from parameter counts here
+    assert auto[0] == 0 and auto[-1] == 6 and len(auto) == 3 and auto[1] in range(1, 6)
+    args.custom_partition = [0, 0, 6]                                         # a stage without shards
+    assert lp.partition("custom") == lp.uniform()
+    import pytest
+    with pytest.raises(ValueError):
+        lp.partition("nonsense")
