@@ -103,6 +103,36 @@ class _no_layerdrop:
         return False
 
 
+class _dict_outputs_inside:
+    """Configurations written for older ``transformers`` set ``return_dict=False`` (every model
+    configuration of the reference's examples does).  In transformers 5.x the inner modules then hand
+    tuples to heads that read ``outputs.last_hidden_state``.  While exporting, the configurations say
+    ``return_dict=True`` and only the outermost call is asked for a tuple (``_constant_kwargs``)."""
+
+    def __init__(self, model: nn.Module):
+        self.model, self.saved = model, []
+
+    def __enter__(self):
+        seen = set()
+        for m in self.model.modules():
+            cfg = getattr(m, "config", None)
+            if cfg is None or id(cfg) in seen:
+                continue
+            seen.add(id(cfg))
+            try:
+                if getattr(cfg, "return_dict", True) is False:
+                    cfg.return_dict = True
+                    self.saved.append(cfg)
+            except Exception:
+                pass
+        return self
+
+    def __exit__(self, *exc):
+        for cfg in self.saved:
+            cfg.return_dict = False
+        return False
+
+
 class _all_on_meta:
     """A model built under ``init_empty_weights`` has its large weights on the meta device and the rest
     (norm weights, rotary tables) in host memory; tracing needs one device.  For the duration of the
@@ -145,7 +175,8 @@ def export_flat(model: nn.Module, dummy_inputs: Dict[str, torch.Tensor], dynamic
         args = tuple(t.to("meta") for t in args)
     fused_saved, fused_tp.ENABLED = fused_tp.ENABLED, False
     try:
-        with shape_only_collectives(), _no_layerdrop(), (_all_on_meta(model) if on_meta else contextlib.nullcontext()):
+        with shape_only_collectives(), _no_layerdrop(), _dict_outputs_inside(model), \
+                (_all_on_meta(model) if on_meta else contextlib.nullcontext()):
             ep = None
             if dynamic_batch and all(t.dim() >= 1 and t.shape[0] == args[0].shape[0] and t.shape[0] > 1 for t in args):
                 try:
@@ -402,7 +433,7 @@ def _agrees(gm: fx.GraphModule, model: nn.Module, dummy_inputs: Dict[str, torch.
     try:
         model.eval()
         gm.eval()
-        with torch.no_grad():
+        with torch.no_grad(), _dict_outputs_inside(model):
             want = _TensorInputsOnly(model, names, _constant_kwargs(model, names))(*dummy_inputs.values())
             got = gm(*dummy_inputs.values())
         want = want if isinstance(want, (tuple, list)) else (want,)

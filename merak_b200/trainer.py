@@ -223,12 +223,12 @@ class MerakTrainer:
         if self.engine is not None:
             return self.engine
         a = self.args
-        self.train_dataloader = self.create_dataloader(self.train_dataset, a.per_device_train_batch_size)
+        self.train_dataloader = self._make_dataloader(self.train_dataset, a.per_device_train_batch_size, True)
         n_mb = len(self.train_dataloader) if self.train_dataloader is not None and hasattr(self.train_dataloader, "__len__") else None
         self.params.train(n_mb)
         self.engine = PipelineEngine(self.pipe_model, a, optimizer=self.optimizer, lr_scheduler=self.lr_scheduler,
                                      loss_fn=self.loss_fn,
-                                     optimizer_factory=(lambda p: self.create_optimizer(p)) if self._wants_custom_optimizer() else None,
+                                     optimizer_factory=self._make_optimizer if self._wants_custom_optimizer() else None,
                                      lr_scheduler_factory=self.create_lr_scheduler)
         self.optimizer, self.lr_scheduler = self.engine.optimizer, self.engine.lr_scheduler
         # Tracing, sharding and the tensor-parallel rebuild have drawn from the default generators since the
@@ -237,6 +237,29 @@ class MerakTrainer:
         # tensor-parallel group draw the same dropout masks for the activations they all hold.
         model_parallel_manual_seed(a.seed)
         return self.engine
+
+    # The hooks may be overridden with this class's signatures or with the reference's
+    # (``create_dataloader(self)`` sets / returns the training loader, Merak/merak_trainer.py:189-223;
+    # ``create_optimizer(self, model)`` reads ``model.named_parameters()``, :225-257): both forms are called
+    # the way they were written.
+    @staticmethod
+    def _positional_count(fn) -> int:
+        import inspect
+        return sum(1 for p in inspect.signature(fn).parameters.values()
+                   if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD, p.VAR_POSITIONAL))
+
+    def _make_dataloader(self, dataset, batch_size: int, train: bool):
+        if self._positional_count(self.create_dataloader) == 0:       # reference-style override, training data only
+            if not train:
+                return MerakTrainer.create_dataloader(self, dataset, batch_size, False)
+            made = self.create_dataloader()
+            return made if made is not None else self.train_dataloader
+        return self.create_dataloader(dataset, batch_size, train)
+
+    def _make_optimizer(self, params):
+        if self._positional_count(self.create_optimizer) == 0:
+            return self.create_optimizer()
+        return self.create_optimizer(_OptimizerTarget(params, self.pipe_model))
 
     def _wants_custom_optimizer(self) -> bool:
         return self.args.adafactor or type(self).create_optimizer is not MerakTrainer.create_optimizer
@@ -300,7 +323,7 @@ class MerakTrainer:
                 log_dist("the traced graph has the micro-batch size %d built in: evaluating with it instead of %d"
                          % (static, bs), ranks=[0])
                 bs = static
-            self.eval_dataloader = self.create_dataloader(self.eval_dataset, bs, False)
+            self.eval_dataloader = self._make_dataloader(self.eval_dataset, bs, False)
         it = self._batch_iter(self.eval_dataloader)
         n_steps = max(1, len(self.eval_dataloader) // engine.micro_batches)
         if max_batches:
@@ -378,6 +401,33 @@ class MerakTrainer:
         from .lora import inject_lora
         cfg = self.args.get_lora_config()
         inject_lora(self.engine, cfg, self.args.adapter_name)
+
+
+class _OptimizerTarget(list):
+    """What ``create_optimizer`` receives: the list of this stage's parameters to optimise (each once, tied
+    copies removed), which also answers ``named_parameters()`` / ``parameters()`` / ``named_modules()`` /
+    ``modules()`` like the pipeline module the reference passes, restricted to those parameters."""
+
+    def __init__(self, params, module: nn.Module):
+        super().__init__(params)
+        self._module = module
+
+    def named_parameters(self, *args, **kwargs):
+        keep = {id(p) for p in self}
+        seen = set()
+        for name, p in self._module.named_parameters(*args, **kwargs):
+            if id(p) in keep and id(p) not in seen:
+                seen.add(id(p))
+                yield name, p
+
+    def parameters(self, *args, **kwargs):
+        return iter(self)
+
+    def named_modules(self, *args, **kwargs):
+        return self._module.named_modules(*args, **kwargs)
+
+    def modules(self):
+        return self._module.modules()
 
 
 class _WholeModel(nn.Module):

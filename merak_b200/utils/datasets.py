@@ -17,7 +17,7 @@ class DynamicGenDataset(Dataset):
                  image_size: Optional[int] = None, seed: int = 0, vocab_limit: Optional[int] = 1000):
         if mode not in MODES:
             raise ValueError("mode must be one of %s" % (MODES,))
-        self.cfg, self.mode, self.size = model_config, mode, dataset_size
+        self.cfg, self.mode, self.size = model_config, mode, int(dataset_size)      # the reference scripts pass 1e6
         self.seq = seq_length or int(getattr(model_config, "max_position_embeddings", None)
                                      or getattr(model_config, "n_positions", 128) or 128)
         img = image_size or getattr(model_config, "image_size", 224)

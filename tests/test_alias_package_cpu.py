@@ -125,3 +125,77 @@ def test_reference_style_script_runs(tmp_path):
     out = res.stdout + res.stderr
     assert res.returncode == 0, out[-3000:]
     assert "steps: 2 loss:" in out and "dp rank 0 done" in out
+
+
+def test_reference_style_trainer_subclass(tmp_path):
+    """A trainer subclass with the reference's hook signatures (examples/bert_pretraining/run_bert.py:90-145 of
+    the reference: ``create_dataloader(self)`` that sets ``self.train_dataloader``, ``create_optimizer(self,
+    opt_model)`` that groups ``opt_model.named_parameters()``, ``create_lr_scheduler``, ``get_loss_fn``) trains."""
+    import os
+    import subprocess
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "run.py"
+    script.write_text(textwrap.dedent("""
+        import sys
+        sys.path.insert(0, %r)
+        import torch
+        import Merak
+        from Merak import MerakArguments, MerakTrainer
+        from Merak.core import mpu
+        from Merak.utils import WorkerInitObj
+        from Merak.utils.datasets import DynamicGenDataset
+        from transformers import BertConfig, BertForMaskedLM
+
+        Merak.init(1, 1, 1, backend="gloo")
+        args = MerakArguments(output_dir=%r, per_device_train_batch_size=2, gradient_accumulation_steps=2, max_steps=3,
+                              logging_steps=1, no_cuda=True, report_to="none", learning_rate=1e-3)
+        config = BertConfig(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, intermediate_size=128,
+                            max_position_embeddings=64, vocab_size=512, return_dict=False,
+                            hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+        model = BertForMaskedLM(config)
+        calls = []
+
+        class BertTrainer(MerakTrainer):
+            def create_dataloader(self):
+                sampler = torch.utils.data.RandomSampler(self.train_dataset)
+                worker_init = WorkerInitObj(self.args.seed + mpu.get_data_parallel_rank())
+                self.train_dataloader = torch.utils.data.DataLoader(
+                    self.train_dataset, sampler=sampler, batch_size=self.args.per_device_train_batch_size,
+                    num_workers=0, worker_init_fn=worker_init)
+                calls.append("dataloader")
+
+            def get_loss_fn(self):
+                criterion = torch.nn.CrossEntropyLoss(ignore_index=-100)
+                def loss_fn(outputs, labels):
+                    logits = outputs[0] if isinstance(outputs, (tuple, list)) else outputs
+                    return criterion(logits.view(-1, logits.size(-1)).float(), labels.view(-1))
+                return loss_fn
+
+            def create_optimizer(self, opt_model):
+                named = list(opt_model.named_parameters())
+                assert named and len({id(p) for _, p in named}) == len(named)
+                no_decay = ["bias", "LayerNorm"]
+                groups = [{"params": [p for n, p in named if not any(nd in n for nd in no_decay)], "weight_decay": 0.01},
+                          {"params": [p for n, p in named if any(nd in n for nd in no_decay)], "weight_decay": 0.0}]
+                assert groups[0]["params"] and groups[1]["params"]
+                calls.append("optimizer")
+                return torch.optim.AdamW(groups, lr=self.args.learning_rate)
+
+            def create_lr_scheduler(self, optimizer):
+                calls.append("scheduler")
+                return torch.optim.lr_scheduler.LambdaLR(optimizer, lambda step: 1.0)
+
+        dataset = DynamicGenDataset(config, mode="text_only", dataset_size=32, seq_length=32)
+        trainer = BertTrainer(model=model, args=args, train_dataset=dataset)
+        trainer.train()
+        assert calls == ["dataloader", "optimizer", "scheduler"], calls
+        assert isinstance(trainer.engine.optimizer, torch.optim.AdamW)
+        print("hooks ok")
+    """ % (root, str(tmp_path))))
+    env = dict(os.environ, MERAK_QUIET="1", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29000 + (os.getpid() + 47) % 1000),
+               RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", OMP_NUM_THREADS="2")
+    res = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=600, env=env, cwd=str(tmp_path))
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-3000:]
+    assert "steps: 3 loss:" in out and "hooks ok" in out
