@@ -33,6 +33,7 @@ from .layers import ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedd
 COL_PARA_LIST: List[str] = []
 ROW_PARA_LIST: List[str] = []
 CONV_PARA_LIST: List[str] = []
+WEIGHT_CHANGE_LIST: List = []       # (name fragment, dimension): weights that are not linear layers but hold one slice per head
 TP_ATTR_LIST: List[str] = ["num_heads", "split_size", "n_heads", "inner_dim", "num_attention_heads",
                            "all_head_size", "num_key_value_heads", "embed_dim"]
 MANUAL = {"set": False}
@@ -45,7 +46,10 @@ DEFAULT_FEATURES: Dict[str, Dict[str, List[str]]] = {
               "row": ["o_proj", "down_proj"]},
     "t5": {"col": ["SelfAttention.q", "SelfAttention.k", "SelfAttention.v", "EncDecAttention.q", "EncDecAttention.k",
                    "EncDecAttention.v", "DenseReluDense.wi"], "row": ["SelfAttention.o", "EncDecAttention.o",
-                                                                       "DenseReluDense.wo"]},
+                                                                       "DenseReluDense.wo"],
+           # the relative position bias is an embedding [buckets, heads]: each rank keeps its heads' columns
+           # (Merak/core/tensor_parallel/mp_mapping.py:34-40)
+           "weight": [("relative_attention_bias", 1)]},
     "vit": {"col": ["attention.query", "attention.key", "attention.value", "intermediate.dense"],
             "row": ["attention.output.dense", "output.dense"]},
 }
@@ -57,9 +61,13 @@ for alias, base in (("qwen", "llama"), ("qwen2", "llama"), ("mistral", "llama"),
 def set_tp_layer_lists(col_para_list: Optional[Sequence[str]] = None, row_para_list: Optional[Sequence[str]] = None,
                        conv_para_list: Optional[Sequence[str]] = None, input_output_mapping=None,
                        weight_change_list=None, tp_attr_list: Optional[Sequence[str]] = None):
-    """Registers which layers (by name fragment) become column-/row-parallel.  ``input_output_mapping``
-    and ``weight_change_list`` are accepted for signature compatibility: shapes are derived from the
-    layers themselves here, so they carry no extra information."""
+    """Registers which layers (by name fragment) become column-/row-parallel.  ``weight_change_list``:
+    ``(name fragment, dim)`` pairs of other weights that are cut along ``dim`` (T5's relative position bias;
+    a linear layer named there becomes column-parallel for ``dim`` 0 and row-parallel for ``dim`` 1, as in
+    Merak/core/tensor_parallel/mp_attrs.py:57-81).  ``input_output_mapping`` is accepted for signature
+    compatibility: shapes are derived from the layers themselves here."""
+    if weight_change_list is not None:
+        WEIGHT_CHANGE_LIST[:] = [(str(n), int(d)) for n, d in weight_change_list]
     if col_para_list is not None:
         COL_PARA_LIST[:] = list(col_para_list)
     if row_para_list is not None:
@@ -120,6 +128,15 @@ class ColPara(nn.Module):
             p.model_parallel, p.partition_dim = True, 0
         self.fused_parts, self.fused_sizes = parts, sizes
 
+    # model code that inspects ``layer.weight`` / ``layer.bias`` (dtype checks in Hugging Face's T5) sees the shard
+    @property
+    def weight(self):
+        return self.col_linear.weight
+
+    @property
+    def bias(self):
+        return self.col_linear.bias
+
     def forward(self, x, residual=None):
         y = self.col_linear(x)
         return y if residual is None else y + residual
@@ -147,6 +164,14 @@ class RowPara(nn.Module):
         if self.row_linear.bias is not None and self.row_linear.sequence_parallel:
             # added to this rank's sequence shard only: its gradient is summed over the group
             self.row_linear.bias.sequence_parallel = True
+
+    @property
+    def weight(self):
+        return self.row_linear.weight
+
+    @property
+    def bias(self):
+        return self.row_linear.bias
 
     def forward(self, x, residual=None):
         y = self.row_linear(x)
@@ -198,6 +223,33 @@ def feature_lists(model_type: Optional[str]):
     return feats["col"], feats["row"]
 
 
+def weight_change_list(model_type: Optional[str]):
+    if MANUAL["set"]:
+        return list(WEIGHT_CHANGE_LIST)
+    return list((DEFAULT_FEATURES.get((model_type or "").lower()) or {}).get("weight", []))
+
+
+def _shard_listed_weights(model: nn.Module, pairs, tp: int, rank: int) -> List[str]:
+    """Cuts the ``weight`` of every non-linear module named in ``pairs`` along the given dimension and keeps
+    this rank's slice (rank order, like the heads of the column-parallel projections beside it)."""
+    done = []
+    for name, m in model.named_modules():
+        for frag, d in pairs:
+            w = getattr(m, "weight", None)
+            if not _matches(name, [frag]) or isinstance(m, (nn.Linear, ColPara, RowPara)) or \
+                    not isinstance(w, nn.Parameter) or getattr(w, "model_parallel", False):
+                continue
+            if w.shape[d] % tp:
+                raise ValueError("%s.weight has %d entries along dim %d, not divisible by tp=%d" % (name, w.shape[d], d, tp))
+            piece = nn.Parameter(w.data.chunk(tp, dim=d)[rank].contiguous(), requires_grad=w.requires_grad)
+            piece.model_parallel, piece.partition_dim = True, d
+            m.weight = piece
+            if isinstance(m, nn.Embedding):
+                m.num_embeddings, m.embedding_dim = piece.shape
+            done.append(name)
+    return done
+
+
 def convert_conv1d(model: nn.Module, fragments: Sequence[str]) -> int:
     """Hugging Face GPT-2 style ``Conv1D`` layers (``y = x @ W + b`` with ``W`` of shape [in, out])
     named in the feature lists become ``nn.Linear`` layers holding ``W^T``, the form the column /
@@ -235,6 +287,9 @@ def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, me
         return []
     model_type = model_type or getattr(getattr(model, "config", None), "model_type", None)
     col, row = feature_lists(model_type)
+    extra = weight_change_list(model_type)
+    col = list(col) + [f for f, d in extra if d == 0]          # linear layers named there: dim 0 = column, 1 = row
+    row = list(row) + [f for f, d in extra if d == 1]
     replaced = []
     convert_conv1d(model, col + row)
     for parent_name, parent in list(model.named_modules()):
@@ -253,6 +308,7 @@ def apply_tensor_parallel(model: nn.Module, model_type: Optional[str] = None, me
             elif _matches(full, col):
                 setattr(parent, child_name, ColPara(child, sequence_parallel=megatron_sp, seq_dim=seq_dim))
                 replaced.append(full)
+    replaced += _shard_listed_weights(model, extra, tp, mpu.get_model_parallel_rank())
     # head-count style attributes are per-rank after sharding
     for m in model.modules():
         if any(isinstance(c, (ColPara, RowPara)) for c in m.children()):

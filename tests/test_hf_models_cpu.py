@@ -57,7 +57,7 @@ def test_hf_model_pp2_matches_single(tmp_path, model):
     close(pp2["losses"], single["losses"])
 
 
-@pytest.mark.parametrize("model", ["gpt2", "llama"])
+@pytest.mark.parametrize("model", ["gpt2", "llama", "t5"])        # t5: the relative position bias is cut by heads
 def test_hf_model_tp2_matches_single(tmp_path, model):
     single = single_run(tmp_path, model)
     tp2 = run(tmp_path, model + "_tp2", 2, ["--model", model, "--tp", "2"])
