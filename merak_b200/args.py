@@ -43,6 +43,9 @@ class MerakArguments:
     logging_steps: int = 500
     save_steps: int = 500
     eval_steps: Optional[int] = None
+    eval_strategy: str = field(default="no", metadata={
+        "help": "When to evaluate during training: no | steps (every eval_steps) | epoch.  do_eval=true alone means epoch."})
+    evaluation_strategy: Optional[str] = field(default=None, metadata={"help": "Older spelling of eval_strategy."})
     seed: int = 42
     fp16: bool = False
     bf16: bool = False
@@ -162,6 +165,16 @@ class MerakArguments:
             raise ValueError("half_precision_backend must be cuda_amp, apex or cpu_amp")
         if self.fp16 and self.bf16:
             raise ValueError("choose one of fp16 / bf16")
+        if self.evaluation_strategy is not None:
+            self.eval_strategy = self.evaluation_strategy
+        self.eval_strategy = str(getattr(self.eval_strategy, "value", self.eval_strategy)).lower()
+        if self.eval_strategy not in ("no", "steps", "epoch"):
+            raise ValueError("eval_strategy must be no, steps or epoch")
+        if self.eval_strategy == "no" and self.do_eval:
+            self.eval_strategy = "epoch"
+        self.do_eval = self.eval_strategy != "no"
+        if self.eval_strategy == "steps" and not self.eval_steps:
+            self.eval_steps = self.logging_steps          # as in Hugging Face's TrainingArguments
         if isinstance(self.activation_checkpoint_ratio, (str, float, int)):
             self.activation_checkpoint_ratio = [str(self.activation_checkpoint_ratio)]
         self._setup_devices()

@@ -305,7 +305,9 @@ class MerakTrainer:
             if self.params.should_save():
                 self.save_checkpoint()
             spe = self.params.num_steps_per_epoch
-            if a.do_eval and spe and self.params.global_steps % spe == 0:
+            if a.eval_strategy == "steps" and a.eval_steps and self.params.global_steps % a.eval_steps == 0:
+                self.evaluation()
+            elif a.eval_strategy == "epoch" and spe and self.params.global_steps % spe == 0:
                 epoch = self.params.global_steps // spe
                 if epoch != last_eval_epoch:
                     self.evaluation()

@@ -73,3 +73,33 @@ def test_evaluation_accuracy_matches_direct_computation(tmp_path):
         assert torch.allclose(torch.cat(lg), logits[:16], atol=1e-6) and float(l) > 0
     finally:
         Merak.initialize.destroy()
+
+
+def test_eval_strategy_arguments_and_step_evaluation(tmp_path):
+    """``--evaluation_strategy`` (the spelling of the reference's READMEs) / ``--eval_strategy``: ``steps``
+    evaluates every ``eval_steps`` optimizer steps, ``epoch`` after every pass over the data; ``do_eval`` alone
+    means ``epoch``; ``--input_name`` abbreviates ``--input_names`` as in the reference's command lines."""
+    from merak_b200.args import MerakArguments, parse_args
+    a = parse_args(["--evaluation_strategy=epoch", "--no_cuda", "true", "--input_name", "x", "y"])
+    assert (a.eval_strategy, a.do_eval, a.input_names) == ("epoch", True, ["x", "y"])
+    b = MerakArguments(no_cuda=True, eval_strategy="steps", logging_steps=7)
+    assert (b.eval_steps, b.do_eval) == (7, True)
+    assert MerakArguments(no_cuda=True, do_eval=True).eval_strategy == "epoch"
+    assert MerakArguments(no_cuda=True).do_eval is False
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29000 + (os.getpid() + 5) % 1000), RANK="0",
+                      WORLD_SIZE="1", LOCAL_RANK="0", MERAK_QUIET="1")
+    Merak.init(1, 1, 1, backend="gloo")
+    try:
+        args = Merak.MerakArguments(output_dir=str(tmp_path), per_device_train_batch_size=8, per_device_eval_batch_size=8,
+                                    gradient_accumulation_steps=1, max_steps=10, logging_steps=0, no_cuda=True,
+                                    report_to="none", input_names=["x"], eval_strategy="steps", eval_steps=5)
+        trainer = Merak.MerakTrainer(_Net(), args, train_dataset=_Set(256, 3), eval_dataset=_Set(16, 7),
+                                     loss_fn=lambda out, labels: F.cross_entropy(out.float(), labels))
+        at_steps = []
+        plain = trainer.evaluation
+        trainer.evaluation = lambda *a, **k: (at_steps.append(trainer.params.global_steps), plain(*a, **k))[1]
+        trainer.train()
+        assert at_steps == [5, 10], at_steps
+    finally:
+        Merak.initialize.destroy()
