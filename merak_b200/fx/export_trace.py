@@ -243,20 +243,29 @@ def _clean_graph(graph: fx.Graph, devices_are_placeholders: bool):
             graph.erase_node(node)
     if not devices_are_placeholders:
         return
-    first = next((n for n in graph.nodes if n.op == "placeholder"), None)
-    dev_node = None
+    # The device comes from a tensor next to the node that needs it (an operand, else the latest activation
+    # before it), through a ``getattr`` node of its own placed right before it and carrying its module stack:
+    # when the graph is later cut into pipeline stages no ``torch.device`` value has to cross a boundary.
+    is_meta = lambda a: isinstance(a, torch.device) and a.type == "meta"
+    latest = None
     for node in list(graph.nodes):
-        if node.op != "call_function":
-            continue
-        is_meta = lambda a: isinstance(a, torch.device) and a.type == "meta"
-        if first is None or not (any(is_meta(a) for a in node.args) or any(is_meta(v) for v in node.kwargs.values())):
-            continue
-        if dev_node is None:
-            last_ph = [n for n in graph.nodes if n.op == "placeholder"][-1]
-            with graph.inserting_after(last_ph):
-                dev_node = graph.call_function(getattr, (first, "device"))
-        node.args = tuple(dev_node if is_meta(a) else a for a in node.args)
-        node.kwargs = {k: (dev_node if is_meta(v) else v) for k, v in node.kwargs.items()}
+        if node.op == "call_function" and (any(is_meta(a) for a in node.args) or any(is_meta(v) for v in node.kwargs.values())):
+            src = next((a for a in node.all_input_nodes if _is_activation(a)), None) or latest
+            if src is not None:
+                with graph.inserting_before(node):
+                    dev = graph.call_function(getattr, (src, "device"))
+                dev.meta = {k: v for k, v in node.meta.items() if k in ("nn_module_stack", "stack_trace", "source_fn_stack")}
+                node.args = tuple(dev if is_meta(a) else a for a in node.args)
+                node.kwargs = {k: (dev if is_meta(v) else v) for k, v in node.kwargs.items()}
+        if _is_activation(node):
+            latest = node
+
+
+def _is_activation(n: fx.Node) -> bool:
+    """A graph input or a computed tensor (not a parameter / buffer read)."""
+    if n.op == "placeholder":
+        return True
+    return n.op in ("call_function", "call_module") and isinstance(n.meta.get("val"), torch.Tensor)
 
 
 # ---------------------------------------------------------------------------------------------
