@@ -241,6 +241,11 @@ def _clean_graph(graph: fx.Graph, devices_are_placeholders: bool):
     for node in list(graph.nodes):
         if node.op == "call_function" and "_assert" in str(node.target) and not node.users:
             graph.erase_node(node)
+        elif node.op == "call_function" and node.target is torch.ops.aten.detach_.default:
+            # ``torch.tensor(c)`` inside the model exports as an in-place detach of a lifted constant.  When that
+            # constant reaches the node through a shard boundary or a recomputed segment it is an alias made by
+            # ``detach()``, on which the in-place form is an error; the out-of-place form gives the same value.
+            node.target = torch.ops.aten.detach.default
     if not devices_are_placeholders:
         return
     # The device comes from a tensor next to the node that needs it (an operand, else the latest activation
