@@ -15,13 +15,5 @@ TINY_S2T = dict(max_source_positions=64, max_target_positions=64, num_conv_layer
                 conv_channels=32, input_feat_per_channel=80, pad_token_id=0, decoder_start_token_id=0, eos_token_id=1)
 
 
-def time_major(sample):
-    """The generated mel features are [bins, frames]; this family takes [frames, bins] (256 frames here)."""
-    out = dict(sample)
-    out["input_features"] = sample["input_features"].t()[:256].contiguous()
-    return out
-
-
 if __name__ == "__main__":
-    run(T.Speech2TextConfig, T.Speech2TextForConditionalGeneration, mode="speech2text", tiny_overrides=TINY_S2T,
-        sample_fn=time_major)
+    run(T.Speech2TextConfig, T.Speech2TextForConditionalGeneration, mode="speech2text", tiny_overrides=TINY_S2T)   # features arrive as [frames, filter banks]

@@ -88,6 +88,7 @@ def split_graph(gm: fx.GraphModule, node_to_shard: Dict[fx.Node, int], num_shard
             g.output(tuple(env[n] for n in live_out))
         else:
             g.output(fx.node.map_arg(output_node.args[0], lambda a: env[a]))
+        _no_inplace_on_inputs(gm, g)
         sub = ShardModule(gm, g, class_name="Shard%d" % s)
         sub.input_names = [n.name for n in live_in]
         sub.external_inputs = [ph.name for ph in external]
@@ -95,6 +96,52 @@ def split_graph(gm: fx.GraphModule, node_to_shard: Dict[fx.Node, int], num_shard
         sub.shard_index = s
         shards.append(sub)
     return shards, input_to_shard
+
+
+def _no_inplace_on_inputs(gm: fx.GraphModule, g: fx.Graph):
+    """A shard's inputs arrive as leaf tensors that require grad (stage boundary, recomputed segment); an
+    in-place operation on such a tensor is an autograd error.  Where a shard's first use of an input is in
+    place (``nn.ReLU(inplace=True)`` right after a cut in torchvision's ResNets, ``x.add_(...)``,
+    ``F.relu(x, inplace=True)``), the operation runs out of place and every later reader of that input reads
+    its result, which is what the in-place form would have shown them."""
+    import copy
+    order = {n: i for i, n in enumerate(g.nodes)}
+    for node in list(g.nodes):
+        first = node.args[0] if node.args and isinstance(node.args[0], fx.Node) else None
+        if first is None or first.op != "placeholder":
+            continue
+        changed = False
+        if node.op == "call_module":
+            mod = gm.get_submodule(node.target)
+            if getattr(mod, "inplace", False) is True:
+                name = node.target + "_out_of_place"
+                try:
+                    gm.get_submodule(name)
+                except AttributeError:
+                    clone = copy.copy(mod)
+                    clone.inplace = False
+                    gm.add_submodule(name, clone)
+                node.target = name
+                changed = True
+        elif node.op == "call_function" and node.kwargs.get("inplace") is True:
+            node.kwargs = {**node.kwargs, "inplace": False}
+            changed = True
+        elif node.op == "call_function" and isinstance(node.target, torch._ops.OpOverload) and \
+                node.target._schema.name.endswith("_") and node.target._schema.name.startswith("aten::"):
+            # an ATen in-place overload of an exported graph (aten.relu_.default, aten.add_.Tensor)
+            base = getattr(torch.ops.aten, node.target._schema.name[len("aten::"):-1], None)
+            twin = getattr(base, node.target._overloadname, None) if base is not None else None
+            if twin is not None:
+                node.target = twin
+                changed = True
+        elif node.op == "call_method" and node.target.endswith("_") and not node.target.endswith("__") and \
+                hasattr(torch.Tensor, node.target[:-1]):
+            node.target = node.target[:-1]
+            changed = True
+        if changed:
+            for user in list(first.users):
+                if user is not node and order[user] > order[node]:
+                    user.replace_input_with(first, node)
 
 
 def run_shards(shards: List[ShardModule], inputs: Dict[str, torch.Tensor]):

@@ -145,11 +145,59 @@ def _as_list(x):
 
 
 # ---- tensor metadata handshake ----------------------------------------------------------------
-def encode_meta(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
-    """Flat int64 description: [count, (dtype_id, requires_grad, ndim, *shape) ...]."""
+# Values that are not tensors travel as 0-dim tensors; the second field of their description says what to
+# turn them back into on the receiving stage (Python int / float / bool; a ``torch.device`` becomes the
+# receiver's own device).
+KIND_INT, KIND_FLOAT, KIND_BOOL, KIND_DEVICE = 10, 11, 12, 13
+
+
+def to_wire(values, device):
+    """``(tensors, kinds)``: every value as a tensor that can be sent, and its kind code (0 for tensors)."""
+    tensors, kinds = [], []
+    for v in values:
+        if isinstance(v, torch.Tensor):
+            tensors.append(v)
+            kinds.append(0)
+        elif isinstance(v, bool):
+            tensors.append(torch.tensor(v, dtype=torch.bool, device=device))
+            kinds.append(KIND_BOOL)
+        elif isinstance(v, int):
+            tensors.append(torch.tensor(v, dtype=torch.int64, device=device))
+            kinds.append(KIND_INT)
+        elif isinstance(v, float):
+            tensors.append(torch.tensor(v, dtype=torch.float64, device=device))
+            kinds.append(KIND_FLOAT)
+        elif isinstance(v, torch.device):
+            tensors.append(torch.zeros((), dtype=torch.int64, device=device))
+            kinds.append(KIND_DEVICE)
+        else:
+            raise TypeError("a value of type %s cannot travel between pipeline stages" % type(v).__name__)
+    return tensors, kinds
+
+
+def from_wire(tensors, meta, device):
+    """Undoes ``to_wire`` on the receiving stage (``meta`` as returned by ``recv_meta``)."""
+    out = []
+    for t, (_, kind, _) in zip(tensors, meta):
+        if kind == KIND_INT:
+            out.append(int(t.item()))
+        elif kind == KIND_FLOAT:
+            out.append(float(t.item()))
+        elif kind == KIND_BOOL:
+            out.append(bool(t.item()))
+        elif kind == KIND_DEVICE:
+            out.append(torch.device(device))
+        else:
+            out.append(t)
+    return out
+
+
+def encode_meta(tensors: Sequence[torch.Tensor], kinds: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Flat int64 description: [count, (dtype_id, requires_grad or kind code, ndim, *shape) ...]."""
     vals = [len(tensors)]
-    for t in tensors:
-        vals += [_DTYPE_ID[t.dtype], int(t.requires_grad or t.is_floating_point()), t.dim(), *t.shape]
+    for i, t in enumerate(tensors):
+        flag = kinds[i] if kinds and kinds[i] else int(t.requires_grad or t.is_floating_point())
+        vals += [_DTYPE_ID[t.dtype], flag, t.dim(), *t.shape]
     return torch.tensor(vals, dtype=torch.int64)
 
 
@@ -160,15 +208,15 @@ def decode_meta(meta: torch.Tensor) -> List[Tuple[torch.dtype, bool, Tuple[int, 
         dt, rg, nd = vals[pos], vals[pos + 1], vals[pos + 2]
         shape = tuple(vals[pos + 3: pos + 3 + nd])
         pos += 3 + nd
-        out.append((_DTYPES[dt], bool(rg), shape))
+        out.append((_DTYPES[dt], int(rg), shape))           # 0 / 1: tensor without / with gradient; >= 10: kind code
     return out
 
 
-_META_MAX = 256
+_META_MAX = 4096        # int64 words: room for a few hundred tensors crossing one boundary
 
 
-def send_meta(tensors: Sequence[torch.Tensor], to_rank: int, device):
-    meta = encode_meta(tensors)
+def send_meta(tensors: Sequence[torch.Tensor], to_rank: int, device, kinds: Optional[Sequence[int]] = None):
+    meta = encode_meta(tensors, kinds)
     buf = torch.zeros(_META_MAX, dtype=torch.int64)
     buf[0] = meta.numel()
     buf[1:1 + meta.numel()] = meta

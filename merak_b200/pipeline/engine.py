@@ -558,7 +558,7 @@ class PipelineEngine:
             self.buf_out_grads[buf] = None
         if not self.is_first:
             ins = self.buf_inputs[buf] or ()
-            self.buf_in_grads[buf] = [t.grad if (isinstance(t, torch.Tensor) and t.grad is not None) else
+            self.buf_in_grads[buf] = [None if not isinstance(t, torch.Tensor) else t.grad if t.grad is not None else
                                       (torch.zeros_like(t) if t.is_floating_point() else None) for t in ins]
             self.buf_inputs[buf] = None
         if overlap:
@@ -583,7 +583,7 @@ class PipelineEngine:
         bufs = []
         for dtype, rg, shape in meta:
             t = torch.empty(shape, dtype=dtype, device=self.device)
-            if requires_grad_ok and rg and t.is_floating_point():
+            if requires_grad_ok and rg == 1 and t.is_floating_point():
                 t.requires_grad_(True)
             bufs.append(t)
         return bufs
@@ -591,8 +591,7 @@ class PipelineEngine:
     def _exec_send_activations(self, buf: int):
         if self.is_last:
             return
-        outs = [o.detach() if isinstance(o, torch.Tensor) else o for o in self.buf_outputs[buf]]
-        self._ensure_act_meta_sent(outs)
+        outs = self._wire_outputs(buf)
         if self.wall_clock_breakdown:
             self.timers("pipe_send_output").start()
         p2p.send_forward(outs)
@@ -626,9 +625,17 @@ class PipelineEngine:
                 res.append(torch.empty(shape, dtype=dtype, device=o.device))
         return res
 
-    def _ensure_act_meta_sent(self, outs):
+    def _wire_outputs(self, buf: int):
+        """This buffer's stage outputs as the tensors that go to the next stage (Python numbers and devices that
+        a graph cut left among them travel as tagged 0-dim tensors); sends their description once."""
+        outs, kinds = p2p.to_wire([o.detach() if isinstance(o, torch.Tensor) else o for o in self.buf_outputs[buf]],
+                                  self.device)
+        self._ensure_act_meta_sent(outs, kinds)
+        return outs
+
+    def _ensure_act_meta_sent(self, outs, kinds=None):
         if not self._meta_sent["act"]:
-            p2p.send_meta(outs, mpu.get_pipeline_model_parallel_next_rank(), self.device)
+            p2p.send_meta(outs, mpu.get_pipeline_model_parallel_next_rank(), self.device, kinds)
             self._meta_sent["act"] = True
 
     def _ensure_act_meta_recv(self):
@@ -646,7 +653,12 @@ class PipelineEngine:
         p2p.recv_forward(bufs)
         if self.wall_clock_breakdown:
             self.timers("pipe_recv_input").stop()
-        self.buf_inputs[buf] = tuple(bufs)
+        self.buf_inputs[buf] = self._unwire_inputs(bufs)
+
+    def _unwire_inputs(self, bufs):
+        if all(kind < 10 for _, kind, _ in self._recv_act_meta):
+            return tuple(bufs)
+        return tuple(p2p.from_wire(bufs, self._recv_act_meta, self.device))
 
     def _grad_meta(self, buf: int):
         return [(o.dtype, False, tuple(o.shape)) for o in self.buf_outputs[buf] if isinstance(o, torch.Tensor)]
@@ -686,8 +698,7 @@ class PipelineEngine:
         send_buf, recv_buf = bufs
         if self.is_last:
             return
-        outs = [o.detach() for o in self.buf_outputs[send_buf]]
-        self._ensure_act_meta_sent(outs)
+        outs = self._wire_outputs(send_buf)
         routs = self.buf_outputs[recv_buf]
         gb = self._grad_buffers_like(recv_buf)
         if self.wall_clock_breakdown:
@@ -714,7 +725,7 @@ class PipelineEngine:
         if self.wall_clock_breakdown:
             self.timers("pipe_send_grad_recv_input").stop()
         self.buf_in_grads[send_buf] = None
-        self.buf_inputs[recv_buf] = tuple(rb)
+        self.buf_inputs[recv_buf] = self._unwire_inputs(rb)
 
     # -- reductions --------------------------------------------------------------------------------
     def _exec_reduce_tied_grads(self):

@@ -189,11 +189,13 @@ class MerakTrainer:
 
     # ------------------------------------------------------------------------------------------
     def get_dummy_inputs(self) -> Optional[Dict[str, torch.Tensor]]:
-        if self.train_dataset is None:
+        dataset = self.train_dataset if self.train_dataset is not None else self.eval_dataset
+        if dataset is None:
             return None
         # one micro-batch of real samples: a graph exported with static shapes bakes this batch size in
-        n = max(1, min(int(self.args.per_device_train_batch_size), len(self.train_dataset)))
-        sample = self.data_collator([self.train_dataset[i] for i in range(n)])
+        size = self.args.per_device_train_batch_size if self.train_dataset is not None else self.args.per_device_eval_batch_size
+        n = max(1, min(int(size), len(dataset)))
+        sample = self.data_collator([dataset[i] for i in range(n)])
         if isinstance(sample, dict):
             names = self.args.input_names or [k for k in sample if k not in ("labels", "label")]
             return {k: sample[k] for k in names if k in sample}

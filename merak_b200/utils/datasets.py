@@ -9,6 +9,7 @@ import torch
 from torch.utils.data import Dataset
 
 MODES = ("text_only", "multimodal", "vision_only", "condition", "speech", "speech2text", "for_qa")
+SEQ_LENGTH_KEYS = ("seq_length", "max_position_embeddings", "n_positions", "embed_dim", "max_target_positions")
 
 
 class DynamicGenDataset(Dataset):
@@ -18,12 +19,17 @@ class DynamicGenDataset(Dataset):
         if mode not in MODES:
             raise ValueError("mode must be one of %s" % (MODES,))
         self.cfg, self.mode, self.size = model_config, mode, int(dataset_size)      # the reference scripts pass 1e6
-        self.seq = seq_length or int(getattr(model_config, "max_position_embeddings", None)
-                                     or getattr(model_config, "n_positions", 128) or 128)
-        img = image_size or getattr(model_config, "image_size", 224)
+        # two-tower configurations (CLIP, AltCLIP) keep the text sizes in ``text_config`` and the image sizes in
+        # ``vision_config``; the sequence length is the first of the reference's keys the configuration has
+        # (Merak/utils/datasets.py:31-37,88-99)
+        text = getattr(model_config, "text_config", None) or model_config
+        vision = getattr(model_config, "vision_config", None) or model_config
+        inferred = next((getattr(text, k) for k in SEQ_LENGTH_KEYS if isinstance(getattr(text, k, None), int)), None)
+        self.seq = int(seq_length or inferred or 128)
+        img = image_size or getattr(vision, "image_size", None) or getattr(model_config, "image_size", 224)
         self.image_size = img if isinstance(img, int) else img[0]
-        self.channels = int(getattr(model_config, "num_channels", 3))
-        vocab = int(getattr(model_config, "vocab_size", 1000) or 1000)
+        self.channels = int(getattr(vision, "num_channels", 3))
+        vocab = int(getattr(text, "vocab_size", 1000) or 1000)
         self.vocab = min(vocab, vocab_limit) if vocab_limit else vocab
         self.seed = seed
 
@@ -41,6 +47,11 @@ class DynamicGenDataset(Dataset):
         if self.mode == "text_only":
             return {"input_ids": ids, "labels": ids.clone()}
         if self.mode == "for_qa":
+            if hasattr(self.cfg, "visual_feat_dim"):          # LXMERT: region features and boxes beside the question
+                return {"input_ids": ids,
+                        "visual_feats": torch.randn(self.seq, int(self.cfg.visual_feat_dim), generator=g),
+                        "visual_pos": torch.randn(self.seq, int(self.cfg.visual_pos_dim), generator=g),
+                        "labels": torch.zeros(1, dtype=torch.long)}
             return {"input_ids": ids, "start_positions": torch.randint(0, self.seq, (), generator=g),
                     "end_positions": torch.randint(0, self.seq, (), generator=g)}
         if self.mode == "condition":
@@ -54,6 +65,9 @@ class DynamicGenDataset(Dataset):
         feats = torch.randn(16000, generator=g)
         if self.mode == "speech":
             return {"input_values": feats, "labels": torch.randint(1, self.vocab, (32,), generator=g)}
+        if hasattr(self.cfg, "input_feat_per_channel"):    # Speech2Text: [frames, features] filter banks
+            feats = torch.randn(self.seq, int(self.cfg.input_feat_per_channel), generator=g)
+            return {"input_features": feats, "decoder_input_ids": ids.clone(), "labels": ids.clone()}
         mel = torch.randn(int(getattr(self.cfg, "num_mel_bins", 80)), 3000, generator=g)
         return {"input_features": mel, "decoder_input_ids": ids.clone(), "labels": ids.clone()}
 
