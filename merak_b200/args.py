@@ -280,8 +280,10 @@ def mergeargs(training_args: MerakArguments, model_config) -> MerakArguments:
     def lookup(cfg, names):
         for n in names:
             v = getattr(cfg, n, None)
-            if isinstance(v, int):
+            if isinstance(v, int) and not isinstance(v, bool):
                 return v
+            if isinstance(v, dict) and v and all(isinstance(x, int) for x in v.values()):
+                return sum(v.values())      # LXMERT: {"vision": 5, "cross_encoder": 5, "language": 9}
         return None
 
     cfgs = [model_config]
@@ -299,8 +301,11 @@ def mergeargs(training_args: MerakArguments, model_config) -> MerakArguments:
     if training_args.num_layers is None and depths is not None:
         training_args.num_layers = int(sum(depths))
     if training_args.num_layers is None:
-        raise ValueError("num_layers could not be derived from the model config; pass --num_layers")
-    if training_args.shard_count is None:
+        # three-stream configurations (LXMERT: language, cross-modality and region layers)
+        streams = [getattr(model_config, k, None) for k in ("l_layers", "x_layers", "r_layers")]
+        if all(isinstance(v, int) for v in streams):
+            training_args.num_layers = sum(streams)
+    if training_args.shard_count is None and training_args.num_layers is not None:
         training_args.shard_count = 2 * training_args.num_layers + 4
     return training_args
 

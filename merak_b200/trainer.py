@@ -103,7 +103,7 @@ class MerakTrainer:
         config = getattr(model, "config", None)
         if config is not None:
             mergeargs(self.args, config)
-        elif self.args.num_layers is None:
+        if self.args.num_layers is None:        # no configuration, or one that does not state the depth
             self.args.num_layers = max(1, sum(1 for _ in model.children()))
             if self.args.shard_count is None:
                 self.args.shard_count = 2 * self.args.num_layers + 4
