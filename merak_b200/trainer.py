@@ -332,6 +332,10 @@ class MerakTrainer:
         n_steps = max(1, len(self.eval_dataloader) // engine.micro_batches)
         if max_batches:
             n_steps = min(n_steps, max_batches)
+        elif self.args.eval_steps and self.args.eval_strategy != "steps":
+            # the reference's meaning of ``--eval_steps``: how many evaluation steps one evaluation takes
+            # (Merak/utils/parameters.py:72-74); with ``eval_strategy=steps`` it is the interval between evaluations
+            n_steps = min(n_steps, int(self.args.eval_steps))
         total = 0.0
         metrics = AccMetric()
         for _ in range(n_steps):

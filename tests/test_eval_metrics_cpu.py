@@ -101,5 +101,11 @@ def test_eval_strategy_arguments_and_step_evaluation(tmp_path):
         trainer.evaluation = lambda *a, **k: (at_steps.append(trainer.params.global_steps), plain(*a, **k))[1]
         trainer.train()
         assert at_steps == [5, 10], at_steps
+        # without the ``steps`` strategy ``eval_steps`` is the length of one evaluation, as in the reference
+        args.eval_strategy, args.eval_steps = "no", 1
+        calls, eval_batch = [], trainer.engine.eval_batch
+        trainer.engine.eval_batch = lambda *a, **k: (calls.append(1), eval_batch(*a, **k))[1]
+        plain()
+        assert len(calls) == 1, calls
     finally:
         Merak.initialize.destroy()
