@@ -135,7 +135,7 @@ def _no_inplace_on_inputs(gm: fx.GraphModule, g: fx.Graph):
                 node.target = twin
                 changed = True
         elif node.op == "call_method" and node.target.endswith("_") and not node.target.endswith("__") and \
-                hasattr(torch.Tensor, node.target[:-1]):
+                callable(getattr(torch.Tensor, node.target[:-1], None)):       # not ``requires_grad_`` (an attribute)
             node.target = node.target[:-1]
             changed = True
         if changed:
