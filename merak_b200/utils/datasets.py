@@ -14,8 +14,9 @@ SEQ_LENGTH_KEYS = ("seq_length", "max_position_embeddings", "n_positions", "embe
 
 class DynamicGenDataset(Dataset):
 
-    def __init__(self, model_config, mode: str = "text_only", dataset_size: int = 10000, seq_length: Optional[int] = None,
-                 image_size: Optional[int] = None, seed: int = 0, vocab_limit: Optional[int] = 1000):
+    def __init__(self, model_config, mode: str = "text_only", dataset_size: int = 10000, image_size: Optional[int] = None,
+                 seq_length: Optional[int] = None, seed: int = 0, vocab_limit: Optional[int] = 1000):
+        # positional order as in the reference (Merak/utils/datasets.py:62-69)
         if mode not in MODES:
             raise ValueError("mode must be one of %s" % (MODES,))
         self.cfg, self.mode, self.size = model_config, mode, int(dataset_size)      # the reference scripts pass 1e6
